@@ -1,0 +1,329 @@
+"""Decode throughput of the 'cuda fp16i8' path at the RWKV-4 7B shape, one JSON line.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (N = 1 and every rank at N > 1): RWKV-4 7B-shape model (32 x 4096, ffn 16384,
+vocab 50277), seeded random-init weights packed to uint8 on the GPU, a 1024-token seeded
+prompt, then greedy decoding.  One "step" = one decoded token.  Ranks are independent
+streams (token seed 2000 + rank), no collective on the data path: weak scaling.
+
+  value     tokens/s over all ranks; token ids stay on the device (argmax -> next forward).
+  e2e       the same loop through RWKV.forward([int], state) with HOST token ids in and the
+            fp32 logits copied to pinned host memory out, host-side argmax.
+  roofline  mm8_one GEMV launches of a decode step timed one by one with CUDA events:
+            algorithmic bytes / time, against the measured HBM copy bandwidth.
+  cpu_baseline  the reference's CPU arithmetic for the same matmuls (dequantise, then fp32
+            matmul) timed on the host cores over a bounded sample, scaled to a whole token.
+
+--impl reference runs only that CPU arm (rank 0), printing the same line shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOAD = "v4-7b"
+PROMPT = 1024
+METRIC = "fp16i8_decode_tokens_per_s_rwkv4_7b_shape"
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm: the reference's CPU arithmetic for mm8 (dequantise the matrix, then fp32 matmul),
+# restated in oracle/rwkv_oracle.py::mm8_spec, on a bounded sample of a 7B-shape token.
+# ------------------------------------------------------------------------------------------
+def matrices_of_token(shape):
+    import chatrwkv_b200.synth as synth
+    L, D, Fn, V = synth.SHAPES[shape]
+    per_layer = [(D, D)] * 4 + [(D, D), (D, Fn), (Fn, D)]
+    return L, per_layer, (D, V)
+
+
+def cpu_sample_setup(N, M):
+    import torch
+    g = torch.Generator().manual_seed(3000)
+    w = torch.randint(0, 256, (N, M), dtype=torch.uint8, generator=g)
+    mx = torch.randn(M, generator=g) * 0.01
+    rx = torch.rand(M, generator=g) * 0.01
+    my = torch.randn(N, 1, generator=g) * 0.01
+    ry = torch.rand(N, 1, generator=g) * 0.01
+    x = torch.randn(N, generator=g)
+    return x, w, mx, rx, my, ry
+
+
+def cpu_arm(steps, warmup, budget_s=100.0):
+    """Times mm8_spec on (4096, 4096) matrices -- the cost is proportional to the number of
+    weight bytes -- and scales to the 7,185,256,448 weight bytes of one 7B-shape token."""
+    import torch
+    from oracle import rwkv_oracle as orc
+    L, per_layer, head = matrices_of_token(WORKLOAD)
+    token_bytes = L * sum(n * m for n, m in per_layer) + head[0] * head[1]
+    N = M = per_layer[0][0]
+    args = cpu_sample_setup(N, M)
+    t0 = time.perf_counter()
+    orc.mm8_spec(*args)
+    t_one = time.perf_counter() - t0
+    total = max(1, steps + warmup)
+    reps = max(1, min(8, int(budget_s / (t_one * total))))      # matrices per step
+    for _ in range(warmup):
+        for _ in range(reps):
+            orc.mm8_spec(*args)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        for _ in range(reps):
+            orc.mm8_spec(*args)
+    dt = time.perf_counter() - t0
+    bytes_done = steps * reps * N * M
+    tok_s = (bytes_done / dt) / token_bytes
+    return {"value": tok_s, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{steps} steps x {reps} mm8 (dequantise + fp32 matmul) of {N}x{M} uint8, scaled by weight "
+                      f"bytes to a {token_bytes}-byte token", "ms_per_step": dt / steps * 1e3,
+            "host_cpus": os.cpu_count()}
+
+
+# ------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--shape", default=WORKLOAD)
+    ap.add_argument("--prompt", type=int, default=PROMPT)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        cb = cpu_arm(a.steps, a.warmup)
+        line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s", "n_gpus": a.gpus,
+                "steps": a.steps, "warmup": a.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "rwkv4-7b-shape greedy decode, batch 1 (CPU sample of its mm8 matmuls)"},
+                "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from chatrwkv_b200 import synth
+    from chatrwkv_b200.model import RWKV
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    L, D, Fn, V = synth.SHAPES[a.shape]
+    version = 6 if a.shape.startswith("v6") else 4
+    ck = synth.make_checkpoint(version, L, D, Fn, V, seed=1002, device=dev)
+    model = RWKV(ck, f"cuda:{local_rank} fp16i8", verbose=False)
+    del ck
+    torch.cuda.empty_cache()
+    prompt = synth.make_tokens(a.prompt, V, 2000 + rank)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- prefill (reported, not the headline) ------------------------------------------
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    ev0.record()
+    logits, state = model.forward(prompt, None)
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    prefill_ms = ev0.elapsed_time(ev1)
+
+    # ---- device-resident greedy decode --------------------------------------------------
+    tok = torch.argmax(logits).reshape(1)
+    for _ in range(a.warmup):
+        logits, state = model.forward(tok, state)
+        tok = torch.argmax(logits).reshape(1)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    ev0.record()
+    for _ in range(a.steps):
+        logits, state = model.forward(tok, state)
+        tok = torch.argmax(logits).reshape(1)
+    ev1.record()
+    barrier()
+    dev_ms = ev0.elapsed_time(ev1)
+
+    # ---- end to end: host token in, logits to pinned host memory, host argmax ----------
+    host_logits = torch.empty(V, dtype=torch.float32).pin_memory()
+    t_host = int(tok.item())
+    for _ in range(a.warmup):
+        logits, state = model.forward([t_host], state)
+        host_logits.copy_(logits, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        t_host = int(host_logits.argmax())
+    barrier()
+    ev0.record()
+    for _ in range(a.steps):
+        logits, state = model.forward([t_host], state)
+        host_logits.copy_(logits, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        t_host = int(host_logits.argmax())
+    ev1.record()
+    barrier()
+    clocks = sampler.stop()
+    e2e_ms = ev0.elapsed_time(ev1)
+
+    times = torch.tensor([dev_ms, e2e_ms, prefill_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms, prefill_ms = times.tolist()
+
+    # ---- roofline of the dominant kernel (rank 0): each GEMV launch of a token, event-timed
+    roof = None
+    if rank == 0:
+        roof = gemv_roofline(model, dev)
+    cb = None
+    if rank == 0 and world == 1 and not a.no_cpu_baseline:
+        cb = cpu_arm(steps=6, warmup=1, budget_s=25.0)
+
+    if rank == 0:
+        n_mm = L * (7 if version == 4 else 8)
+        launches_per_token = L * 7 + 2
+        line = {
+            "metric": METRIC, "value": world * a.steps / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+            "steps": a.steps, "warmup": a.warmup, "ms_per_step": dev_ms / a.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"rwkv{version}-7b-shape (L={L}, D={D}, ffn={Fn}, vocab={V}) 'cuda fp16i8', batch 1 per "
+                                   f"GPU: {a.prompt}-token prefill then greedy decode; one independent stream per GPU",
+                       "l2": "inputs larger than L2 (7.19 GB of packed weights streamed per step)",
+                       "mm8_matmuls_per_token": n_mm + 1},
+            "e2e": {"value": world * a.steps / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 8,
+                    "d2h_bytes_per_step": V * 4},
+            "gpu_launches": launches_per_token * a.steps * 2,
+            "prefill": {"tokens": a.prompt, "ms": prefill_ms, "tokens_per_s": a.prompt / (prefill_ms / 1e3)},
+            "clocks": clocks, "roofline": roof, "cpu_baseline": cb,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def gemv_roofline(model, dev, reps=3):
+    """Event-time every mm8_one launch of one decode step (eager, outside the graph)."""
+    import torch
+    from chatrwkv_b200 import ops
+    peak, how = measured_peaks()
+    records = []
+    orig = ops.mm8_one_batch
+
+    def timed(problems, dtype, device, ws=None):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        orig(problems, dtype, device, ws)
+        e1.record()
+        nbytes = 0
+        for p in problems:
+            out_b = 4 if p.epilogue in (0, 6) else 2
+            nbytes += p.N * p.M + 6 * p.N + 4 * p.M + out_b * p.M
+        records.append((e0, e1, nbytes))
+
+    ops.mm8_one_batch = timed
+    try:
+        import chatrwkv_b200.model as mm
+        saved = [s.clone() for s in model._gstate]
+        for _ in range(reps):
+            model._step_one()
+        torch.cuda.synchronize(dev)
+        torch._foreach_copy_(model._gstate, saved)
+    finally:
+        ops.mm8_one_batch = orig
+    tot_b = sum(r[2] for r in records)
+    tot_ms = sum(r[0].elapsed_time(r[1]) for r in records)
+    n = len(records)
+    achieved = tot_b / (tot_ms / 1e3) / 1e9
+    traffic = None
+    try:
+        with open(os.path.join(ROOT, "profiles", "mm8_one_traffic.json")) as f:
+            t = json.load(f)
+        traffic = t["dram_bytes_per_algorithmic_byte"] * tot_b / n
+    except Exception:
+        pass
+    return {"bound": "hbm", "kernel": "mm8_one_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "peak_source": how, "traffic": traffic, "launches_timed": n,
+            "avg_launch_us": tot_ms / n * 1e3, "algorithmic_bytes_per_launch": tot_b / n,
+            "frac_of_8000": achieved / 8000.0}
+
+
+if __name__ == "__main__":
+    main()

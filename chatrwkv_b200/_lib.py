@@ -1,0 +1,77 @@
+"""ctypes binding of librwkv_b200.so (the C ABI declared in include/rwkv_b200.h).
+
+The library is the only compute path: when it is missing this module raises, there is no
+CPU or pure-torch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "librwkv_b200.so")
+
+OK = 0
+F32, F16, BF16 = 0, 1, 2
+EPI_ACC_F32, EPI_STORE, EPI_SIGMOID, EPI_RELU_SQ, EPI_RESIDUAL, EPI_MUL_RESIDUAL, EPI_STORE_F32 = range(7)
+
+
+class RwkvB200Error(RuntimeError):
+    pass
+
+
+class Mm8Problem(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("w_stride", C.c_int64),
+        ("mx", C.c_void_p), ("rx", C.c_void_p), ("my", C.c_void_p), ("ry", C.c_void_p),
+        ("y", C.c_void_p), ("aux", C.c_void_p), ("aux2", C.c_void_p),
+        ("N", C.c_int32), ("M", C.c_int32), ("epilogue", C.c_int32), ("out_scale", C.c_float),
+    ]
+
+
+_vp, _i64, _i32, _sz, _f = C.c_void_p, C.c_int64, C.c_int, C.c_size_t, C.c_float
+
+# name -> (restype, argtypes); every symbol include/rwkv_b200.h declares.
+SIGNATURES = {
+    "rwkv_b200_version": (_i32, []),
+    "rwkv_b200_error_string": (C.c_char_p, [_i32]),
+    "rwkv_quantize_weight_workspace_bytes": (_sz, [_i64, _i64]),
+    "rwkv_quantize_weight": (_i32, [_vp, _i32, _i64, _i64, _f, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _sz, _vp]),
+    "rwkv_mm8_one_workspace_bytes": (_sz, [_i64, _i64]),
+    "rwkv_mm8_one": (_i32, [_i64, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _sz, _vp]),
+    "rwkv_mm8_one_batch_workspace_bytes": (_sz, [C.POINTER(Mm8Problem), _i32]),
+    "rwkv_mm8_one_batch": (_i32, [C.POINTER(Mm8Problem), _i32, _i32, _vp, _sz, _vp]),
+    "rwkv_mm8_one_set_split": (None, [_i32]),
+    "rwkv_mm8_seq_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "rwkv_mm8_seq": (_i32, [_i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _sz, _vp]),
+    "rwkv_wkv4_forward": (_i32, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp]),
+    "rwkv_wkv5_forward": (_i32, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp]),
+    "rwkv_wkv6_forward": (_i32, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp]),
+    "rwkv_ln_mix": (_i32, [_i64, _i64, _vp, _i64, _vp, _vp, _vp, _i32, _i32, C.POINTER(_vp), _i64, C.POINTER(_vp), _i64, _vp, _i64, _vp, _vp]),
+    "rwkv_wkv4_one": (_i32, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+}
+
+_lib = None
+
+
+def lib():
+    """Load the library once; raise if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RwkvB200Error(
+                f"{LIB_PATH} not found: build it with `python -m chatrwkv_b200.build` "
+                "(there is no fallback path)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(code, what=""):
+    if code != OK:
+        msg = lib().rwkv_b200_error_string(code).decode()
+        raise RwkvB200Error(f"{what}: {msg} (code {code})")

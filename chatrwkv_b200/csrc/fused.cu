@@ -1,0 +1,158 @@
+// Pointwise pieces of the att / ffn steps, fused into single launches: LayerNorm + token
+// shift mixes (reference: the first lines of att_one / att_seq / ffn_one / ffn_seq and their
+// v6 forms, pkg/model.py:984-1029, 1034-1038, 1263-1276) and the RWKV-4 one-step WKV update
+// (pkg/model.py:1044-1055).  Every torch op on fp16 tensors in the reference rounds once to
+// fp16; r16() marks the same rounding points here.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kLnThreads = 256;
+constexpr int kLnMaxPer = 32;   // D <= 8192
+
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLnThreads / 32; ++i) t += sh[i];
+    return t;
+}
+
+// LayerNorm of one row held in registers: fp32 statistics, one rounding of the result.
+template <int PER>
+__device__ __forceinline__ void layer_norm_row(const __half* __restrict__ x, int D, const __half* __restrict__ w,
+                                               const __half* __restrict__ b, float (&out)[PER], float* sh) {
+    float v[PER];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = threadIdx.x + i * kLnThreads;
+        v[i] = d < D ? __half2float(x[d]) : 0.f;
+        s += v[i];
+    }
+    const float mean = block_sum(s, sh) / float(D);
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = threadIdx.x + i * kLnThreads;
+        const float c = d < D ? v[i] - mean : 0.f;
+        q = fmaf(c, c, q);
+    }
+    const float rstd = rsqrtf(block_sum(q, sh) / float(D) + 1e-5f);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = threadIdx.x + i * kLnThreads;
+        out[i] = d < D ? r16((v[i] - mean) * rstd * __half2float(w[d]) + __half2float(b[d])) : 0.f;
+    }
+}
+
+struct LnMixArgs {
+    const __half* x; long long x_stride;      // [T, D]
+    const __half* sx;                          // [D] previous token's LayerNorm output (state)
+    const __half* ln_w; const __half* ln_b;
+    const __half* mix[5];                      // [D] each (or [T, D] when mix_stride != 0)
+    long long mix_stride;
+    __half* out[5]; long long out_stride;      // [T, D] each
+    __half* xx_out; long long xx_stride;       // optional [T, D]: the LayerNorm output itself
+    __half* new_state;                         // [D]: LayerNorm output of the last row
+    int T, D, n_mix, mode;
+};
+
+// mode 0 (RWKV-4/5):  out = xx*mix + sx*(1-mix)      (pkg/model.py:986, 1036)
+// mode 1 (RWKV-6):    out = xx + (sx-xx)*mix         (pkg/model.py:1009-1011, 1272)
+template <int PER>
+__global__ void __launch_bounds__(kLnThreads) ln_mix_kernel(const LnMixArgs a) {
+    __shared__ float sh[kLnThreads / 32];
+    const int t = blockIdx.x;
+    float xx[PER], prev[PER];
+    layer_norm_row<PER>(a.x + (long long)t * a.x_stride, a.D, a.ln_w, a.ln_b, xx, sh);
+    if (a.n_mix > 0) {
+        if (t == 0) {
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int d = threadIdx.x + i * kLnThreads;
+                prev[i] = d < a.D ? __half2float(a.sx[d]) : 0.f;
+            }
+        } else {
+            layer_norm_row<PER>(a.x + (long long)(t - 1) * a.x_stride, a.D, a.ln_w, a.ln_b, prev, sh);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = threadIdx.x + i * kLnThreads;
+        if (d >= a.D) continue;
+        if (a.xx_out) a.xx_out[(long long)t * a.xx_stride + d] = __float2half_rn(xx[i]);
+        for (int m = 0; m < a.n_mix; ++m) {
+            const float mv = __half2float(a.mix[m][(long long)t * a.mix_stride + d]);
+            float o;
+            if (a.mode == 0) o = r16(r16(xx[i] * mv) + r16(prev[i] * r16(1.0f - mv)));
+            else o = r16(xx[i] + r16(r16(prev[i] - xx[i]) * mv));
+            a.out[m][(long long)t * a.out_stride + d] = __float2half_rn(o);
+        }
+        if (t == a.T - 1 && a.new_state) a.new_state[d] = __float2half_rn(xx[i]);
+    }
+}
+
+// RWKV-4 one-step WKV (pkg/model.py:1041-1055): k, v are the fp16 matmul results widened to
+// fp32; r already went through sigmoid; out = r * wkv in fp16; state in place.
+__global__ void wkv4_one_kernel(int C, const float* __restrict__ t_decay, const float* __restrict__ t_first,
+                                const __half* __restrict__ r, const __half* __restrict__ k,
+                                const __half* __restrict__ v, float* __restrict__ aa, float* __restrict__ bb,
+                                float* __restrict__ pp, __half* __restrict__ out) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const float kk = __half2float(k[c]), vv = __half2float(v[c]);
+    const float a = aa[c], b = bb[c], p0 = pp[c];
+    float ww = t_first[c] + kk;
+    float p = fmaxf(p0, ww);
+    float e1 = expf(p0 - p), e2 = expf(ww - p);
+    const float wkv = r16((e1 * a + e2 * vv) / (e1 * b + e2));
+    ww = t_decay[c] + p0;
+    p = fmaxf(ww, kk);
+    e1 = expf(ww - p); e2 = expf(kk - p);
+    aa[c] = e1 * a + e2 * vv;
+    bb[c] = e1 * b + e2;
+    pp[c] = p;
+    out[c] = __float2half_rn(__half2float(r[c]) * wkv);
+}
+
+}  // namespace
+
+extern "C" int rwkv_ln_mix(int64_t T, int64_t D, const void* x, int64_t x_stride, const void* sx,
+                           const void* ln_w, const void* ln_b, int mode, int n_mix,
+                           const void* const* mix, int64_t mix_stride, void* const* out, int64_t out_stride,
+                           void* xx_out, int64_t xx_stride, void* new_state, void* stream) {
+    RWKV_CHECK_ARG(T >= 1 && T <= INT32_MAX && D >= 1 && D <= kLnThreads * kLnMaxPer);
+    RWKV_CHECK_ARG(x && ln_w && ln_b && n_mix >= 0 && n_mix <= 5 && (mode == 0 || mode == 1));
+    RWKV_CHECK_ARG(n_mix == 0 || (sx && mix && out));
+    LnMixArgs a;
+    a.x = (const __half*)x; a.x_stride = x_stride; a.sx = (const __half*)sx;
+    a.ln_w = (const __half*)ln_w; a.ln_b = (const __half*)ln_b;
+    for (int m = 0; m < 5; ++m) {
+        a.mix[m] = m < n_mix ? (const __half*)mix[m] : nullptr;
+        a.out[m] = m < n_mix ? (__half*)out[m] : nullptr;
+        RWKV_CHECK_ARG(m >= n_mix || (a.mix[m] && a.out[m]));
+    }
+    a.mix_stride = mix_stride; a.out_stride = out_stride;
+    a.xx_out = (__half*)xx_out; a.xx_stride = xx_stride; a.new_state = (__half*)new_state;
+    a.T = int(T); a.D = int(D); a.n_mix = n_mix; a.mode = mode;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int per = int((D + kLnThreads - 1) / kLnThreads);
+    if (per <= 4) ln_mix_kernel<4><<<int(T), kLnThreads, 0, st>>>(a);
+    else if (per <= 16) ln_mix_kernel<16><<<int(T), kLnThreads, 0, st>>>(a);
+    else ln_mix_kernel<kLnMaxPer><<<int(T), kLnThreads, 0, st>>>(a);
+    return rwkv_launch_status();
+}
+
+extern "C" int rwkv_wkv4_one(int64_t C, const float* t_decay, const float* t_first, const void* r,
+                             const void* k, const void* v, float* aa, float* bb, float* pp, void* out,
+                             void* stream) {
+    RWKV_CHECK_ARG(C >= 1 && C <= INT32_MAX && t_decay && t_first && r && k && v && aa && bb && pp && out);
+    wkv4_one_kernel<<<int((C + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        int(C), t_decay, t_first, (const __half*)r, (const __half*)k, (const __half*)v, aa, bb, pp, (__half*)out);
+    return rwkv_launch_status();
+}

@@ -1,0 +1,122 @@
+// mm8_seq: prefill-time dequantising GEMM  y[B,M] = x[B,N] @ dequant(W[N,M]).
+//
+// Same factorisation as mm8_one:  y[i,k] = rx[k] * sum_j x'[i,j] (w[j,k]-128)
+//                                        + rx[k]*128.5*SXR[i] + mx[k]*SX[i] + SXMY[i]
+// with x' = x*ry, SX = sum_j x, SXR = sum_j x', SXMY = sum_j x*my (per row i).
+//
+// This file holds the shape-agnostic CUDA-core kernel (any B, N, M, any stride or
+// alignment).  It is the path for ragged or misaligned operands and for small B.
+#include "common.cuh"
+
+namespace {
+
+constexpr int TM = 64;   // rows of x per CTA
+constexpr int TN = 64;   // columns of W per CTA
+constexpr int TK = 32;   // reduction slice
+
+template <typename F>
+__global__ void __launch_bounds__(256) mm8_seq_simt(int B, int N, int M,
+                                                    const F* __restrict__ x, long long x_stride,
+                                                    const uint8_t* __restrict__ w, long long w_stride,
+                                                    const F* __restrict__ mx, const F* __restrict__ rx,
+                                                    const F* __restrict__ my, const F* __restrict__ ry,
+                                                    F* __restrict__ y, long long y_stride) {
+    __shared__ float xs[TK][TM + 4];
+    __shared__ float ws[TK][TN];
+    __shared__ float rsum[3][TM];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int i0 = blockIdx.y * TM, k0 = blockIdx.x * TN;
+
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+    // Row sums: thread (row = tid / 4, quarter = tid % 4) covers 8 of the 32 j's of a slice.
+    float sx = 0.f, sxr = 0.f, sxmy = 0.f;
+    const int lr = tid >> 2, lq = tid & 3;
+
+    for (int jb = 0; jb < N; jb += TK) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int jj = lq * 8 + e, j = jb + jj, i = i0 + lr;
+            float xp = 0.f;
+            if (i < B && j < N) {
+                const float xv = to_f32<F>(x[(long long)i * x_stride + j]);
+                xp = xv * to_f32<F>(ry[j]);
+                sx += xv;
+                sxr += xp;
+                sxmy = fmaf(xv, to_f32<F>(my[j]), sxmy);
+            }
+            xs[jj][lr] = xp;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int idx = tid + e * 256, jj = idx >> 6, kk = idx & 63;
+            const int j = jb + jj, k = k0 + kk;
+            ws[jj][kk] = (j < N && k < M) ? float(int(w[(long long)j * w_stride + k]) - 128) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int jj = 0; jj < TK; ++jj) {
+            const float4 xa = *reinterpret_cast<const float4*>(&xs[jj][ty * 4]);
+            const float4 wb = *reinterpret_cast<const float4*>(&ws[jj][tx * 4]);
+            const float xv[4] = {xa.x, xa.y, xa.z, xa.w};
+            const float wv[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(xv[a], wv[b], acc[a][b]);
+        }
+        __syncthreads();
+    }
+    // combine the four quarters of each row sum
+    sx += __shfl_xor_sync(0xffffffffu, sx, 1); sx += __shfl_xor_sync(0xffffffffu, sx, 2);
+    sxr += __shfl_xor_sync(0xffffffffu, sxr, 1); sxr += __shfl_xor_sync(0xffffffffu, sxr, 2);
+    sxmy += __shfl_xor_sync(0xffffffffu, sxmy, 1); sxmy += __shfl_xor_sync(0xffffffffu, sxmy, 2);
+    if (lq == 0) { rsum[0][lr] = sx; rsum[1][lr] = sxr; rsum[2][lr] = sxmy; }
+    __syncthreads();
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const int k = k0 + tx * 4 + b;
+        if (k >= M) continue;
+        const float rxk = to_f32<F>(rx[k]), mxk = to_f32<F>(mx[k]);
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const int r = ty * 4 + a, i = i0 + r;
+            if (i >= B) continue;
+            const float val = fmaf(rxk, acc[a][b], fmaf(rxk * 128.5f, rsum[1][r], fmaf(mxk, rsum[0][r], rsum[2][r])));
+            y[(long long)i * y_stride + k] = from_f32<F>(val);
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" size_t rwkv_mm8_seq_workspace_bytes(int64_t B, int64_t N, int64_t M) {
+    (void)B; (void)N; (void)M;
+    return 0;
+}
+
+extern "C" int rwkv_mm8_seq(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
+                            const uint8_t* w, int64_t w_stride,
+                            const void* mx, const void* rx, const void* my, const void* ry, int dtype,
+                            void* y, int64_t y_stride, void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace; (void)workspace_bytes;
+    RWKV_CHECK_ARG(B >= 1 && N >= 1 && M >= 1 && N <= INT32_MAX && M <= INT32_MAX && B <= INT32_MAX);
+    RWKV_CHECK_ARG(x && w && mx && rx && my && ry && y);
+    RWKV_CHECK_ARG(x_stride >= N && w_stride >= M && y_stride >= M);
+    RWKV_CHECK_ARG(dtype == RWKV_F16 || dtype == RWKV_F32);
+    dim3 grid((unsigned)((M + TN - 1) / TN), (unsigned)((B + TM - 1) / TM));
+    if (grid.y > 65535) return RWKV_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == RWKV_F16)
+        mm8_seq_simt<__half><<<grid, 256, 0, st>>>(int(B), int(N), int(M), (const __half*)x, x_stride, w, w_stride,
+                                                    (const __half*)mx, (const __half*)rx, (const __half*)my,
+                                                    (const __half*)ry, (__half*)y, y_stride);
+    else
+        mm8_seq_simt<float><<<grid, 256, 0, st>>>(int(B), int(N), int(M), (const float*)x, x_stride, w, w_stride,
+                                                   (const float*)mx, (const float*)rx, (const float*)my,
+                                                   (const float*)ry, (float*)y, y_stride);
+    return rwkv_launch_status();
+}

@@ -1,0 +1,496 @@
+"""`RWKV(model, strategy).forward(tokens, state)` for the 'cuda fp16i8' strategy, on sm_100a
+kernels.
+
+Mirrors the public surface of the reference runtime class (rwkv_pip_package/src/rwkv/
+model.py:612-1677): constructor arguments, `forward(tokens, state, full_output)`, the state
+list layout (model.py:1448-1471), `.args`, `.version`, `.strategy[i].{device,atype,wtype}`
+and the tensor names in `.w`.  What differs, by design:
+
+  * only single-device `cuda[:N] fp16i8` strategies are implemented (anything else the
+    reference's strategy grammar accepts raises NotImplementedError);
+  * the loader packs on the GPU (ops.quantize_weight) and keeps `emb.weight` on the GPU;
+  * packed matrices have a row stride padded to 16 bytes (their shape is unchanged);
+  * a one-token `forward` is a single CUDA-graph replay of fused kernels; the state tensors
+    it returns are persistent buffers that are updated in place by the next call (pass
+    `copy.deepcopy(state)` around to keep a snapshot, as the reference's callers do).
+
+`model` may also be a checkpoint dict instead of a file name.
+"""
+from __future__ import annotations
+
+import gc
+import os
+import re
+import types
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib, ops
+from ._lib import (EPI_MUL_RESIDUAL, EPI_RELU_SQ, EPI_RESIDUAL, EPI_SIGMOID, EPI_STORE, EPI_STORE_F32, check, lib)
+
+STRATEGY_REGEX = r"^(?:(?:^|->) *(?:cuda(?::[\d]+)?|cpu|mps|dml) (?:fp(?:16|32)|bf16)(?:i8|i4|i3)?(?: \*[\d]+\+?)? *)+$"
+_MATRIX_KEYS = ("key.weight", "value.weight", "receptance.weight", "gate.weight", "output.weight", "head.weight")
+
+
+def _ptr_array(tensors):
+    import ctypes as C
+    arr = (C.c_void_p * max(1, len(tensors)))()
+    for i, t in enumerate(tensors):
+        arr[i] = t.data_ptr()
+    return arr
+
+
+class RWKV:
+    def __init__(self, model, strategy, verbose=True, convert_and_save_and_exit=None):
+        prxxx = print if verbose else (lambda *a, **k: None)
+        if not re.match(STRATEGY_REGEX, strategy):
+            raise ValueError("Invalid strategy. Please read https://pypi.org/project/rwkv/")
+        strategy = ("->".join([x.strip() for x in strategy.split("->")])).replace("->", " -> ")
+        m = re.fullmatch(r"(cuda(?::\d+)?) fp16i8", strategy)
+        if m is None:
+            raise NotImplementedError(
+                f"strategy '{strategy}': this runtime implements single-device 'cuda[:N] fp16i8' only")
+        lib()  # fail loudly now if the CUDA library is not built
+        self.device = torch.device(m.group(1) if ":" in m.group(1) else "cuda:%d" % torch.cuda.current_device())
+        dev = self.device
+        self.args = types.SimpleNamespace()
+        args = self.args
+        args.strategy_string = strategy
+        try:
+            self.RESCALE_LAYER = int(os.environ["RWKV_RESCALE_LAYER"])
+        except Exception:
+            self.RESCALE_LAYER = 6      # 'fp16' in strategy (model.py:634)
+        self._use_graph = os.environ.get("RWKV_B200_GRAPH", "1") != "0"
+
+        if isinstance(model, dict):
+            args.MODEL_NAME = "<dict>"
+            w = dict(model)
+        else:
+            args.MODEL_NAME = model.strip()
+            if not args.MODEL_NAME.endswith(".pth"):
+                args.MODEL_NAME += ".pth"
+            prxxx(f"Loading {args.MODEL_NAME} ...")
+            w = torch.load(args.MODEL_NAME, map_location="cpu")
+        self.w = w
+
+        with torch.no_grad(), torch.cuda.device(dev):
+            already = False
+            if "_strategy" in w:                                     # model.py:646-656
+                already = True
+                assert convert_and_save_and_exit is None
+                prxxx(f"Converted model: strategy {w['_strategy']}, version {w['_version']}\n")
+                assert w["_strategy"] == args.strategy_string
+                assert float(w["_version"]) >= 0.7
+                assert w["_rescale_layer"] == self.RESCALE_LAYER
+                del w["_strategy"], w["_version"], w["_rescale_layer"]
+
+            args.n_embd = w["emb.weight"].shape[1]
+            args.n_att = w["blocks.0.att.key.weight"].shape[0]
+            args.n_ffn = w["blocks.0.ffn.key.weight"].shape[0]
+            if already:   # converted matrices are stored [in, out]
+                args.n_att = w["blocks.0.att.key.weight"].shape[1]
+                args.n_ffn = w["blocks.0.ffn.key.weight"].shape[1]
+            args.n_layer = 0
+            self.version = 4
+            for x in list(w.keys()):                                 # model.py:662-679
+                layer_id = int(x.split(".")[1]) if ("blocks." in x) else 0
+                args.n_layer = max(args.n_layer, layer_id + 1)
+                if "ln_x" in x:
+                    self.version = max(5, self.version)
+                if "gate.weight" in x:
+                    self.version = max(5.1, self.version)
+                if int(self.version) == 5 and "att.time_decay" in x:
+                    args.n_head = w[x].shape[0]
+                    if len(w[x].shape) > 1 and w[x].shape[1] > 1:
+                        self.version = max(5.2, self.version)
+                if "time_maa" in x:
+                    self.version = max(6, self.version)
+                if int(self.version) == 6 and "time_faaaa" in x:
+                    args.n_head = w[x].shape[0]
+            prxxx(f"Model detected: v{self.version:.1f}")
+            if self.version not in (4, 5.2, 6):
+                raise NotImplementedError(f"RWKV v{self.version}: this runtime implements v4, v5.2 and v6")
+            if self.version != 4:
+                self._use_graph = False     # the v5/v6 one-step path still allocates per call
+
+            self.strategy = [types.SimpleNamespace(device=str(dev) if ":" in m.group(1) else "cuda",
+                                                   atype=torch.float16, wtype=torch.uint8, stream=False)
+                             for _ in range(args.n_layer + 1)]
+
+            if not already:                                          # model.py:754-760
+                emb = w["emb.weight"].to(dev)
+                w["emb.weight"] = F.layer_norm(emb.float(), (args.n_embd,),
+                                               weight=w["blocks.0.ln0.weight"].to(dev).float(),
+                                               bias=w["blocks.0.ln0.bias"].to(dev).float())
+                del w["blocks.0.ln0.weight"], w["blocks.0.ln0.bias"], emb
+
+            real_time_first = any(".time_faaaa" in k for k in w)
+            args.time_state = any(".time_state" in k for k in w)
+            if real_time_first:
+                w = {k.replace(".time_faaaa", ".time_first"): v for k, v in w.items()}
+                self.w = w
+
+            for x in list(w.keys()):                                 # model.py:774-869
+                if x.endswith(("_mx", "_rx", "_my", "_ry")):
+                    w[x] = w[x].to(dev).contiguous()
+                    continue
+                layer_id = int(x.split(".")[1]) if ("blocks." in x) else 0
+                if ("ln_out." in x) or ("head." in x):
+                    layer_id = args.n_layer
+                t = w[x].to(dev)
+                t.requires_grad = False
+                if already:
+                    if t.dtype == torch.uint8:
+                        t = self._repad(t)
+                    w[x] = t.contiguous() if t.dtype != torch.uint8 else t
+                    continue
+                scale = 1.0
+                if self.RESCALE_LAYER > 0 and ("att.output.weight" in x or "ffn.value.weight" in x):
+                    scale = 1.0 / (2 ** int(layer_id // self.RESCALE_LAYER))
+                if ".time_" in x:
+                    t = t.squeeze()
+                is_matrix = any(s in x for s in _MATRIX_KEYS)
+                if is_matrix:
+                    t = t.t()
+                if ".time_decay" in x and "_w" not in x:
+                    if self.version == 4:
+                        t = -torch.exp(t.float())
+                    elif self.version == 5.2:
+                        t = torch.exp(-torch.exp(t.float())).reshape(args.n_head, -1, 1)
+                    else:
+                        t = t.float().reshape(args.n_head, -1, 1)
+                elif ".time_first" in x:
+                    if self.version == 4:
+                        t = t.float()
+                    else:
+                        t = t.float().reshape(-1, 1, 1) if real_time_first else torch.exp(t.float()).reshape(-1, 1, 1)
+                        t = t.reshape(args.n_head, -1, 1)
+                elif ".ln_x" in x:
+                    t = t.float()
+                elif len(t.shape) == 2 and "emb" not in x and "_w1" not in x and "_w2" not in x:
+                    q, mx, rx, my, ry = ops.quantize_weight(t, torch.float16, scale)
+                    t = q
+                    w[x + "_mx"], w[x + "_rx"], w[x + "_my"], w[x + "_ry"] = mx, rx, my, ry
+                else:
+                    if scale != 1.0:
+                        t = t * scale
+                    t = t.to(dtype=torch.float16)
+                w[x] = t if t.dtype == torch.uint8 else t.contiguous()
+                if "ffn.value.weight" in x:
+                    gc.collect()
+
+            if convert_and_save_and_exit:                             # model.py:894-903
+                out = {k: (v.contiguous().cpu() if torch.is_tensor(v) else v) for k, v in w.items()}
+                out["_strategy"] = args.strategy_string
+                out["_rescale_layer"] = self.RESCALE_LAYER
+                out["_version"] = "0.7"
+                if not convert_and_save_and_exit.endswith(".pth"):
+                    convert_and_save_and_exit += ".pth"
+                prxxx(f"Saving to {convert_and_save_and_exit}...")
+                torch.save(out, convert_and_save_and_exit)
+                prxxx("Converted and saved. Now this will exit.")
+                raise SystemExit(0)
+
+            if self.version != 4:
+                args.n_head = w["blocks.0.att.time_first"].shape[0]
+            self._init_buffers()
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    # -----------------------------------------------------------------------------------
+    @staticmethod
+    def _repad(q):
+        """Give a contiguous packed matrix the 16-byte row stride the fast kernels want."""
+        N, M = q.shape
+        P = ops.padded_stride(M)
+        if q.stride(0) == P and q.stride(1) == 1:
+            return q
+        full = torch.zeros((N, P), dtype=torch.uint8, device=q.device)
+        full[:, :M].copy_(q)
+        return full[:, :M]
+
+    def _init_buffers(self):
+        a, dev = self.args, self.device
+        D, Fn = a.n_embd, a.n_ffn
+        h = lambda n: torch.zeros(n, dtype=torch.float16, device=dev)
+        self._b = types.SimpleNamespace(
+            x=h(D), m0=h(D), m1=h(D), m2=h(D), m3=h(D), m4=h(D), r=h(a.n_att), k=h(a.n_att), v=h(a.n_att),
+            g=h(a.n_att), att=h(a.n_att), fk=h(Fn), fr=h(D), xln=h(D),
+            logits=torch.zeros(self.w["head.weight"].shape[1], dtype=torch.float32, device=dev),
+            tok=torch.zeros(1, dtype=torch.int64, device=dev))
+        self._tok_host = torch.zeros(256, dtype=torch.int64).pin_memory()   # ring of H2D staging slots
+        self._tok_slot = 0
+        self._ws = torch.zeros(96 << 20, dtype=torch.uint8, device=dev)
+        self._gstate = None     # persistent state tensors the decode graph is bound to
+        self._graph = None
+        self._mm = {}
+
+    def _scales(self, name):
+        e = self._mm.get(name)
+        if e is None:
+            w = self.w
+            e = (w[name], w[name + "_mx"], w[name + "_rx"], w[name + "_my"], w[name + "_ry"])
+            self._mm[name] = e
+        return e
+
+    def _problem(self, x, name, y, epi, aux=None, aux2=None, out_scale=1.0):
+        wq, mx, rx, my, ry = self._scales(name)
+        return ops.make_problem(x, wq, mx, rx, my, ry, y, epi, aux, aux2, out_scale)
+
+    def _gemv(self, problems):
+        ops.mm8_one_batch(problems, torch.float16, self.device, self._ws)
+
+    def _ln_mix(self, T, x, sx, ln_w, ln_b, mode, mixes, outs, xx_out=None, new_state=None, mix_stride=0):
+        D = self.args.n_embd
+        check(lib().rwkv_ln_mix(T, D, x.data_ptr(), x.stride(0) if x.dim() == 2 else D,
+                                sx.data_ptr() if sx is not None else None, ln_w.data_ptr(), ln_b.data_ptr(),
+                                mode, len(mixes), _ptr_array(mixes), mix_stride, _ptr_array(outs),
+                                outs[0].stride(0) if (outs and outs[0].dim() == 2) else D,
+                                xx_out.data_ptr() if xx_out is not None else None,
+                                (xx_out.stride(0) if xx_out.dim() == 2 else D) if xx_out is not None else 0,
+                                new_state.data_ptr() if new_state is not None else None,
+                                torch.cuda.current_stream(self.device).cuda_stream), "ln_mix")
+
+    # -----------------------------------------------------------------------------------
+    def _zero_state(self):
+        """model.py:1448-1471."""
+        a, dev = self.args, self.device
+        st = []
+        for i in range(a.n_layer):
+            if self.version == 4:
+                st += [torch.zeros(a.n_embd, dtype=torch.float16, device=dev),
+                       torch.zeros(a.n_att, dtype=torch.float32, device=dev),
+                       torch.zeros(a.n_att, dtype=torch.float32, device=dev),
+                       torch.zeros(a.n_att, dtype=torch.float32, device=dev) - 1e30,
+                       torch.zeros(a.n_embd, dtype=torch.float16, device=dev)]
+            else:
+                N = a.n_att // a.n_head
+                if a.time_state:
+                    s = self.w[f"blocks.{i}.att.time_state"].transpose(1, 2).to(dtype=torch.float, device=dev).contiguous()
+                else:
+                    s = torch.zeros((a.n_head, N, N), dtype=torch.float32, device=dev)
+                st += [torch.zeros(a.n_embd, dtype=torch.float16, device=dev), s,
+                       torch.zeros(a.n_embd, dtype=torch.float16, device=dev)]
+        return st
+
+    def forward(self, tokens, state, full_output=False):
+        with torch.no_grad(), torch.cuda.device(self.device):
+            if state is None:
+                state = self._zero_state()
+            if torch.is_tensor(tokens):
+                if tokens.is_cuda and tokens.numel() == 1:
+                    return self._forward_one(tokens, state)      # token id stays on the device
+                tokens = tokens.tolist()
+            if len(tokens) == 1:
+                return self._forward_one(int(tokens[0]), state)
+            return self._forward_seq([int(t) for t in tokens], state, full_output)
+
+    # ----- one token ---------------------------------------------------------------------
+    def _bind_state(self, state):
+        """Make `state` the tensors the decode step (and its graph) works on."""
+        g = self._gstate
+        if g is None:
+            self._gstate = [s.contiguous().clone() for s in state]
+            return
+        if len(g) == len(state) and all(a is b for a, b in zip(g, state)):
+            return
+        torch._foreach_copy_(g, [s for s in state])
+
+    def _forward_one(self, token, state):
+        self._bind_state(state)
+        if torch.is_tensor(token):
+            self._b.tok.copy_(token.reshape(1))
+        else:
+            slot = self._tok_slot = (self._tok_slot + 1) % self._tok_host.numel()
+            self._tok_host[slot] = token
+            self._b.tok.copy_(self._tok_host[slot:slot + 1], non_blocking=True)
+        if not self._use_graph:
+            self._step_one()
+        elif self._graph is None:
+            # one eager step on a scratch copy of the state warms every kernel up
+            saved = [s.clone() for s in self._gstate]
+            self._step_one()
+            torch._foreach_copy_(self._gstate, saved)
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._step_one()
+            self._graph = graph
+            torch._foreach_copy_(self._gstate, saved)
+            graph.replay()
+        else:
+            self._graph.replay()
+        return self._b.logits.clone(), list(self._gstate)
+
+    def _step_one(self):
+        b, w, a = self._b, self.w, self.args
+        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
+        st = self._gstate
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        for i in range(a.n_layer):
+            bb, att, ffn = f"blocks.{i}.", f"blocks.{i}.att.", f"blocks.{i}.ffn."
+            if self.version == 4:
+                self._ln_mix(1, b.x, st[i * 5 + 0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 0,
+                             [w[att + "time_mix_k"], w[att + "time_mix_v"], w[att + "time_mix_r"]],
+                             [b.m0, b.m1, b.m2], new_state=st[i * 5 + 0])
+                self._gemv([self._problem(b.m2, att + "receptance.weight", b.r, EPI_SIGMOID),
+                            self._problem(b.m0, att + "key.weight", b.k, EPI_STORE),
+                            self._problem(b.m1, att + "value.weight", b.v, EPI_STORE)])
+                check(lib().rwkv_wkv4_one(a.n_att, w[att + "time_decay"].data_ptr(), w[att + "time_first"].data_ptr(),
+                                          b.r.data_ptr(), b.k.data_ptr(), b.v.data_ptr(), st[i * 5 + 1].data_ptr(),
+                                          st[i * 5 + 2].data_ptr(), st[i * 5 + 3].data_ptr(), b.att.data_ptr(), stream),
+                      "wkv4_one")
+                self._gemv([self._problem(b.att, att + "output.weight", b.x, EPI_RESIDUAL, aux=b.x)])
+                ffn_state = st[i * 5 + 4]
+                mixes = [w[ffn + "time_mix_k"], w[ffn + "time_mix_r"]]
+                mode = 0
+            else:
+                self._att_one_v56(i)
+                ffn_state = st[i * 3 + 2]
+                mixes = [w[ffn + "time_maa_k"], w[ffn + "time_maa_r"]] if self.version == 6 else \
+                        [w[ffn + "time_mix_k"], w[ffn + "time_mix_r"]]
+                mode = 1 if self.version == 6 else 0
+            self._ln_mix(1, b.x, ffn_state, w[bb + "ln2.weight"], w[bb + "ln2.bias"], mode, mixes,
+                         [b.m0, b.m1], new_state=ffn_state)
+            self._gemv([self._problem(b.m1, ffn + "receptance.weight", b.fr, EPI_SIGMOID),
+                        self._problem(b.m0, ffn + "key.weight", b.fk, EPI_RELU_SQ)])
+            scale = 0.5 if (self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0) else 1.0
+            self._gemv([self._problem(b.fk, ffn + "value.weight", b.x, EPI_MUL_RESIDUAL, aux=b.x, aux2=b.fr,
+                                      out_scale=scale)])
+        self._ln_mix(1, b.x, None, w["ln_out.weight"], w["ln_out.bias"], 0, [], [], xx_out=b.xln)
+        self._gemv([self._problem(b.xln, "head.weight", b.logits, EPI_STORE_F32)])
+
+    def _att_one_v56(self, i):
+        """att_one_v5_1 / att_one_v6_0 (model.py:1157-1181, 1263-1298) on the resident state."""
+        b, w, a, st = self._b, self.w, self.args, self._gstate
+        x = b.x.view(1, -1)
+        xs = [st[i * 3 + 0], st[i * 3 + 1]]
+        out = self._att_seq_v56(x, xs, i)
+        b.x.copy_(out.view(-1))
+        st[i * 3 + 0].copy_(xs[0])
+        if xs[1] is not st[i * 3 + 1]:
+            st[i * 3 + 1].copy_(xs[1])
+
+    # ----- sequence ------------------------------------------------------------------------
+    def _mm_seq(self, x, name, out_dtype=None):
+        wq, mx, rx, my, ry = self._scales(name)
+        T = x.shape[0]
+        N, M = wq.shape
+        y = torch.empty((T, M), dtype=torch.float16, device=x.device)
+        torch.ops.rwkv.mm8_seq(T, N, M, x, wq, mx, rx, my, ry, y)
+        return y if out_dtype is None else y.to(out_dtype)
+
+    def _att_seq_v4(self, x, st, i):
+        """cuda_att_seq (model.py:1346-1360)."""
+        w, a = self.w, self.args
+        T, C = x.shape
+        bb, att = f"blocks.{i}.", f"blocks.{i}.att."
+        kx, vx, rx = (torch.empty_like(x) for _ in range(3))
+        new_sx = torch.empty_like(st[i * 5 + 0])
+        self._ln_mix(T, x, st[i * 5 + 0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 0,
+                     [w[att + "time_mix_k"], w[att + "time_mix_v"], w[att + "time_mix_r"]], [kx, vx, rx],
+                     new_state=new_sx)
+        r = torch.sigmoid(self._mm_seq(rx, att + "receptance.weight"))
+        k = self._mm_seq(kx, att + "key.weight", torch.float32)
+        v = self._mm_seq(vx, att + "value.weight", torch.float32)
+        y = torch.empty((T, C), dtype=torch.float32, device=x.device)
+        torch.ops.rwkv.wkv_forward(1, T, C, w[att + "time_decay"], w[att + "time_first"], k, v, y,
+                                   st[i * 5 + 1], st[i * 5 + 2], st[i * 5 + 3])
+        out = self._mm_seq(r * y.to(x.dtype), att + "output.weight")
+        st[i * 5 + 0] = new_sx
+        return x + out
+
+    def _att_seq_v56(self, x, st2, i):
+        """cuda_att_seq_v5_2 / cuda_att_seq_v6_0 (model.py:1363-1439) and, with T = 1, the
+        one-step forms.  `st2` = [att_xx, att_kv]; both entries are replaced."""
+        w, a = self.w, self.args
+        T, C = x.shape
+        H = a.n_head
+        bb, att = f"blocks.{i}.", f"blocks.{i}.att."
+        new_sx = torch.empty_like(st2[0])
+        if self.version == 6:
+            xx = torch.empty_like(x)
+            xxx = torch.empty_like(x)
+            self._ln_mix(T, x, st2[0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 1, [w[att + "time_maa_x"]], [xxx],
+                         xx_out=xx, new_state=new_sx)
+            sx = torch.cat((st2[0].unsqueeze(0), xx[:-1, :])) - xx
+            xxx = torch.tanh(xxx @ w[att + "time_maa_w1"]).view(T, 5, -1).transpose(0, 1)
+            xxx = torch.bmm(xxx, w[att + "time_maa_w2"]).view(5, T, -1)
+            mw, mk, mv, mr, mg = xxx.unbind(dim=0)
+            wx = xx + sx * (w[att + "time_maa_w"] + mw)
+            kx = xx + sx * (w[att + "time_maa_k"] + mk)
+            vx = xx + sx * (w[att + "time_maa_v"] + mv)
+            rx = xx + sx * (w[att + "time_maa_r"] + mr)
+            gx = xx + sx * (w[att + "time_maa_g"] + mg)
+        else:
+            kx, vx, rx, gx = (torch.empty_like(x) for _ in range(4))
+            self._ln_mix(T, x, st2[0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 0,
+                         [w[att + f"time_mix_{n}"] for n in "kvrg"], [kx, vx, rx, gx], new_state=new_sx)
+        r = self._mm_seq(rx, att + "receptance.weight", torch.float32)
+        k = self._mm_seq(kx, att + "key.weight", torch.float32)
+        v = self._mm_seq(vx, att + "value.weight", torch.float32)
+        g = F.silu(self._mm_seq(gx, att + "gate.weight"))
+        S = st2[1].transpose(-1, -2).contiguous()          # kernel layout [H, value, key]
+        y = torch.empty((T, C), dtype=torch.float32, device=x.device)
+        u = w[att + "time_first"]
+        if self.version == 6:
+            ww = w[att + "time_decay"].view(1, C) + (torch.tanh(wx @ w[att + "time_decay_w1"]) @ w[att + "time_decay_w2"]).float()
+            eew = torch.exp(-torch.exp(ww.float())).contiguous()
+            torch.ops.rwkv6.forward_fp32(1, T, C, H, S, r, k, v, eew, u.reshape(-1).contiguous(), y)
+        else:
+            torch.ops.rwkv5.forward_fp32(1, T, C, H, S, r, k, v, w[att + "time_decay"].reshape(-1).contiguous(),
+                                         u.reshape(-1).contiguous(), y)
+        out = F.group_norm(y, num_groups=H, weight=w[att + "ln_x.weight"], bias=w[att + "ln_x.bias"], eps=64e-5)
+        out = out.to(dtype=x.dtype) * g
+        out = self._mm_seq(out, att + "output.weight")
+        st2[0] = new_sx
+        st2[1] = S.transpose(-1, -2)
+        return x + out
+
+    def _ffn_seq(self, x, sx, i):
+        """ffn_seq / ffn_seq_v6 (model.py:995-1004, 1019-1029)."""
+        w = self.w
+        T = x.shape[0]
+        bb, ffn = f"blocks.{i}.", f"blocks.{i}.ffn."
+        kx, rx = torch.empty_like(x), torch.empty_like(x)
+        new_sx = torch.empty_like(sx)
+        if self.version == 6:
+            self._ln_mix(T, x, sx, w[bb + "ln2.weight"], w[bb + "ln2.bias"], 1,
+                         [w[ffn + "time_maa_k"], w[ffn + "time_maa_r"]], [kx, rx], new_state=new_sx)
+        else:
+            self._ln_mix(T, x, sx, w[bb + "ln2.weight"], w[bb + "ln2.bias"], 0,
+                         [w[ffn + "time_mix_k"], w[ffn + "time_mix_r"]], [kx, rx], new_state=new_sx)
+        r = torch.sigmoid(self._mm_seq(rx, ffn + "receptance.weight"))
+        vx = torch.relu(self._mm_seq(kx, ffn + "key.weight")) ** 2
+        out = r * self._mm_seq(vx, ffn + "value.weight")
+        return x + out, new_sx
+
+    def _forward_seq(self, tokens, state, full_output):
+        w, a = self.w, self.args
+        state = list(state)
+        idx = torch.tensor(tokens, dtype=torch.int64, device=self.device)
+        x = w["emb.weight"].index_select(0, idx)
+        for i in range(a.n_layer):
+            if self.version == 4:
+                x = self._att_seq_v4(x, state, i)
+                x, state[i * 5 + 4] = self._ffn_seq(x, state[i * 5 + 4], i)
+            else:
+                st2 = [state[i * 3 + 0], state[i * 3 + 1]]
+                x = self._att_seq_v56(x, st2, i)
+                state[i * 3 + 0], state[i * 3 + 1] = st2
+                x, state[i * 3 + 2] = self._ffn_seq(x, state[i * 3 + 2], i)
+            if self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0:
+                x = x / 2
+        if not full_output:
+            x = x[-1:, :]
+        xln = torch.empty_like(x)
+        self._ln_mix(x.shape[0], x, None, w["ln_out.weight"], w["ln_out.bias"], 0, [], [], xx_out=xln)
+        if full_output:
+            out = self._mm_seq(xln, "head.weight")
+        else:
+            wq, mx, rx, my, ry = self._scales("head.weight")
+            y = torch.zeros(wq.shape[1], dtype=torch.float32, device=self.device)
+            torch.ops.rwkv.mm8_one(wq.shape[0], wq.shape[1], xln[0], wq, mx, rx, my, ry, y)
+            out = y.to(torch.float16)
+        return out.float(), state

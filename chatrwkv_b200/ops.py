@@ -1,0 +1,233 @@
+"""The operator boundary of the reference, re-registered over the sm_100a kernels.
+
+Registers, with the reference's argument lists (rwkv_pip_package/src/rwkv/cuda/wrapper.cpp:
+125-141, rwkv5_op.cpp:30-34, rwkv6_op.cpp:30-34):
+
+    torch.ops.rwkv.mm8_one(N, M, x, w, mx, rx, my, ry, y)
+    torch.ops.rwkv.mm8_seq(B, N, M, x, w, mx, rx, my, ry, y)
+    torch.ops.rwkv.wkv_forward(B, T, C, w, u, k, v, y, aa, bb, pp)
+    torch.ops.rwkv5.forward_{bf16,fp16,fp32}(B, T, C, H, state, r, k, v, w, u, y)
+    torch.ops.rwkv6.forward_{bf16,fp16,fp32}(B, T, C, H, state, r, k, v, w, u, y)
+
+Outputs are written in place into caller-allocated tensors, as in the reference.  Where
+the reference aborts with a C assert (non-unit inner strides, unsupported dtype) these
+raise.  Kernels run on torch's current stream, so calls can be captured into CUDA graphs
+(the reference launches on the legacy default stream).
+
+Also exposes `quantize_weight`, the loader's inline packing block (model.py:818-847) as a
+function.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import Mm8Problem, check, lib
+
+_DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+# ---------------------------------------------------------------------------------------
+# workspace: one zero-initialised buffer per (device, stream); kernels leave it clean.
+# ---------------------------------------------------------------------------------------
+_workspaces = {}
+
+
+def workspace(device, nbytes):
+    """Scratch for the split-K reductions.  Keyed by (device, stream): calls that share a
+    buffer are ordered by the stream."""
+    if nbytes == 0:
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise _lib.RwkvB200Error("workspace must be sized before stream capture (run one eager step first)")
+        buf = torch.zeros(max(nbytes, 64 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def _stream(device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require(cond, msg):
+    if not cond:
+        raise _lib.RwkvB200Error(msg)
+
+
+# ---------------------------------------------------------------------------------------
+# packing
+# ---------------------------------------------------------------------------------------
+def padded_stride(M):
+    """Row stride (bytes) of a packed matrix: rows start on 16-byte boundaries so that every
+    row can be read with 128-bit loads (and by TMA), e.g. 50277 -> 50288."""
+    return (M + 15) // 16 * 16
+
+
+def quantize_weight(w, atype=torch.float16, scale=1.0):
+    """uint8-pack `w[N_in, M_out]` (any strides, e.g. the `.t()` view of an nn.Linear
+    weight; fp32, fp16 or bf16) on the GPU.
+
+    Returns `(q, mx, rx, my, ry)`: `q` uint8 of shape [N, M] whose row stride is padded to a
+    multiple of 16 bytes; `mx`, `rx` of shape [M] and `my`, `ry` of shape [N, 1] in `atype`,
+    bit-identical to the reference loader's values (model.py:822-847).  `scale` (a power of
+    two) multiplies the source first: the loader's division of att.output / ffn.value by
+    2**(layer // 6) (model.py:785-789).
+    """
+    _require(w.is_cuda and w.dim() == 2, "quantize_weight needs a 2-D CUDA tensor")
+    _require(w.dtype in _DT and atype in (torch.float16, torch.float32), "unsupported dtype")
+    N, M = w.shape
+    dev = w.device
+    with torch.cuda.device(dev):
+        q_full = torch.empty((N, padded_stride(M)), dtype=torch.uint8, device=dev)
+        if padded_stride(M) != M:
+            q_full[:, M:].zero_()
+        q = q_full[:, :M]
+        mx = torch.empty(M, dtype=atype, device=dev)
+        rx = torch.empty(M, dtype=atype, device=dev)
+        my = torch.empty((N, 1), dtype=atype, device=dev)
+        ry = torch.empty((N, 1), dtype=atype, device=dev)
+        nbytes = lib().rwkv_quantize_weight_workspace_bytes(N, M)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        check(lib().rwkv_quantize_weight(
+            w.data_ptr(), _DT[w.dtype], w.stride(0), w.stride(1), float(scale), N, M,
+            q.data_ptr(), q.stride(0), mx.data_ptr(), rx.data_ptr(), my.data_ptr(), ry.data_ptr(),
+            _DT[atype], ws.data_ptr(), nbytes, _stream(dev)), "quantize_weight")
+    return q, mx, rx, my, ry
+
+
+# ---------------------------------------------------------------------------------------
+# op implementations (in-place, reference argument order)
+# ---------------------------------------------------------------------------------------
+def _check_mm8(x, w, mx, rx, my, ry, y):
+    _require(w.dtype == torch.uint8 and w.stride(1) == 1, "w must be uint8 with unit inner stride")
+    _require(x.stride(-1) == 1 and y.stride(-1) == 1, "x and y need unit inner stride")
+    _require(mx.stride(0) == 1 and rx.stride(0) == 1 and my.stride(0) == 1 and ry.stride(0) == 1,
+             "scale vectors need unit stride")
+    _require(x.dtype in (torch.float16, torch.float32), "Only FP16 and FP32 are currently supported")
+    _require(x.dtype == mx.dtype == rx.dtype == my.dtype == ry.dtype, "x and the scale vectors must share a dtype")
+
+
+def mm8_one_(N, M, x, w, mx, rx, my, ry, y):
+    _check_mm8(x, w, mx, rx, my, ry, y)
+    _require(y.dtype == torch.float32, "mm8_one accumulates into an fp32 y")
+    dev = w.device
+    with torch.cuda.device(dev):
+        nbytes = lib().rwkv_mm8_one_workspace_bytes(N, M)
+        ws = workspace(dev, nbytes)
+        check(lib().rwkv_mm8_one(N, M, x.data_ptr(), w.data_ptr(), w.stride(0), mx.data_ptr(), rx.data_ptr(),
+                                 my.data_ptr(), ry.data_ptr(), _DT[x.dtype], y.data_ptr(),
+                                 ws.data_ptr(), ws.numel(), _stream(dev)), "mm8_one")
+
+
+def mm8_seq_(B, N, M, x, w, mx, rx, my, ry, y):
+    _check_mm8(x, w, mx, rx, my, ry, y)
+    _require(y.dtype == x.dtype, "mm8_seq writes y in x.dtype")
+    dev = w.device
+    with torch.cuda.device(dev):
+        nbytes = lib().rwkv_mm8_seq_workspace_bytes(B, N, M)
+        ws = workspace(dev, nbytes)
+        check(lib().rwkv_mm8_seq(B, N, M, x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0),
+                                 mx.data_ptr(), rx.data_ptr(), my.data_ptr(), ry.data_ptr(), _DT[x.dtype],
+                                 y.data_ptr(), y.stride(0), ws.data_ptr() if ws is not None else None,
+                                 ws.numel() if ws is not None else 0, _stream(dev)), "mm8_seq")
+
+
+def wkv_forward_(B, T, C, w, u, k, v, y, aa, bb, pp):
+    _require(k.dtype in (torch.float16, torch.float32) and k.dtype == v.dtype == y.dtype,
+             "Only FP16 and FP32 are currently supported")
+    _require(all(t.dtype == torch.float32 for t in (w, u, aa, bb, pp)), "w, u and the state must be fp32")
+    _require(all(t.is_contiguous() for t in (w, u, k, v, y, aa, bb, pp)), "wkv_forward needs contiguous tensors")
+    dev = w.device
+    with torch.cuda.device(dev):
+        check(lib().rwkv_wkv4_forward(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(),
+                                      _DT[k.dtype], aa.data_ptr(), bb.data_ptr(), pp.data_ptr(), _stream(dev)),
+              "wkv_forward")
+
+
+def _wkv56(which, dtype):
+    fn_name = f"rwkv_wkv{which}_forward"
+
+    def impl(B, T, C, H, state, r, k, v, w, u, y):
+        _require(state.dtype == torch.float32 and w.dtype == torch.float32, "state and w must be fp32")
+        _require(r.dtype == k.dtype == v.dtype == u.dtype == y.dtype == dtype, f"r, k, v, u, y must be {dtype}")
+        _require(all(t.is_contiguous() for t in (state, r, k, v, w, u, y)), "needs contiguous tensors")
+        dev = state.device
+        with torch.cuda.device(dev):
+            check(getattr(lib(), fn_name)(B, T, C, H, state.data_ptr(), r.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                          w.data_ptr(), u.data_ptr(), y.data_ptr(), _DT[dtype], _stream(dev)),
+                  fn_name)
+    return impl
+
+
+# ---------------------------------------------------------------------------------------
+# torch.library registration
+# ---------------------------------------------------------------------------------------
+_libs = []
+
+
+def _register():
+    T7 = "Tensor x, Tensor w, Tensor mx, Tensor rx, Tensor my, Tensor ry, Tensor(a!) y"
+    rw = torch.library.Library("rwkv", "DEF")
+    rw.define(f"mm8_one(int N, int M, {T7}) -> ()")
+    rw.define(f"mm8_seq(int B, int N, int M, {T7}) -> ()")
+    rw.define("wkv_forward(int B, int T, int C, Tensor w, Tensor u, Tensor k, Tensor v, Tensor(a!) y, "
+              "Tensor(b!) aa, Tensor(c!) bb, Tensor(d!) pp) -> ()")
+    rw.impl("mm8_one", mm8_one_, "CUDA")
+    rw.impl("mm8_seq", mm8_seq_, "CUDA")
+    rw.impl("wkv_forward", wkv_forward_, "CUDA")
+    _libs.append(rw)
+    sig = ("(int B, int T, int C, int H, Tensor(a!) state, Tensor r, Tensor k, Tensor v, Tensor w, Tensor u, "
+           "Tensor(b!) y) -> ()")
+    for which in (5, 6):
+        lb = torch.library.Library(f"rwkv{which}", "DEF")
+        for suffix, dt in (("bf16", torch.bfloat16), ("fp16", torch.float16), ("fp32", torch.float32)):
+            lb.define(f"forward_{suffix}{sig}")
+            lb.impl(f"forward_{suffix}", _wkv56(which, dt), "CUDA")
+        _libs.append(lb)
+
+
+_register()
+
+
+class _Wkv56Module:
+    """Stands in for the `rwkv5` / `rwkv6` extension modules the reference loads
+    (model.py:907, 940): same function names, same argument order."""
+
+    def __init__(self, which):
+        ns = getattr(torch.ops, f"rwkv{which}")
+        self.forward_bf16 = ns.forward_bf16
+        self.forward_fp16 = ns.forward_fp16
+        self.forward_fp32 = ns.forward_fp32
+
+
+rwkv5 = _Wkv56Module(5)
+rwkv6 = _Wkv56Module(6)
+
+
+# ---------------------------------------------------------------------------------------
+# fused GEMV launches for the decode step
+# ---------------------------------------------------------------------------------------
+def make_problem(x, w, mx, rx, my, ry, y, epilogue, aux=None, aux2=None, out_scale=1.0):
+    p = Mm8Problem()
+    p.x, p.w, p.w_stride = x.data_ptr(), w.data_ptr(), w.stride(0)
+    p.mx, p.rx, p.my, p.ry = mx.data_ptr(), rx.data_ptr(), my.data_ptr(), ry.data_ptr()
+    p.y = y.data_ptr()
+    p.aux = aux.data_ptr() if aux is not None else None
+    p.aux2 = aux2.data_ptr() if aux2 is not None else None
+    p.N, p.M = w.shape
+    p.epilogue, p.out_scale = epilogue, out_scale
+    return p
+
+
+def mm8_one_batch(problems, dtype, device, ws=None):
+    """One launch for 1..3 GEMVs with fused epilogues.  `ws`: zero-initialised uint8 scratch
+    owned by the caller (needed under stream capture); default: the per-stream workspace."""
+    n = len(problems)
+    arr = (Mm8Problem * n)(*problems)
+    if ws is None:
+        ws = workspace(device, lib().rwkv_mm8_one_batch_workspace_bytes(arr, n))
+    check(lib().rwkv_mm8_one_batch(arr, n, _DT[dtype], ws.data_ptr(), ws.numel(), _stream(device)), "mm8_one_batch")

@@ -1,0 +1,206 @@
+/* C ABI of librwkv_b200.so: sm_100a kernels for the quantized ('cuda fp16i8') inference
+ * path of the rwkv pip package.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its comment says "host".
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream.
+ *     Work is enqueued, never synchronised; the calls are safe inside stream capture
+ *     (no allocation, no host synchronisation) unless stated otherwise.
+ *   - Every entry point returns RWKV_OK (0) or a negative RWKV_ERR_* code and launches
+ *     nothing when it returns an argument error.  The reference aborts the process with a
+ *     C assert in the same situations (rwkv_pip_package/src/rwkv/cuda/wrapper.cpp:55-59,
+ *     89-93, 80-82, 114-116).
+ *   - "Reference" citations are paths inside the BlinkDL/ChatRWKV project;
+ *     pkg/ = rwkv_pip_package/src/rwkv/.
+ */
+#ifndef RWKV_B200_H
+#define RWKV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    RWKV_OK = 0,
+    RWKV_ERR_INVALID_ARG = -1,  /* bad size, NULL pointer, unknown dtype/epilogue */
+    RWKV_ERR_ALIGNMENT = -2,    /* a pointer or stride breaks an alignment the kernel needs */
+    RWKV_ERR_WORKSPACE = -3,    /* workspace missing or too small */
+    RWKV_ERR_LAUNCH = -4,       /* the CUDA runtime rejected the launch */
+    RWKV_ERR_UNSUPPORTED = -5   /* valid request this build has no kernel for */
+};
+
+enum { RWKV_F32 = 0, RWKV_F16 = 1, RWKV_BF16 = 2 };
+
+/* Library version (major*1000 + minor) and a static string for an error code. */
+int rwkv_b200_version(void);
+const char* rwkv_b200_error_string(int code);
+
+/* ---------------------------------------------------------------------------------------
+ * int8 packing — replaces the inline block pkg/model.py:818-847 (and the power-of-two
+ * pre-division pkg/model.py:785-789 through `scale`).
+ *
+ * Logical input: fp32 W[N, M] (N = in-features = reduction index, M = out-features) read
+ * as  src[j * src_stride_n + k * src_stride_m]  (strides in elements), so the loader's
+ * transposed view of an [M, N] nn.Linear weight is (src_stride_n = 1, src_stride_m = N).
+ * src_dtype is RWKV_F32 / RWKV_F16 / RWKV_BF16; values are widened to fp32 and multiplied
+ * by `scale` (a power of two; 1.0f for no rescale) before anything else.
+ * Outputs: q uint8 [N, M] with row stride q_stride (>= M); mx, rx [M] and my, ry [N] in
+ * scale_dtype (RWKV_F16 or RWKV_F32); rx and ry already divided by 16 as the reference
+ * stores them.  Results are bit-identical to the reference's CPU tensor ops.
+ * workspace: rwkv_quantize_weight_workspace_bytes(N, M) bytes of scratch, 16-byte aligned.
+ * ------------------------------------------------------------------------------------- */
+size_t rwkv_quantize_weight_workspace_bytes(int64_t N, int64_t M);
+int rwkv_quantize_weight(const void* src, int src_dtype, int64_t src_stride_n, int64_t src_stride_m,
+                         float scale, int64_t N, int64_t M,
+                         uint8_t* q, int64_t q_stride,
+                         void* mx, void* rx, void* my, void* ry, int scale_dtype,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * mm8_one — replaces cuda_mm8_one<F> (pkg/cuda/operators.cu:193-246) behind
+ * torch.ops.rwkv.mm8_one (pkg/cuda/wrapper.cpp:84-117).
+ *
+ *   y[k] += sum_j x[j] * ((w[j,k] + 0.5) * rx[k] * ry[j] + mx[k] + my[j])      k in [0, M)
+ *
+ * x, mx, rx, my, ry have dtype `dtype` (RWKV_F16 or RWKV_F32); y is fp32 [M] and is
+ * ACCUMULATED into, as in the reference (callers pass zeros, pkg/model.py:84).  The sum is
+ * evaluated in fp32 in a fixed order: two calls on equal inputs give equal bits.
+ * w: uint8 [N, M], row stride w_stride >= M.  The 128-bit-load kernel is used when w is
+ * 16-byte aligned, w_stride % 16 == 0 and every row has round_up(M,16) readable bytes
+ * (M % 16 == 0 or w_stride >= round_up(M,16)); any other layout takes a byte-load kernel.
+ * workspace: rwkv_mm8_one_workspace_bytes(N, M) bytes that were ZERO when first handed to
+ * the library; each call leaves its counters zero again.  Calls sharing a workspace must
+ * be ordered on one stream.
+ * ------------------------------------------------------------------------------------- */
+size_t rwkv_mm8_one_workspace_bytes(int64_t N, int64_t M);
+int rwkv_mm8_one(int64_t N, int64_t M, const void* x, const uint8_t* w, int64_t w_stride,
+                 const void* mx, const void* rx, const void* my, const void* ry, int dtype,
+                 float* y, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * mm8_one with a fused epilogue, up to three matrices per launch — the building block of
+ * the fused decode steps that replace att_one / ffn_one (pkg/model.py:984-992, 1034-1055)
+ * and their v5/v6 forms (pkg/model.py:1007-1016, 1157-1181, 1263-1298).  `val` below is the
+ * fp32 sum of mm8_one; r16() is one rounding to `dtype`, which is where the reference
+ * rounds (pkg/model.py:86).
+ *   RWKV_EPI_ACC_F32       y fp32:  y[k] += val
+ *   RWKV_EPI_STORE         y[k] = r16(val)
+ *   RWKV_EPI_SIGMOID       y[k] = sigmoid(r16(val))                     (receptance)
+ *   RWKV_EPI_RELU_SQ       y[k] = relu(r16(val))^2                      (pkg/model.py:990)
+ *   RWKV_EPI_RESIDUAL      y[k] = (aux[k] + r16(val)) * out_scale       (pkg/model.py:1055, 1660-1662)
+ *   RWKV_EPI_MUL_RESIDUAL  y[k] = (aux[k] + aux2[k]*r16(val)) * out_scale  (pkg/model.py:991-992)
+ *   RWKV_EPI_STORE_F32     y fp32:  y[k] = r16(val)   (the head: fp16-rounded logits returned
+ *                          as fp32, pkg/model.py:1675-1677)
+ * Every intermediate is rounded to `dtype` like the torch ops it replaces; out_scale is 1
+ * or 0.5 (the every-6-layers halving).  y may alias aux.
+ * ------------------------------------------------------------------------------------- */
+enum {
+    RWKV_EPI_ACC_F32 = 0,
+    RWKV_EPI_STORE = 1,
+    RWKV_EPI_SIGMOID = 2,
+    RWKV_EPI_RELU_SQ = 3,
+    RWKV_EPI_RESIDUAL = 4,
+    RWKV_EPI_MUL_RESIDUAL = 5,
+    RWKV_EPI_STORE_F32 = 6
+};
+
+typedef struct rwkv_mm8_problem {
+    const void* x;          /* [N] activations */
+    const uint8_t* w;       /* [N, M] codes */
+    int64_t w_stride;
+    const void* mx;         /* [M] */
+    const void* rx;         /* [M] */
+    const void* my;         /* [N] */
+    const void* ry;         /* [N] */
+    void* y;                /* [M] output */
+    const void* aux;        /* [M] residual input, or NULL */
+    const void* aux2;       /* [M] multiplier, or NULL */
+    int32_t N, M;
+    int32_t epilogue;
+    float out_scale;
+} rwkv_mm8_problem;
+
+/* `problems` is a HOST array of 1..3 entries, read during the call. */
+size_t rwkv_mm8_one_batch_workspace_bytes(const rwkv_mm8_problem* problems, int count);
+int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, int dtype,
+                       void* workspace, size_t workspace_bytes, void* stream);
+/* Tuning hook: force the number of K-splits (0 = automatic). Not thread-safe. */
+void rwkv_mm8_one_set_split(int split);
+
+/* ---------------------------------------------------------------------------------------
+ * mm8_seq — replaces cuda_mm8_seq<F> (pkg/cuda/operators.cu:102-154) behind
+ * torch.ops.rwkv.mm8_seq (pkg/cuda/wrapper.cpp:50-83).
+ *
+ *   y[i,k] = sum_j x[i,j] * ((w[j,k] + 0.5) * rx[k] * ry[j] + mx[k] + my[j])   i in [0, B)
+ *
+ * x [B, N] row stride x_stride, y [B, M] row stride y_stride, both in `dtype`, fp32
+ * accumulation, one rounding to `dtype` at the store (operators.cu:138).
+ * ------------------------------------------------------------------------------------- */
+size_t rwkv_mm8_seq_workspace_bytes(int64_t B, int64_t N, int64_t M);
+int rwkv_mm8_seq(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
+                 const uint8_t* w, int64_t w_stride,
+                 const void* mx, const void* rx, const void* my, const void* ry, int dtype,
+                 void* y, int64_t y_stride, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * WKV-v4 — replaces cuda_wkv_forward<F> (pkg/cuda/operators.cu:11-58) behind
+ * torch.ops.rwkv.wkv_forward (pkg/cuda/wrapper.cpp:27-48).
+ * w = -exp(time_decay), u = time_first: fp32 [C].  k, v, y: [B, T, C] in kv_dtype
+ * (RWKV_F16 or RWKV_F32).  aa, bb, pp: fp32 [B, C] state, updated in place.
+ * ------------------------------------------------------------------------------------- */
+int rwkv_wkv4_forward(int64_t B, int64_t T, int64_t C, const float* w, const float* u,
+                      const void* k, const void* v, void* y, int kv_dtype,
+                      float* aa, float* bb, float* pp, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * WKV5 / WKV6 — replace cuda_forward_{bf16,fp16,fp32} of pkg/cuda/rwkv5.cu:8-88 and
+ * pkg/cuda/rwkv6.cu:8-87 behind rwkv5.forward_* / rwkv6.forward_*
+ * (pkg/cuda/rwkv5_op.cpp:12-34, pkg/cuda/rwkv6_op.cpp:12-34).
+ * state fp32 [H, N, N] in the kernel layout [head, value index, key index], updated in
+ * place (B must be 1, as in the reference).  r, k, v, y: [T, C] in `dtype`; u: [H*N] in
+ * `dtype`.  v5: w fp32 [H*N] = exp(-exp(decay)).  v6: w fp32 [T, C], already
+ * exp(-exp(.)) (pkg/model.py:959).  The head size N = C / H may be 16, 32, 64 or 128 and
+ * is a run-time argument here (the reference compiles it in with -D_N_).
+ * ------------------------------------------------------------------------------------- */
+int rwkv_wkv5_forward(int64_t B, int64_t T, int64_t C, int64_t H, float* state,
+                      const void* r, const void* k, const void* v, const float* w, const void* u,
+                      void* y, int dtype, void* stream);
+int rwkv_wkv6_forward(int64_t B, int64_t T, int64_t C, int64_t H, float* state,
+                      const void* r, const void* k, const void* v, const float* w, const void* u,
+                      void* y, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * LayerNorm + token-shift mixes in one launch — the opening lines of att_one / att_seq /
+ * ffn_one / ffn_seq (pkg/model.py:985-987, 996-999, 1035-1038, 1059-1063) and of their
+ * RWKV-6 forms (pkg/model.py:1008-1011, 1020-1024).  fp16 only.
+ *   xx[t]  = layer_norm(x[t]; ln_w, ln_b)                 (fp32 statistics, eps 1e-5)
+ *   prev   = t == 0 ? sx : xx[t-1]
+ *   mode 0: out_m[t] = xx[t]*mix_m + prev*(1 - mix_m)
+ *   mode 1: out_m[t] = xx[t] + (prev - xx[t])*mix_m
+ * with one fp16 rounding per torch op of the reference.  mix_m is [D] (mix_stride 0) or
+ * [T, D].  `mix` and `out` are HOST arrays of n_mix (0..5) device pointers.  xx_out
+ * (optional) receives xx; new_state (optional, may alias sx only when T == 1) receives
+ * xx[T-1].
+ * ------------------------------------------------------------------------------------- */
+int rwkv_ln_mix(int64_t T, int64_t D, const void* x, int64_t x_stride, const void* sx,
+                const void* ln_w, const void* ln_b, int mode, int n_mix,
+                const void* const* mix, int64_t mix_stride, void* const* out, int64_t out_stride,
+                void* xx_out, int64_t xx_stride, void* new_state, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * RWKV-4 one-step WKV — the fp32 island of att_one (pkg/model.py:1044-1055).
+ * r (after sigmoid), k, v: fp16 [C]; t_decay = -exp(time_decay), t_first: fp32 [C];
+ * aa, bb, pp: fp32 [C] updated in place; out = r * wkv in fp16 (the operand of the output
+ * matmul).
+ * ------------------------------------------------------------------------------------- */
+int rwkv_wkv4_one(int64_t C, const float* t_decay, const float* t_first, const void* r,
+                  const void* k, const void* v, float* aa, float* bb, float* pp, void* out,
+                  void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RWKV_B200_H */
