@@ -259,7 +259,7 @@ def main():
 
     if rank == 0:
         n_mm = L * (7 if version == 4 else 8)
-        launches_per_token = L * 7 + 2
+        launches_per_token = L * 4 + 1
         line = {
             "metric": METRIC, "value": world * a.steps / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": dev_ms / a.steps, "higher_is_better": True,
@@ -300,12 +300,9 @@ def gemv_roofline(model, dev, reps=3):
 
     ops.mm8_one_batch = timed
     try:
-        import chatrwkv_b200.model as mm
-        saved = [s.clone() for s in model._gstate]
         for _ in range(reps):
-            model._step_one()
+            model._step_one_v4(model._cur)      # reads the current state set, writes the other one
         torch.cuda.synchronize(dev)
-        torch._foreach_copy_(model._gstate, saved)
     finally:
         ops.mm8_one_batch = orig
     tot_b = sum(r[2] for r in records)

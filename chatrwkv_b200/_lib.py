@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_HERE, "librwkv_b200.so")
 
 OK = 0
 F32, F16, BF16 = 0, 1, 2
+PRO_PLAIN, PRO_LN_MIX, PRO_WKV4 = 0, 1, 2
 EPI_ACC_F32, EPI_STORE, EPI_SIGMOID, EPI_RELU_SQ, EPI_RESIDUAL, EPI_MUL_RESIDUAL, EPI_STORE_F32 = range(7)
 
 
@@ -26,6 +27,11 @@ class Mm8Problem(C.Structure):
         ("mx", C.c_void_p), ("rx", C.c_void_p), ("my", C.c_void_p), ("ry", C.c_void_p),
         ("y", C.c_void_p), ("aux", C.c_void_p), ("aux2", C.c_void_p),
         ("N", C.c_int32), ("M", C.c_int32), ("epilogue", C.c_int32), ("out_scale", C.c_float),
+        ("prologue", C.c_int32), ("mode", C.c_int32),
+        ("ln_w", C.c_void_p), ("ln_b", C.c_void_p), ("sx", C.c_void_p), ("mix", C.c_void_p), ("xx_out", C.c_void_p),
+        ("k", C.c_void_p), ("v", C.c_void_p), ("t_decay", C.c_void_p), ("t_first", C.c_void_p),
+        ("aa", C.c_void_p), ("bb", C.c_void_p), ("pp", C.c_void_p),
+        ("aa_out", C.c_void_p), ("bb_out", C.c_void_p), ("pp_out", C.c_void_p),
     ]
 
 
@@ -42,6 +48,7 @@ SIGNATURES = {
     "rwkv_mm8_one_batch_workspace_bytes": (_sz, [C.POINTER(Mm8Problem), _i32]),
     "rwkv_mm8_one_batch": (_i32, [C.POINTER(Mm8Problem), _i32, _i32, _vp, _sz, _vp]),
     "rwkv_mm8_one_set_split": (None, [_i32]),
+    "rwkv_mm8_one_set_variant": (None, [_i32]),
     "rwkv_mm8_seq_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "rwkv_mm8_seq": (_i32, [_i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _sz, _vp]),
     "rwkv_wkv4_forward": (_i32, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp]),

