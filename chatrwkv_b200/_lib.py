@@ -45,6 +45,7 @@ SIGNATURES = {
     "rwkv_quantize_weight": (_i32, [_vp, _i32, _i64, _i64, _f, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _sz, _vp]),
     "rwkv_mm8_one_workspace_bytes": (_sz, [_i64, _i64]),
     "rwkv_mm8_one": (_i32, [_i64, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _sz, _vp]),
+    "rwkv_mm8_one_static": (_i32, [_i64, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _vp]),
     "rwkv_mm8_one_batch_workspace_bytes": (_sz, [C.POINTER(Mm8Problem), _i32]),
     "rwkv_mm8_one_batch": (_i32, [C.POINTER(Mm8Problem), _i32, _i32, _vp, _sz, _vp]),
     "rwkv_mm8_one_set_split": (None, [_i32]),

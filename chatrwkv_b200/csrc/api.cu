@@ -11,6 +11,7 @@ extern "C" const char* rwkv_b200_error_string(int code) {
     case RWKV_ERR_WORKSPACE: return "workspace missing or too small";
     case RWKV_ERR_LAUNCH: return "CUDA runtime rejected the kernel launch";
     case RWKV_ERR_UNSUPPORTED: return "no kernel for this configuration";
+    case RWKV_ERR_STATIC_LIMIT: return "M exceeds the fixed scratch of rwkv_mm8_one_static (M <= 32768)";
     default: return "unknown error code";
     }
 }

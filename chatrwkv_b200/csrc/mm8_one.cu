@@ -572,3 +572,53 @@ extern "C" int rwkv_mm8_one(int64_t N, int64_t M, const void* x, const uint8_t* 
     q.epilogue = RWKV_EPI_ACC_F32; q.out_scale = 1.0f; q.prologue = RWKV_PRO_PLAIN;
     return rwkv_mm8_one_batch(&q, 1, dtype, workspace, workspace_bytes, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// mm8_one for callers that cannot allocate device memory.
+//
+// Same kernel, same split plan and the same result as rwkv_mm8_one, but the split-K scratch
+// (panel tickets, per-split scalar sums, per-split partial rows) lives in one fixed array in
+// the library's own device image instead of a caller-provided workspace.  The array costs
+// kStaticScratchBytes (about 9 MiB) on every GPU that loads the library, for as long as the
+// process lives, and bounds the out-feature count at kStaticMaxM.
+//
+// `g_static_scratch` names a DEVICE symbol.  In host code that name is only a stand-in: the
+// address a kernel may use comes from cudaGetSymbolAddress, looked up once per device (with
+// that device current) on the first call and remembered in g_static_ptr[].
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr int kStaticMaxM = 32768;
+constexpr size_t kStaticScratchBytes =
+    size_t(kCounterBytes) + size_t(kSumsBytes) + size_t(kMaxSplit) * size_t(kStaticMaxM) * sizeof(float);
+constexpr int kStaticMaxDevices = 64;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+void* g_static_ptr[kStaticMaxDevices] = {};
+}  // namespace
+
+extern "C" int rwkv_mm8_one_static(int64_t N, int64_t M, const void* x, const uint8_t* w, int64_t w_stride,
+                                   const void* mx, const void* rx, const void* my, const void* ry, int dtype,
+                                   float* y, void* stream) {
+    RWKV_CHECK_ARG(N >= 1 && M >= 1 && N <= INT32_MAX);
+    if (M > kStaticMaxM) return RWKV_ERR_STATIC_LIMIT;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) {
+        cudaGetLastError();
+        return RWKV_ERR_LAUNCH;
+    }
+    if (g_static_ptr[dev] == nullptr) {
+        // First call on this device: resolve the symbol to this device's copy of the array.
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+            cudaGetLastError();
+            return RWKV_ERR_LAUNCH;
+        }
+        g_static_ptr[dev] = p;
+    }
+    // The tickets must read zero when the kernel starts.  Every finished call leaves them so;
+    // clearing them here as well makes the call independent of how an earlier one ended.
+    if (cudaMemsetAsync(g_static_ptr[dev], 0, kCounterBytes, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+        cudaGetLastError();
+        return RWKV_ERR_LAUNCH;
+    }
+    return rwkv_mm8_one(N, M, x, w, w_stride, mx, rx, my, ry, dtype, y, g_static_ptr[dev], kStaticScratchBytes, stream);
+}

@@ -29,7 +29,8 @@ enum {
     RWKV_ERR_ALIGNMENT = -2,    /* a pointer or stride breaks an alignment the kernel needs */
     RWKV_ERR_WORKSPACE = -3,    /* workspace missing or too small */
     RWKV_ERR_LAUNCH = -4,       /* the CUDA runtime rejected the launch */
-    RWKV_ERR_UNSUPPORTED = -5   /* valid request this build has no kernel for */
+    RWKV_ERR_UNSUPPORTED = -5,  /* valid request this build has no kernel for */
+    RWKV_ERR_STATIC_LIMIT = -6  /* size beyond the fixed scratch of rwkv_mm8_one_static */
 };
 
 enum { RWKV_F32 = 0, RWKV_F16 = 1, RWKV_BF16 = 2 };
@@ -79,6 +80,33 @@ size_t rwkv_mm8_one_workspace_bytes(int64_t N, int64_t M);
 int rwkv_mm8_one(int64_t N, int64_t M, const void* x, const uint8_t* w, int64_t w_stride,
                  const void* mx, const void* rx, const void* my, const void* ry, int dtype,
                  float* y, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * mm8_one without a workspace argument — an addition of this library; the reference has no
+ * counterpart (there, torch allocates whatever the operators need).
+ *
+ * It is meant for hosts that may not obtain device memory on behalf of the library: a
+ * plugin that is handed raw tensor pointers and nothing else, a server that sizes one arena
+ * at start-up and forbids later driver allocations, code running where cudaMalloc's implicit
+ * device synchronisation is not acceptable.  The call allocates nothing (no cudaMalloc,
+ * cudaFree or allocating library routine); the split-K scratch that rwkv_mm8_one takes as
+ * `workspace` is a fixed array inside the library's device image instead.
+ *
+ * Same arguments, arithmetic and result as rwkv_mm8_one (y is accumulated into).  Limits and
+ * rules:
+ *   - M <= 32768; a larger M returns RWKV_ERR_STATIC_LIMIT and launches nothing.
+ *   - The array (about 9 MiB) is held on every GPU that loads the library until the process
+ *     exits, whether or not this entry point is ever called.
+ *   - The first call on each device looks the array's device address up (with the caller's
+ *     current device) before launching.  Make that first call outside of any stream capture.
+ *   - All calls on a device share the one array, which keeps whatever the previous call left
+ *     in it; the call clears the part that has to start at zero on `stream` before the kernel.
+ *     Two calls that can overlap on the GPU (different streams, no dependency) race on it:
+ *     order them, or use rwkv_mm8_one with separate workspaces.
+ * ------------------------------------------------------------------------------------- */
+int rwkv_mm8_one_static(int64_t N, int64_t M, const void* x, const uint8_t* w, int64_t w_stride,
+                        const void* mx, const void* rx, const void* my, const void* ry, int dtype,
+                        float* y, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * mm8_one with a fused epilogue, up to three matrices per launch — the building block of
