@@ -259,7 +259,7 @@ def main():
 
     if rank == 0:
         n_mm = L * (7 if version == 4 else 8)
-        launches_per_token = L * 4 + 1
+        launches_per_token = 2 if model._use_chain else L * 4 + 1
         line = {
             "metric": METRIC, "value": world * a.steps / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": dev_ms / a.steps, "higher_is_better": True,
@@ -279,47 +279,44 @@ def main():
         dist.destroy_process_group()
 
 
-def gemv_roofline(model, dev, reps=3):
-    """Event-time every mm8_one launch of one decode step (eager, outside the graph)."""
+def gemv_roofline(model, dev, reps=30):
+    """HBM roofline of the decode kernel.  One decode step is timed with CUDA events on the
+    launching stream (direct launches, no graph, token id already on the device) and divided
+    into the algorithmic bytes of its mm8_one problems: N*M weight bytes + 6N (x, my, ry) +
+    4M (mx, rx) + the output vector, summed over every matmul of the token."""
     import torch
-    from chatrwkv_b200 import ops
     peak, how = measured_peaks()
-    records = []
-    orig = ops.mm8_one_batch
-
-    def timed(problems, dtype, device, ws=None):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        orig(problems, dtype, device, ws)
-        e1.record()
-        nbytes = 0
-        for p in problems:
+    launches = model._launches_v4(model._cur)
+    tot_b = 0
+    for probs in launches:
+        for p in probs:
             out_b = 4 if p.epilogue in (0, 6) else 2
-            nbytes += p.N * p.M + 6 * p.N + 4 * p.M + out_b * p.M
-        records.append((e0, e1, nbytes))
-
-    ops.mm8_one_batch = timed
-    try:
-        for _ in range(reps):
-            model._step_one_v4(model._cur)      # reads the current state set, writes the other one
-        torch.cuda.synchronize(dev)
-    finally:
-        ops.mm8_one_batch = orig
-    tot_b = sum(r[2] for r in records)
-    tot_ms = sum(r[0].elapsed_time(r[1]) for r in records)
-    n = len(records)
-    achieved = tot_b / (tot_ms / 1e3) / 1e9
+            tot_b += p.N * p.M + 6 * p.N + 4 * p.M + out_b * p.M
+    chain = bool(model._use_chain)
+    for _ in range(3):
+        model._step_one_v4(model._cur)          # reads the current state set, writes the other one
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        model._step_one_v4(model._cur)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / reps
+    n_launch = 2 if chain else len(launches)
+    achieved = tot_b / (ms / 1e3) / 1e9
     traffic = None
     try:
-        with open(os.path.join(ROOT, "profiles", "mm8_one_traffic.json")) as f:
+        with open(os.path.join(ROOT, "profiles", "mm8_traffic.json")) as f:
             t = json.load(f)
-        traffic = t["dram_bytes_per_algorithmic_byte"] * tot_b / n
+        traffic = t["dram_bytes_per_algorithmic_byte"] * tot_b / n_launch
     except Exception:
         pass
-    return {"bound": "hbm", "kernel": "mm8_one_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "peak_source": how, "traffic": traffic, "launches_timed": n,
-            "avg_launch_us": tot_ms / n * 1e3, "algorithmic_bytes_per_launch": tot_b / n,
-            "frac_of_8000": achieved / 8000.0}
+    return {"bound": "hbm", "kernel": "mm8_chain_kernel" if chain else "mm8_one_kernel", "achieved": achieved,
+            "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": how, "traffic": traffic,
+            "launches_per_step": n_launch, "avg_launch_us": ms / n_launch * 1e3,
+            "algorithmic_bytes_per_launch": tot_b / n_launch, "frac_of_8000": achieved / 8000.0,
+            "chain_error": model.chain_error() if chain else 0}
 
 
 if __name__ == "__main__":

@@ -50,6 +50,11 @@ SIGNATURES = {
     "rwkv_mm8_one_batch": (_i32, [C.POINTER(Mm8Problem), _i32, _i32, _vp, _sz, _vp]),
     "rwkv_mm8_one_set_split": (None, [_i32]),
     "rwkv_mm8_one_set_variant": (None, [_i32]),
+    "rwkv_mm8_chain_ctas": (_i32, []),
+    "rwkv_mm8_chain_table_bytes": (_sz, [_i32, _i32]),
+    "rwkv_mm8_chain_plan": (_i32, [C.POINTER(Mm8Problem), C.POINTER(C.c_int32), _i32, _i32, _i32, _vp, _sz, _vp, _sz]),
+    "rwkv_mm8_chain_run": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp]),
+    "rwkv_mm8_chain_take_error": (_i32, [_vp, _vp, C.POINTER(C.c_int)]),
     "rwkv_mm8_seq_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "rwkv_mm8_seq": (_i32, [_i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _sz, _vp]),
     "rwkv_wkv4_forward": (_i32, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp]),

@@ -228,6 +228,12 @@ class RWKV:
         self._st = None
         self._cur = 0
         self._graphs = [None, None]
+        self._chain = [None, None]      # per direction: (device launch table, n_launches, n_ctas)
+        self._head_launch = [None, None]
+        # RWKV_B200_CHAIN=1: run the layers of a token as one persistent cooperative kernel
+        # (csrc/mm8_chain.cu) instead of four launches per layer.  Both reach the same speed on a
+        # B200; the launch-per-matmul path is the default because it contains no wait loop.
+        self._use_chain = os.environ.get("RWKV_B200_CHAIN", "0") == "1"
         self._mm = {}
 
     def _scales(self, name):
@@ -325,23 +331,32 @@ class RWKV:
             step(cur)
             torch._foreach_copy_(self._st[cur], saved)
             torch.cuda.synchronize(self.device)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                step(cur)
-            self._graphs[cur] = graph
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step(cur)
+                self._graphs[cur] = graph
+            except Exception as e:       # e.g. a launch kind the capture does not accept
+                if os.environ.get("RWKV_B200_VERBOSE"):
+                    print(f"[rwkv_b200] CUDA graph capture failed ({e}); decoding with direct launches")
+                torch.cuda.synchronize(self.device)
+                self._use_graph = False
             torch._foreach_copy_(self._st[cur], saved)
-            graph.replay()
+            if self._use_graph:
+                graph.replay()
+            else:
+                step(cur)
         else:
             self._graphs[cur].replay()
         if fused:
             self._cur = 1 - cur
         return self._b.logits.clone(), list(self._st[self._cur])
 
-    def _step_one_v4(self, cur):
-        """One RWKV-4 token: four GEMV launches per layer, everything pointwise fused into
-        their prologues and epilogues (att_one / ffn_one, model.py:984-992, 1034-1055)."""
+    def _launches_v4(self, cur):
+        """The GEMV launches of one RWKV-4 token, in order: four per layer plus the head, with
+        everything pointwise fused into their prologues and epilogues (att_one / ffn_one,
+        model.py:984-992, 1034-1055).  Reads state set `cur`, writes the other one."""
         b, w, a = self._b, self.w, self.args
-        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
         sin, sout = self._st[cur], self._st[1 - cur]
         P, ln, wk = self._problem, ops.with_ln_mix, ops.with_wkv4
         launches = []
@@ -362,8 +377,49 @@ class RWKV:
             scale = 0.5 if (self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0) else 1.0
             launches.append([P(b.fk, ffn + "value.weight", b.x, EPI_MUL_RESIDUAL, aux=b.x, aux2=b.fr, out_scale=scale)])
         launches.append([ln(P(b.x, "head.weight", b.logits, EPI_STORE_F32), w["ln_out.weight"], w["ln_out.bias"], 2)])
-        for probs in launches:
-            self._gemv(probs)
+        return launches
+
+    def _build_chain(self, cur):
+        """Lay the layers' launches out for the persistent chain kernel (once per direction).
+        The head (one wide matmul) stays a launch of its own."""
+        import ctypes as C
+        launches = self._launches_v4(cur)[:-1]
+        flat = [p for probs in launches for p in probs]
+        arr = (_lib.Mm8Problem * len(flat))(*flat)
+        counts = (C.c_int32 * len(launches))(*[len(p) for p in launches])
+        n_ctas = lib().rwkv_mm8_chain_ctas()
+        nbytes = lib().rwkv_mm8_chain_table_bytes(len(launches), n_ctas)
+        host = torch.zeros(nbytes, dtype=torch.uint8)
+        check(lib().rwkv_mm8_chain_plan(arr, counts, len(launches), _lib.F16, n_ctas, self._ws.data_ptr(),
+                                        self._ws.numel(), host.data_ptr(), nbytes), "mm8_chain_plan")
+        self._chain[cur] = (host.to(self.device), len(launches), n_ctas)
+
+    def _step_one_v4(self, cur):
+        b, w = self._b, self.w
+        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
+        if self._use_chain:
+            if self._chain[cur] is None:
+                self._build_chain(cur)
+            table, n, n_ctas = self._chain[cur]
+            trace = getattr(self, "_trace", None)
+            check(lib().rwkv_mm8_chain_run(table.data_ptr(), n, n_ctas, self._ws.data_ptr(),
+                                           trace.data_ptr() if trace is not None else None,
+                                           torch.cuda.current_stream(self.device).cuda_stream), "mm8_chain_run")
+            if self._head_launch[cur] is None:
+                self._head_launch[cur] = self._launches_v4(cur)[-1]
+            self._gemv(self._head_launch[cur])
+        else:
+            for probs in self._launches_v4(cur):
+                self._gemv(probs)
+
+    def chain_error(self):
+        """1 if a grid barrier of the persistent decode kernel ever gave up waiting since the
+        last call (its results were then undefined); synchronises the current stream."""
+        import ctypes as C
+        e = C.c_int(0)
+        check(lib().rwkv_mm8_chain_take_error(self._ws.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream,
+                                              C.byref(e)), "mm8_chain_take_error")
+        return e.value
 
     def _step_one_generic(self, cur):
         """RWKV-5.2 / RWKV-6 token: the sequence-form blocks with T = 1 on the resident state."""

@@ -197,6 +197,40 @@ void rwkv_mm8_one_set_variant(int variant);
 
 
 /* ---------------------------------------------------------------------------------------
+ * mm8 chain — a fixed list of dependent mm8_one launches (one decode step: every att/ffn
+ * matmul of every layer and the head, with their fused prologues and epilogues) run as ONE
+ * persistent cooperative kernel.  Replaces the per-token Python loop of RWKV.forward over
+ * att_one / ffn_one (pkg/model.py:1477-1677) for T = 1.  fp16 only; every matrix must meet
+ * the 16-byte layout of the fast mm8_one path.
+ *
+ *   rwkv_mm8_chain_ctas()        CTAs of the persistent grid on the current device.
+ *   rwkv_mm8_chain_table_bytes() size of the launch table (one record per launch and CTA).
+ *   rwkv_mm8_chain_plan()        HOST-side: lays the launches out into `table_out` (host
+ *                                memory).  problems = all launches' problems back to back,
+ *                                counts[l] = problems of launch l (1..3).  `workspace` is the
+ *                                DEVICE scratch the kernel will use (its address is baked into
+ *                                the table): rwkv_mm8_one_batch_workspace_bytes of the largest
+ *                                launch, zero-initialised once.  Copy the table to the device.
+ *   rwkv_mm8_chain_run()         enqueues one pass over the table (cooperative launch).  trace:
+ *                                NULL, or n_launches x 8 uint64 (device) that receive CTA 0's
+ *                                %globaltimer stamps per launch: start, barrier passed,
+ *                                prologue done, stream done, partials written, ticket taken,
+ *                                epilogue done.
+ *   rwkv_mm8_chain_take_error()  synchronises `stream`, returns and clears the error word: 1
+ *                                when a grid barrier gave up waiting (results undefined).
+ * Launch l+1 may read what launch l wrote; results are bit-identical to issuing the same
+ * problems through rwkv_mm8_one_batch with the same split plan.
+ * ------------------------------------------------------------------------------------- */
+int rwkv_mm8_chain_ctas(void);
+size_t rwkv_mm8_chain_table_bytes(int n_launches, int n_ctas);
+int rwkv_mm8_chain_plan(const rwkv_mm8_problem* problems, const int32_t* counts, int n_launches,
+                        int dtype, int n_ctas, void* workspace, size_t workspace_bytes,
+                        void* table_out, size_t table_bytes);
+int rwkv_mm8_chain_run(const void* table_device, int n_launches, int n_ctas, void* workspace,
+                       void* trace, void* stream);
+int rwkv_mm8_chain_take_error(void* workspace, void* stream, int* error_out);
+
+/* ---------------------------------------------------------------------------------------
  * mm8_seq — replaces cuda_mm8_seq<F> (pkg/cuda/operators.cu:102-154) behind
  * torch.ops.rwkv.mm8_seq (pkg/cuda/wrapper.cpp:50-83).
  *

@@ -90,6 +90,44 @@ def test_graph_and_eager_decode_agree_bitwise(monkeypatch):
         assert torch.equal(a, b)
 
 
+def test_chain_kernel_matches_per_launch_path(monkeypatch):
+    """The persistent one-kernel-per-token path and the launch-per-matmul path run the same
+    arithmetic (only the K-split of the head may differ): logits agree to fp32 round-off."""
+    from chatrwkv_b200.model import RWKV
+    ck = synth.make_checkpoint(**TOY["v4"])
+    monkeypatch.setenv("RWKV_B200_CHAIN", "1")
+    mc = RWKV(copy.deepcopy(ck), "cuda fp16i8", verbose=False)
+    monkeypatch.setenv("RWKV_B200_CHAIN", "0")
+    ml = RWKV(copy.deepcopy(ck), "cuda fp16i8", verbose=False)
+    assert mc._use_chain and not ml._use_chain
+    sc = sl = None
+    for t in TOKENS:
+        a, sc = mc.forward([t], sc)
+        b, sl = ml.forward([t], sl)
+        assert (a - b).abs().max().item() <= 2e-3
+    assert mc.chain_error() == 0
+
+
+def test_chain_kernel_at_config0_shape(monkeypatch):
+    """The persistent chain kernel at the 169M shape (real panel / split plans, 12 layers)
+    against the launch-per-matmul path, token by token."""
+    from chatrwkv_b200.model import RWKV
+    L, D, Fn, V = synth.SHAPES["v4-169m"]
+    ck = synth.make_checkpoint(4, L, D, Fn, V, seed=1000, device="cuda")
+    monkeypatch.setenv("RWKV_B200_CHAIN", "1")
+    mc = RWKV(dict(ck), "cuda fp16i8", verbose=False)
+    monkeypatch.setenv("RWKV_B200_CHAIN", "0")
+    ml = RWKV(dict(ck), "cuda fp16i8", verbose=False)
+    sc = sl = None
+    tok = 17
+    for _ in range(12):
+        a, sc = mc.forward([tok], sc)
+        b, sl = ml.forward([tok], sl)
+        assert (a - b).abs().max().item() <= 4e-3
+        tok = int(b.argmax())
+    assert mc.chain_error() == 0
+
+
 def test_state_snapshot_and_restore():
     """deepcopy(state) is a snapshot: resuming from it reproduces the same logits."""
     m, _ = _models("v4")
