@@ -93,20 +93,36 @@ __global__ void __launch_bounds__(256) mm8_seq_simt(int B, int N, int M,
 
 }  // namespace
 
+// tensor-core path (mm8_seq_tc.cu)
+extern "C" size_t rwkv_mm8_seq_tc_workspace_bytes(int64_t B, int64_t N);
+extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
+                               const uint8_t* w, int64_t w_stride, const void* mx, const void* rx,
+                               const void* my, const void* ry, int dtype, void* y, int64_t y_stride,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
+static int g_seq_path = 0;      // 0 = automatic, 1 = CUDA cores only, 2 = tensor cores whenever the layout allows
+extern "C" void rwkv_mm8_seq_set_path(int path) { g_seq_path = path; }
+constexpr int kTcMinRows = 64;  // below this the 128-row tensor-core tile is mostly padding
+
 extern "C" size_t rwkv_mm8_seq_workspace_bytes(int64_t B, int64_t N, int64_t M) {
-    (void)B; (void)N; (void)M;
-    return 0;
+    (void)M;
+    if (B < 1 || N < 1) return 0;
+    return rwkv_mm8_seq_tc_workspace_bytes(B, N);
 }
 
 extern "C" int rwkv_mm8_seq(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
                             const uint8_t* w, int64_t w_stride,
                             const void* mx, const void* rx, const void* my, const void* ry, int dtype,
                             void* y, int64_t y_stride, void* workspace, size_t workspace_bytes, void* stream) {
-    (void)workspace; (void)workspace_bytes;
     RWKV_CHECK_ARG(B >= 1 && N >= 1 && M >= 1 && N <= INT32_MAX && M <= INT32_MAX && B <= INT32_MAX);
     RWKV_CHECK_ARG(x && w && mx && rx && my && ry && y);
     RWKV_CHECK_ARG(x_stride >= N && w_stride >= M && y_stride >= M);
     RWKV_CHECK_ARG(dtype == RWKV_F16 || dtype == RWKV_F32);
+    if (g_seq_path != 1 && workspace != nullptr && (B >= kTcMinRows || g_seq_path == 2)) {
+        const int rc = rwkv_mm8_seq_tc(B, N, M, x, x_stride, w, w_stride, mx, rx, my, ry, dtype, y, y_stride,
+                                       workspace, workspace_bytes, stream);
+        if (rc != RWKV_ERR_UNSUPPORTED && rc != RWKV_ERR_WORKSPACE) return rc;   // else: CUDA-core kernel below
+    }
     dim3 grid((unsigned)((M + TN - 1) / TN), (unsigned)((B + TM - 1) / TM));
     if (grid.y > 65535) return RWKV_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -1,0 +1,384 @@
+// mm8_seq on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory).
+//
+//   y[t,n] = rx[n] * sum_k x'[t,k] (w[k,n] - 128) + rx[n]*128.5*SXR[t] + mx[n]*SX[t] + SXMY[t]
+//
+// with x' = x*ry, SX = sum_k x, SXR = sum_k x', SXMY = sum_k x*my (per row t): the same
+// factorisation as mm8_one.  The contraction runs as fp16 x fp16 -> fp32 UMMA:
+//   * (w - 128) is exact in fp16 and is produced on the fly: producer threads read uint8 rows
+//     of W, transpose 8x8 byte blocks in registers and write fp16 core matrices (K-major,
+//     no swizzle) into the B tile;
+//   * x' (an fp32 product) is split into hi = fp16(x') and lo = fp16(x' - hi) by a small
+//     preparation kernel; both halves are multiplied into the same accumulator, so the sum
+//     carries ~22 bits of x' and matches the fp32 CUDA-core kernel to rounding.
+//
+// CTA = 128 (rows of x) x 256 (columns of W) output tile, K in blocks of 64, 3 stages.
+//   warps 0-7  producers (cp.async of the A tiles; W rows are fetched four K blocks ahead into
+//              registers and converted into the B tile), then epilogue: tcgen05.ld of their
+//              32 TMEM lanes (warp % 4) x 128 columns (warp / 4), affine epilogue, fp16 stores
+//   warp 8     TMEM allocation; lane 0 issues tcgen05.mma and tcgen05.commit
+// Synchronisation is by mbarriers only.  Every wait is bounded: on give-up the CTA raises an
+// error word, skips the rest of its work, frees its tensor memory and returns.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 3;
+constexpr int kProducers = 256;
+constexpr int kProdWarps = kProducers / 32;
+constexpr int kThreadsTc = kProducers + 32;
+constexpr int kWAhead = 4;                               // K blocks of W held in registers
+constexpr int kTileBytes = 128 * BK * 2;                 // 16 KB: one 128 x 64 fp16 operand tile
+constexpr int kBTileBytes = BN * BK * 2;                 // 32 KB
+constexpr int kStageBytes = 2 * kTileBytes + kBTileBytes;   // A_hi, A_lo, B
+constexpr int kSmemTc = STAGES * kStageBytes + 1024;     // + barriers, TMEM address
+constexpr uint32_t kLBO = 128;                           // bytes between core matrices along K
+constexpr uint32_t kSBO = (BK / 8) * 128;                // bytes between 8-row groups
+constexpr unsigned kWaitLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t s2u(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (unsigned it = 0; it < kWaitLimit; ++it) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// zero-filling 16-byte async copy (src_bytes = 0 writes zeros)
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// arrive on `bar` when all cp.async of this thread issued so far have landed
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major, no swizzle, core matrices of 8 rows x 16 bytes.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);         // start address
+    d |= (uint64_t)(kLBO >> 4) << 16;                    // leading (K) byte offset
+    d |= (uint64_t)(kSBO >> 4) << 32;                    // stride (M/N) byte offset
+    d |= (uint64_t)1 << 46;                              // descriptor version of sm_100
+    return d;                                            // layout type 0: no swizzle
+}
+// Instruction descriptor, kind::f16: fp16 A and B (both K-major), fp32 accumulator, M x N tile.
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
+    uint32_t d = 0;
+    d |= 1u << 4;                       // accumulator format: f32
+    d |= 0u << 7;                       // A: f16
+    d |= 0u << 10;                      // B: f16
+    d |= (uint32_t)(n >> 3) << 17;
+    d |= (uint32_t)(m >> 4) << 24;
+    return d;
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- preparation: x' hi/lo split and the three row sums ---------------------------------------
+template <typename F>
+__global__ void __launch_bounds__(256) mm8_seq_prep(int T, int N, int Npad, const F* __restrict__ x, long long x_stride,
+                                                    const F* __restrict__ ry, const F* __restrict__ my,
+                                                    __half* __restrict__ hi, __half* __restrict__ lo,
+                                                    float* __restrict__ sums) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int t = blockIdx.x;
+    __shared__ float sh[3][8];
+    float sx = 0.f, sxr = 0.f, sxmy = 0.f;
+    for (int k = threadIdx.x; k < Npad; k += 256) {
+        float xp = 0.f;
+        if (k < N) {
+            const float xv = to_f32<F>(x[(long long)t * x_stride + k]);
+            xp = xv * to_f32<F>(ry[k]);
+            sx += xv;
+            sxr += xp;
+            sxmy = fmaf(xv, to_f32<F>(my[k]), sxmy);
+        }
+        const __half h = __float2half_rn(xp);
+        hi[(long long)t * Npad + k] = h;
+        lo[(long long)t * Npad + k] = __float2half_rn(xp - __half2float(h));
+    }
+    sx = warp_sum(sx); sxr = warp_sum(sxr); sxmy = warp_sum(sxmy);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sh[0][warp] = sx; sh[1][warp] = sxr; sh[2][warp] = sxmy; }
+    __syncthreads();
+    if (threadIdx.x < 3) {
+        float s = 0.f;
+        for (int i = 0; i < 8; ++i) s += sh[threadIdx.x][i];
+        sums[t * 4 + threadIdx.x] = s;
+    }
+}
+
+// 8 bytes of one column (k = 0..7) -> 8 fp16 values (byte - 128), packed as a uint4
+__device__ __forceinline__ uint4 bytes_to_half8(uint32_t lo4, uint32_t hi4) {
+    const uint32_t magic = 0x64646464u;          // fp16 0x64xx = 1024 + xx
+    const __half2 off = __floats2half2_rn(1152.f, 1152.f);
+    uint32_t w[4] = {__byte_perm(lo4, magic, 0x5140), __byte_perm(lo4, magic, 0x5342),
+                     __byte_perm(hi4, magic, 0x5140), __byte_perm(hi4, magic, 0x5342)};
+    uint4 out;
+    uint32_t* o = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __half2 h = __hsub2(*reinterpret_cast<__half2*>(&w[i]), off);
+        o[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return out;
+}
+
+struct TcArgs {
+    const __half* hi; const __half* lo; long long lda;      // [T, Npad] fp16 (K contiguous)
+    const float* sums;                                        // [T, 4]: SX, SXR, SXMY
+    const uint8_t* w; long long w_stride;
+    const void* mx; const void* rx;                           // [M] in the output dtype
+    void* y; long long y_stride;
+    int T, N, M;
+    unsigned* error_flag;
+};
+
+template <typename F>
+__global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs a) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const int nkb = (a.N + BK - 1) / BK;
+
+    uint8_t* bars = smem + STAGES * kStageBytes;
+    const uint32_t full0 = s2u(bars), empty0 = full0 + STAGES * 8, accum_bar = empty0 + STAGES * 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + (2 * STAGES + 1) * 8);
+    int* failed = reinterpret_cast<int*>(bars + (2 * STAGES + 1) * 8 + 8);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + s * 8, 2 * kProducers);    // per producer: its cp.async arrival + its own arrive
+            mbar_init(empty0 + s * 8, 1);                // tcgen05.commit
+        }
+        mbar_init(accum_bar, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kProdWarps) {                            // one warp allocates BN fp32 accumulator columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    if (warp < kProdWarps) {
+        // ================= producers =================
+        const int cg = tid & 31, rg = tid >> 5;          // B: 8 columns x 8 k-rows per thread
+        const int ncol = n0 + cg * 8;
+        const bool col_ok = ncol < a.M;                  // M % 8 == 0 is a launch condition
+        uint2 wreg[kWAhead][8];                          // W rows of the next kWAhead K blocks
+        auto load_w = [&](int kb, uint2 (&dst)[8]) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int k = kb * BK + rg * 8 + i;
+                dst[i] = (col_ok && k < a.N) ? __ldg(reinterpret_cast<const uint2*>(a.w + (long long)k * a.w_stride + ncol))
+                                             : make_uint2(0x80808080u, 0x80808080u);   // code 128 -> value 0
+            }
+        };
+#pragma unroll
+        for (int u = 0; u < kWAhead; ++u)
+            if (u < nkb) load_w(u, wreg[u]);
+        bool ok = true;
+        for (int kb0 = 0; kb0 < nkb && ok; kb0 += kWAhead) {
+#pragma unroll
+            for (int u = 0; u < kWAhead; ++u) {
+                const int kb = kb0 + u;
+                if (kb >= nkb || !ok) continue;
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                ok = mbar_wait(empty0 + s * 8, ph ^ 1);
+                if (!ok) continue;
+                uint8_t* stage = smem + s * kStageBytes;
+                // A tiles: 128 rows x 8 chunks of 16 bytes, twice (hi, lo); 4 chunks per thread each
+                const uint32_t a_hi = s2u(stage), a_lo = a_hi + kTileBytes;
+#pragma unroll
+                for (int i = 0; i < (128 * 8) / kProducers; ++i) {
+                    const int c = tid + i * kProducers;
+                    const int row = c >> 3, kc = c & 7;
+                    const int t = m0 + row, k = kb * BK + kc * 8;
+                    const bool in = t < a.T && k < a.lda;    // hi/lo are zero padded up to lda
+                    const long long off = in ? (long long)t * a.lda + k : 0;
+                    const uint32_t dst = (row >> 3) * kSBO + kc * kLBO + (row & 7) * 16;
+                    cp_async16_zfill(a_hi + dst, a.hi + off, in ? 16 : 0);
+                    cp_async16_zfill(a_lo + dst, a.lo + off, in ? 16 : 0);
+                }
+                cp_async_arrive(full0 + s * 8);
+                // B tile: transpose this thread's 8x8 byte block, convert, store one core matrix
+                uint32_t lo4[8], hi4[8];                 // column j: bytes of k = 0..3 and k = 4..7
+                {
+                    uint32_t x0[2], x1[2];
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {   // rows 0-3, rows 4-7
+                        const uint2* r = &wreg[u][half * 4];
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {        // columns 0-3 (.x), 4-7 (.y)
+                            const uint32_t a0 = q ? r[0].y : r[0].x, a1 = q ? r[1].y : r[1].x;
+                            const uint32_t a2 = q ? r[2].y : r[2].x, a3 = q ? r[3].y : r[3].x;
+                            x0[0] = __byte_perm(a0, a1, 0x5140); x0[1] = __byte_perm(a2, a3, 0x5140);
+                            x1[0] = __byte_perm(a0, a1, 0x7362); x1[1] = __byte_perm(a2, a3, 0x7362);
+                            uint32_t* dstw = half ? hi4 : lo4;
+                            dstw[q * 4 + 0] = __byte_perm(x0[0], x0[1], 0x5410);
+                            dstw[q * 4 + 1] = __byte_perm(x0[0], x0[1], 0x7632);
+                            dstw[q * 4 + 2] = __byte_perm(x1[0], x1[1], 0x5410);
+                            dstw[q * 4 + 3] = __byte_perm(x1[0], x1[1], 0x7632);
+                        }
+                    }
+                }
+                if (kb + kWAhead < nkb) load_w(kb + kWAhead, wreg[u]);   // refill this register slot
+                uint8_t* bt = stage + 2 * kTileBytes + cg * kSBO + rg * kLBO;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(bt + j * 16) = bytes_to_half8(lo4[j], hi4[j]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(full0 + s * 8);
+            }
+        }
+        // ================= epilogue =================
+        if (ok) ok = mbar_wait(accum_bar, 0);
+        if (!ok) atomicExch(failed, 1);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const int quarter = warp & 3, chalf = warp >> 2;     // TMEM lanes 32*quarter.., columns 128*chalf..
+            const int t = m0 + quarter * 32 + lane;
+            float sx = 0.f, sxr = 0.f, sxmy = 0.f;
+            if (t < a.T) { sx = a.sums[t * 4 + 0]; sxr = a.sums[t * 4 + 1]; sxmy = a.sums[t * 4 + 2]; }
+            const F* mx = static_cast<const F*>(a.mx);
+            const F* rx = static_cast<const F*>(a.rx);
+            F* yrow = static_cast<F*>(a.y) + (long long)t * a.y_stride;
+#pragma unroll 1
+            for (int c = chalf * 4; c < chalf * 4 + 4; ++c) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 32;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                    "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (t < a.T) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int n = n0 + c * 32 + j;
+                        if (n < a.M) {
+                            const float rxn = to_f32<F>(rx[n]);
+                            const float val = fmaf(rxn, __uint_as_float(v[j]), fmaf(rxn * 128.5f, sxr, fmaf(to_f32<F>(mx[n]), sx, sxmy)));
+                            yrow[n] = from_f32<F>(val);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (lane == 0) {
+        // ================= MMA issuer =================
+        const uint32_t idesc = umma_idesc(BM, BN);
+        bool ok = true;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const int s = kb % STAGES;
+            const uint32_t ph = (kb / STAGES) & 1;
+            ok = mbar_wait(full0 + s * 8, ph);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            const uint32_t a_hi = s2u(smem + s * kStageBytes), a_lo = a_hi + kTileBytes, b_t = a_hi + 2 * kTileBytes;
+#pragma unroll
+            for (int j = 0; j < BK / 16; ++j) {          // one UMMA consumes K = 16: two core matrices
+                const uint64_t bd = umma_desc(b_t + j * 2 * kLBO);
+                umma_f16(tmem_base, umma_desc(a_hi + j * 2 * kLBO), bd, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                umma_f16(tmem_base, umma_desc(a_lo + j * 2 * kLBO), bd, idesc, 1u);
+            }
+            umma_commit(empty0 + s * 8);                 // frees the stage when these MMAs retire
+        }
+        if (ok) umma_commit(accum_bar);                  // accumulator complete
+        else atomicExch(failed, 1);
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == kProdWarps) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    }
+    if (tid == 0 && *failed) atomicExch(a.error_flag, 1u);
+}
+
+}  // namespace
+
+// Scratch of the tensor-core path: hi and lo copies of x' ([B, Npad] fp16 each), the row sums
+// and one error word.
+extern "C" size_t rwkv_mm8_seq_tc_workspace_bytes(int64_t B, int64_t N) {
+    const int64_t npad = (N + BK - 1) / BK * BK;
+    return size_t(B) * size_t(npad) * 4 + size_t(B) * 16 + 256;
+}
+
+// Returns RWKV_ERR_UNSUPPORTED when the operands do not meet the layout the tensor-core kernel
+// needs (the caller then uses the CUDA-core kernel).
+extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
+                               const uint8_t* w, int64_t w_stride, const void* mx, const void* rx,
+                               const void* my, const void* ry, int dtype, void* y, int64_t y_stride,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    RWKV_CHECK_ARG(B >= 1 && N >= 1 && M >= 1 && x && w && mx && rx && my && ry && y);
+    if (dtype != RWKV_F16) return RWKV_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(w) % 8 != 0 || w_stride % 8 != 0 || M % 8 != 0) return RWKV_ERR_UNSUPPORTED;
+    if (workspace == nullptr || workspace_bytes < rwkv_mm8_seq_tc_workspace_bytes(B, N)) return RWKV_ERR_WORKSPACE;
+    RWKV_CHECK_ALIGN(workspace, 256);
+    if ((B + BM - 1) / BM > 65535) return RWKV_ERR_UNSUPPORTED;
+    const int64_t npad = (N + BK - 1) / BK * BK;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    unsigned* err = reinterpret_cast<unsigned*>(ws);
+    float* sums = reinterpret_cast<float*>(ws + 256);
+    __half* hi = reinterpret_cast<__half*>(ws + 256 + size_t(B) * 16);
+    __half* lo = hi + size_t(B) * size_t(npad);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = rwkv_launch_pdl(mm8_seq_prep<__half>, dim3((unsigned)B), dim3(256), 0, st, int(B), int(N), int(npad),
+                             static_cast<const __half*>(x), (long long)x_stride, static_cast<const __half*>(ry),
+                             static_cast<const __half*>(my), hi, lo, sums);
+    if (rc != RWKV_OK) return rc;
+    TcArgs a;
+    a.hi = hi; a.lo = lo; a.lda = npad; a.sums = sums; a.w = w; a.w_stride = w_stride; a.mx = mx; a.rx = rx;
+    a.y = y; a.y_stride = y_stride; a.T = int(B); a.N = int(N); a.M = int(M); a.error_flag = err;
+    auto kern = mm8_seq_tc_kernel<__half>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc) != cudaSuccess) {
+            cudaGetLastError();
+            return RWKV_ERR_LAUNCH;
+        }
+        configured = true;
+    }
+    dim3 grid((unsigned)((M + BN - 1) / BN), (unsigned)((B + BM - 1) / BM));
+    return rwkv_launch_pdl(kern, grid, dim3(kThreadsTc), size_t(kSmemTc), st, a);
+}
+
+extern "C" int rwkv_mm8_seq_tc_take_error(void* workspace, void* stream, int* error_out) {
+    RWKV_CHECK_ARG(workspace != nullptr && error_out != nullptr);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned v = 0;
+    if (cudaMemcpyAsync(&v, workspace, sizeof(v), cudaMemcpyDeviceToHost, st) != cudaSuccess) return RWKV_ERR_LAUNCH;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return RWKV_ERR_LAUNCH;
+    if (v != 0 && cudaMemsetAsync(workspace, 0, sizeof(v), st) != cudaSuccess) return RWKV_ERR_LAUNCH;
+    *error_out = int(v);
+    return RWKV_OK;
+}

@@ -34,12 +34,14 @@ _DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF
 _workspaces = {}
 
 
-def workspace(device, nbytes):
-    """Scratch for the split-K reductions.  Keyed by (device, stream): calls that share a
-    buffer are ordered by the stream."""
+def workspace(device, nbytes, kind="mm8_one"):
+    """Scratch of an operator (split-K partials and tickets of mm8_one; hi/lo activation copies
+    of the tensor-core mm8_seq).  Keyed by (kind, device, stream): the kinds lay their buffers
+    out differently and mm8_one relies on finding its tickets zero, so they never share one;
+    calls that share a buffer are ordered by the stream."""
     if nbytes == 0:
         return None
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (kind, device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         if torch.cuda.is_current_stream_capturing():
@@ -129,7 +131,7 @@ def mm8_seq_(B, N, M, x, w, mx, rx, my, ry, y):
     dev = w.device
     with torch.cuda.device(dev):
         nbytes = lib().rwkv_mm8_seq_workspace_bytes(B, N, M)
-        ws = workspace(dev, nbytes)
+        ws = workspace(dev, nbytes, "mm8_seq")
         check(lib().rwkv_mm8_seq(B, N, M, x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0),
                                  mx.data_ptr(), rx.data_ptr(), my.data_ptr(), ry.data_ptr(), _DT[x.dtype],
                                  y.data_ptr(), y.stride(0), ws.data_ptr() if ws is not None else None,

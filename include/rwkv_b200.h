@@ -238,7 +238,17 @@ int rwkv_mm8_chain_take_error(void* workspace, void* stream, int* error_out);
  *
  * x [B, N] row stride x_stride, y [B, M] row stride y_stride, both in `dtype`, fp32
  * accumulation, one rounding to `dtype` at the store (operators.cu:138).
+ * Two kernels: from 64 rows up, fp16 operands whose w is 8-byte aligned (pointer, stride, M)
+ * run on the tensor cores (tcgen05 UMMA, fp32 accumulation in tensor memory; x*ry enters as
+ * an exact hi + lo pair of fp16 values) and need `workspace` =
+ * rwkv_mm8_seq_workspace_bytes(B, N, M) bytes, 256-byte aligned, zero when first handed over;
+ * everything else (or workspace == NULL) runs on a CUDA-core kernel that accepts any layout.
+ * rwkv_mm8_seq_set_path: 0 automatic, 1 CUDA cores only, 2 tensor cores whenever possible.
+ * rwkv_mm8_seq_tc_take_error synchronises `stream` and returns/clears the workspace's error
+ * word (1 if a bounded wait inside the tensor-core kernel gave up; outputs then undefined).
  * ------------------------------------------------------------------------------------- */
+void rwkv_mm8_seq_set_path(int path);
+int rwkv_mm8_seq_tc_take_error(void* workspace, void* stream, int* error_out);
 size_t rwkv_mm8_seq_workspace_bytes(int64_t B, int64_t N, int64_t M);
 int rwkv_mm8_seq(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
                  const uint8_t* w, int64_t w_stride,

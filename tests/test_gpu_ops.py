@@ -215,3 +215,34 @@ def test_op_schemas(ops):
     for ns in (torch.ops.rwkv5, torch.ops.rwkv6):
         for f in ("forward_bf16", "forward_fp16", "forward_fp32"):
             assert hasattr(ns, f)
+
+
+@pytest.mark.parametrize("T,N,M", [(128, 256, 128), (64, 64, 128), (200, 768, 3072), (1024, 4096, 512), (257, 1000, 264)])
+def test_mm8_seq_tensor_core_path(ops, T, N, M):
+    """Rows >= 64 with an 8-byte-aligned matrix run on tcgen05; same oracle, same tolerance.
+    Includes ragged T (not a multiple of 128), N (not a multiple of 64) and M (not of 128)."""
+    import ctypes
+    from chatrwkv_b200 import _lib
+    from tests.util import packed_case
+    cpu, dev = packed_case(N, M, seed=N * 3 + M + T)
+    g = torch.Generator().manual_seed(T)
+    x = torch.randn(T, N, generator=g).half()
+    ref = orc.mm8_kernel(x, *cpu)
+    y = torch.empty((T, M), dtype=torch.float16, device="cuda")
+    torch.ops.rwkv.mm8_seq(T, N, M, x.cuda(), *dev, y)
+    torch.cuda.synchronize()
+    ws = ops.workspace(torch.device("cuda", torch.cuda.current_device()), 1024, "mm8_seq")
+    e = ctypes.c_int(0)
+    assert _lib.lib().rwkv_mm8_seq_tc_take_error(ws.data_ptr(), None, ctypes.byref(e)) == 0 and e.value == 0
+    err = (y.float().cpu() - ref).abs()
+    tol = ref.abs() * 2 ** -10 + 1e-4
+    assert (err <= tol).all(), err.max().item()
+    assert (y.cpu() != ref.half()).float().mean().item() < 0.05
+    # and against the CUDA-core kernel
+    _lib.lib().rwkv_mm8_seq_set_path(1)
+    try:
+        y2 = torch.empty_like(y)
+        torch.ops.rwkv.mm8_seq(T, N, M, x.cuda(), *dev, y2)
+    finally:
+        _lib.lib().rwkv_mm8_seq_set_path(0)
+    assert ((y.float() - y2.float()).abs() <= y2.float().abs() * 2 ** -9 + 2e-4).all()
