@@ -200,6 +200,7 @@ def main():
         torch.cuda.synchronize(dev)
 
     # ---- prefill (reported, not the headline) ------------------------------------------
+    model.forward(prompt[:192], None)            # untimed: sizes workspaces, loads kernels
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(dev)
     ev0.record()

@@ -28,11 +28,14 @@ constexpr int kProdWarps = kProducers / 32;
 constexpr int kThreadsTc = kProducers + 32;
 constexpr int kWAhead = 4;                               // K blocks of W held in registers
 constexpr int kTileBytes = 128 * BK * 2;                 // 16 KB: one 128 x 64 fp16 operand tile
-constexpr int kBTileBytes = BN * BK * 2;                 // 32 KB
+constexpr uint32_t kSBO_B = (BK / 8) * 128 + 16;         // B: 8-row groups 16 bytes further apart, so that the
+                                                         // 32 lanes that each store one core matrix of a
+                                                         // different group hit different shared-memory banks
+constexpr int kBTileBytes = (BN / 8) * kSBO_B;           // 32.5 KB
 constexpr int kStageBytes = 2 * kTileBytes + kBTileBytes;   // A_hi, A_lo, B
 constexpr int kSmemTc = STAGES * kStageBytes + 1024;     // + barriers, TMEM address
 constexpr uint32_t kLBO = 128;                           // bytes between core matrices along K
-constexpr uint32_t kSBO = (BK / 8) * 128;                // bytes between 8-row groups
+constexpr uint32_t kSBO = (BK / 8) * 128;                // A: bytes between 8-row groups
 constexpr unsigned kWaitLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t s2u(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -62,11 +65,11 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
 }
 
 // Shared-memory matrix descriptor: K-major, no swizzle, core matrices of 8 rows x 16 bytes.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t sbo) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);         // start address
     d |= (uint64_t)(kLBO >> 4) << 16;                    // leading (K) byte offset
-    d |= (uint64_t)(kSBO >> 4) << 32;                    // stride (M/N) byte offset
+    d |= (uint64_t)(sbo >> 4) << 32;                     // stride (M/N) byte offset
     d |= (uint64_t)1 << 46;                              // descriptor version of sm_100
     return d;                                            // layout type 0: no swizzle
 }
@@ -147,6 +150,7 @@ struct TcArgs {
     const void* mx; const void* rx;                           // [M] in the output dtype
     void* y; long long y_stride;
     int T, N, M;
+    int vec_ok;                                               // y, rx, mx allow 16-byte accesses
     unsigned* error_flag;
 };
 
@@ -214,8 +218,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                 const uint32_t a_hi = s2u(stage), a_lo = a_hi + kTileBytes;
 #pragma unroll
                 for (int i = 0; i < (128 * 8) / kProducers; ++i) {
+                    // 8 consecutive lanes = the 8 rows of one core matrix: 128 contiguous bytes of
+                    // shared memory per store phase, 64 contiguous bytes per row on the global side
                     const int c = tid + i * kProducers;
-                    const int row = c >> 3, kc = c & 7;
+                    const int row = ((c >> 6) << 3) | (c & 7), kc = (c >> 3) & 7;
                     const int t = m0 + row, k = kb * BK + kc * 8;
                     const bool in = t < a.T && k < a.lda;    // hi/lo are zero padded up to lda
                     const long long off = in ? (long long)t * a.lda + k : 0;
@@ -246,7 +252,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                     }
                 }
                 if (kb + kWAhead < nkb) load_w(kb + kWAhead, wreg[u]);   // refill this register slot
-                uint8_t* bt = stage + 2 * kTileBytes + cg * kSBO + rg * kLBO;
+                uint8_t* bt = stage + 2 * kTileBytes + cg * kSBO_B + rg * kLBO;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(bt + j * 16) = bytes_to_half8(lo4[j], hi4[j]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -279,13 +285,33 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                     : "r"(taddr) : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (t < a.T) {
+                    const int nb = n0 + c * 32;
+                    if (a.vec_ok && nb + 32 <= a.M) {       // 4 x (8 columns: 16-byte loads of rx, mx, 16-byte store)
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int n = n0 + c * 32 + j;
-                        if (n < a.M) {
-                            const float rxn = to_f32<F>(rx[n]);
-                            const float val = fmaf(rxn, __uint_as_float(v[j]), fmaf(rxn * 128.5f, sxr, fmaf(to_f32<F>(mx[n]), sx, sxmy)));
-                            yrow[n] = from_f32<F>(val);
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 r4 = __ldg(reinterpret_cast<const uint4*>(rx + nb) + q);
+                            const uint4 m4 = __ldg(reinterpret_cast<const uint4*>(mx + nb) + q);
+                            const __half* rh = reinterpret_cast<const __half*>(&r4);
+                            const __half* mh = reinterpret_cast<const __half*>(&m4);
+                            uint4 o4;
+                            __half* oh = reinterpret_cast<__half*>(&o4);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float rxn = __half2float(rh[e]);
+                                oh[e] = __float2half_rn(fmaf(rxn, __uint_as_float(v[q * 8 + e]),
+                                                             fmaf(rxn * 128.5f, sxr, fmaf(__half2float(mh[e]), sx, sxmy))));
+                            }
+                            reinterpret_cast<uint4*>(yrow + nb)[q] = o4;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int n = nb + j;
+                            if (n < a.M) {
+                                const float rxn = to_f32<F>(rx[n]);
+                                const float val = fmaf(rxn, __uint_as_float(v[j]), fmaf(rxn * 128.5f, sxr, fmaf(to_f32<F>(mx[n]), sx, sxmy)));
+                                yrow[n] = from_f32<F>(val);
+                            }
                         }
                     }
                 }
@@ -305,9 +331,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
             const uint32_t a_hi = s2u(smem + s * kStageBytes), a_lo = a_hi + kTileBytes, b_t = a_hi + 2 * kTileBytes;
 #pragma unroll
             for (int j = 0; j < BK / 16; ++j) {          // one UMMA consumes K = 16: two core matrices
-                const uint64_t bd = umma_desc(b_t + j * 2 * kLBO);
-                umma_f16(tmem_base, umma_desc(a_hi + j * 2 * kLBO), bd, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-                umma_f16(tmem_base, umma_desc(a_lo + j * 2 * kLBO), bd, idesc, 1u);
+                const uint64_t bd = umma_desc(b_t + j * 2 * kLBO, kSBO_B);
+                umma_f16(tmem_base, umma_desc(a_hi + j * 2 * kLBO, kSBO), bd, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                umma_f16(tmem_base, umma_desc(a_lo + j * 2 * kLBO, kSBO), bd, idesc, 1u);
             }
             umma_commit(empty0 + s * 8);                 // frees the stage when these MMAs retire
         }
@@ -359,6 +385,8 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
     TcArgs a;
     a.hi = hi; a.lo = lo; a.lda = npad; a.sums = sums; a.w = w; a.w_stride = w_stride; a.mx = mx; a.rx = rx;
     a.y = y; a.y_stride = y_stride; a.T = int(B); a.N = int(N); a.M = int(M); a.error_flag = err;
+    a.vec_ok = (reinterpret_cast<uintptr_t>(y) % 16 == 0 && y_stride % 8 == 0 && reinterpret_cast<uintptr_t>(rx) % 16 == 0 &&
+                reinterpret_cast<uintptr_t>(mx) % 16 == 0) ? 1 : 0;
     auto kern = mm8_seq_tc_kernel<__half>;
     static bool configured = false;
     if (!configured) {
