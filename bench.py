@@ -156,6 +156,8 @@ def main():
     ap.add_argument("--shape", default=WORKLOAD)
     ap.add_argument("--prompt", type=int, default=PROMPT)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="profiling aid: build only this many layers of the shape (the line is then not a bench result)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -186,6 +188,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     L, D, Fn, V = synth.SHAPES[a.shape]
+    if a.layers > 0:
+        L = a.layers
     version = 6 if a.shape.startswith("v6") else 4
     ck = synth.make_checkpoint(version, L, D, Fn, V, seed=1002, device=dev)
     model = RWKV(ck, f"cuda:{local_rank} fp16i8", verbose=False)
@@ -217,6 +221,7 @@ def main():
     sampler = ClockSampler(local_rank)
     barrier()
     sampler.start()
+    torch.cuda.cudart().cudaProfilerStart()      # lets `ncu --profile-from-start off` see the timed region only
     ev0.record()
     for _ in range(a.steps):
         logits, state = model.forward(tok, state)
@@ -242,6 +247,7 @@ def main():
         t_host = int(host_logits.argmax())
     ev1.record()
     barrier()
+    torch.cuda.cudart().cudaProfilerStop()
     clocks = sampler.stop()
     e2e_ms = ev0.elapsed_time(ev1)
 
@@ -275,6 +281,8 @@ def main():
             "prefill": {"tokens": a.prompt, "ms": prefill_ms, "tokens_per_s": a.prompt / (prefill_ms / 1e3)},
             "clocks": clocks, "roofline": roof, "cpu_baseline": cb,
         }
+        if a.layers > 0:
+            line["note"] = f"profiling run with {a.layers} layers: not a benchmark result"
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
