@@ -26,7 +26,7 @@ import types
 import torch
 import torch.nn.functional as F
 
-from . import _lib, ops
+from . import _lib, ops, shard
 from ._lib import (EPI_MUL_RESIDUAL, EPI_RELU_SQ, EPI_RESIDUAL, EPI_SIGMOID, EPI_STORE, EPI_STORE_F32, check, lib)
 
 STRATEGY_REGEX = r"^(?:(?:^|->) *(?:cuda(?::[\d]+)?|cpu|mps|dml) (?:fp(?:16|32)|bf16)(?:i8|i4|i3)?(?: \*[\d]+\+?)? *)+$"
@@ -42,8 +42,12 @@ def _ptr_array(tensors):
 
 
 class RWKV:
-    def __init__(self, model, strategy, verbose=True, convert_and_save_and_exit=None):
+    def __init__(self, model, strategy, verbose=True, convert_and_save_and_exit=None, shard_rank=0, shard_world=1):
+        """`shard_world` > 1 (an addition to the reference's signature): this process is rank
+        `shard_rank` of a torch.distributed group that runs ONE model with every packed matrix
+        split by output columns (shard.py); all ranks must make the same forward calls."""
         prxxx = print if verbose else (lambda *a, **k: None)
+        self._rank, self._world = int(shard_rank), int(shard_world)
         if not re.match(STRATEGY_REGEX, strategy):
             raise ValueError("Invalid strategy. Please read https://pypi.org/project/rwkv/")
         strategy = ("->".join([x.strip() for x in strategy.split("->")])).replace("->", " -> ")
@@ -194,6 +198,18 @@ class RWKV:
 
             if self.version != 4:
                 args.n_head = w["blocks.0.att.time_first"].shape[0]
+            self._full_m = {}
+            if self._world > 1:
+                if self.version != 4:
+                    raise NotImplementedError("column sharding is implemented for RWKV-4")
+                for x in [k for k, t in w.items() if torch.is_tensor(t) and t.dtype == torch.uint8]:
+                    self._full_m[x] = w[x].shape[1]
+                    if shard.column_range(w[x].shape[1], self._world, self._world - 1)[0] >= w[x].shape[1]:
+                        raise ValueError(f"{x}: {w[x].shape[1]} columns are too few for {self._world} ranks")
+                    w[x], w[x + "_mx"], w[x + "_rx"] = shard.column_shard(w[x], w[x + "_mx"], w[x + "_rx"],
+                                                                         self._world, self._rank)
+                self._use_graph = False      # collectives between the launches: direct launches
+                torch.cuda.empty_cache()
             self._init_buffers()
         gc.collect()
         torch.cuda.empty_cache()
@@ -217,7 +233,8 @@ class RWKV:
         self._b = types.SimpleNamespace(
             x=h(D), m0=h(D), m1=h(D), m2=h(D), m3=h(D), m4=h(D), r=h(a.n_att), k=h(a.n_att), v=h(a.n_att),
             g=h(a.n_att), att=h(a.n_att), fk=h(Fn), fr=h(D), xln=h(D),
-            logits=torch.zeros(self.w["head.weight"].shape[1], dtype=torch.float32, device=dev),
+            logits=torch.zeros(self._full_m.get("head.weight", self.w["head.weight"].shape[1]), dtype=torch.float32,
+                               device=dev),
             tok=torch.zeros(1, dtype=torch.int64, device=dev))
         self._tok_host = torch.zeros(256, dtype=torch.int64).pin_memory()   # ring of H2D staging slots
         self._tok_slot = 0
@@ -228,6 +245,7 @@ class RWKV:
         self._st = None
         self._cur = 0
         self._graphs = [None, None]
+        self._locbuf = {}
         self._chain = [None, None]      # per direction: (device launch table, n_launches, n_ctas)
         self._head_launch = [None, None]
         # RWKV_B200_CHAIN=1: run the layers of a token as one persistent cooperative kernel
@@ -321,7 +339,7 @@ class RWKV:
             self._tok_host[slot] = token
             self._b.tok.copy_(self._tok_host[slot:slot + 1], non_blocking=True)
         fused = self.version == 4
-        step = self._step_one_v4 if fused else self._step_one_generic
+        step = (self._step_one_v4_sharded if self._world > 1 else self._step_one_v4) if fused else self._step_one_generic
         cur = self._cur
         if not self._use_graph:
             step(cur)
@@ -394,6 +412,57 @@ class RWKV:
                                         self._ws.numel(), host.data_ptr(), nbytes), "mm8_chain_plan")
         self._chain[cur] = (host.to(self.device), len(launches), n_ctas)
 
+    def _step_one_v4_sharded(self, cur):
+        """One RWKV-4 token with every matmul split by output columns over the ranks: the same
+        launches as `_launches_v4` on this rank's column slices, an all-gather of the fp16
+        slices after each (r, k, v; x; ffn r, k; x; logits) -- four gathers per layer."""
+        b, w, a = self._b, self.w, self.args
+        G, R = self._world, self._rank
+        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
+        sin, sout = self._st[cur], self._st[1 - cur]
+        P, ln, wk = self._problem, ops.with_ln_mix, ops.with_wkv4
+        D, Fn = a.n_embd, a.n_ffn
+
+        def loc(key, M, dtype=torch.float16):
+            t = self._locbuf.get(key)
+            if t is None:
+                t = self._locbuf[key] = torch.zeros(shard.shard_width(M, G), dtype=dtype, device=self.device)
+            return t
+
+        def gather(pairs):
+            for full, local in pairs:
+                full.copy_(shard.gather_columns(local, full.numel(), G))
+
+        def run(problems):
+            problems = [p for p in problems if p.M > 0]
+            if problems:
+                self._gemv(problems)
+
+        lo_d, hi_d = shard.column_range(D, G, R)
+        for i in range(a.n_layer):
+            bb, att, ffn = f"blocks.{i}.", f"blocks.{i}.att.", f"blocks.{i}.ffn."
+            ln1 = (w[bb + "ln1.weight"], w[bb + "ln1.bias"])
+            ln2 = (w[bb + "ln2.weight"], w[bb + "ln2.bias"])
+            s = i * 5
+            lr, lk, lv, lx = loc("r", a.n_att), loc("k", a.n_att), loc("v", a.n_att), loc("x", D)
+            run([ln(P(b.x, att + "receptance.weight", lr, EPI_SIGMOID), *ln1, 0, sin[s], w[att + "time_mix_r"], sout[s]),
+                 ln(P(b.x, att + "key.weight", lk, EPI_STORE), *ln1, 0, sin[s], w[att + "time_mix_k"]),
+                 ln(P(b.x, att + "value.weight", lv, EPI_STORE), *ln1, 0, sin[s], w[att + "time_mix_v"])])
+            gather([(b.r, lr), (b.k, lk), (b.v, lv)])
+            run([wk(P(b.r, att + "output.weight", lx, EPI_RESIDUAL, aux=b.x[lo_d:]), b.k, b.v,
+                    w[att + "time_decay"], w[att + "time_first"], sin[s + 1:s + 4], sout[s + 1:s + 4])])
+            gather([(b.x, lx)])
+            lfr, lfk = loc("fr", D), loc("fk", Fn)
+            run([ln(P(b.x, ffn + "receptance.weight", lfr, EPI_SIGMOID), *ln2, 0, sin[s + 4], w[ffn + "time_mix_r"], sout[s + 4]),
+                 ln(P(b.x, ffn + "key.weight", lfk, EPI_RELU_SQ), *ln2, 0, sin[s + 4], w[ffn + "time_mix_k"])])
+            gather([(b.fr, lfr), (b.fk, lfk)])
+            scale = 0.5 if (self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0) else 1.0
+            run([P(b.fk, ffn + "value.weight", lx, EPI_MUL_RESIDUAL, aux=b.x[lo_d:], aux2=b.fr[lo_d:], out_scale=scale)])
+            gather([(b.x, lx)])
+        ll = loc("logits", b.logits.numel(), torch.float32)
+        run([ln(P(b.x, "head.weight", ll, EPI_STORE_F32), w["ln_out.weight"], w["ln_out.bias"], 2)])
+        gather([(b.logits, ll)])
+
     def _step_one_v4(self, cur):
         b, w = self._b, self.w
         torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
@@ -459,8 +528,15 @@ class RWKV:
         wq, mx, rx, my, ry = self._scales(name)
         T = x.shape[0]
         N, M = wq.shape
-        y = torch.empty((T, M), dtype=torch.float16, device=x.device)
-        torch.ops.rwkv.mm8_seq(T, N, M, x, wq, mx, rx, my, ry, y)
+        if self._world > 1:
+            full = self._full_m[name]
+            y = torch.zeros((T, shard.shard_width(full, self._world)), dtype=torch.float16, device=x.device)
+            if M > 0:
+                torch.ops.rwkv.mm8_seq(T, N, M, x, wq, mx, rx, my, ry, y[:, :M])
+            y = shard.gather_columns(y, full, self._world).contiguous()
+        else:
+            y = torch.empty((T, M), dtype=torch.float16, device=x.device)
+            torch.ops.rwkv.mm8_seq(T, N, M, x, wq, mx, rx, my, ry, y)
         return y if out_dtype is None else y.to(out_dtype)
 
     def _att_seq_v4(self, x, st, i):
@@ -568,8 +644,10 @@ class RWKV:
             x = x[-1:, :]
         xln = torch.empty_like(x)
         self._ln_mix(x.shape[0], x, None, w["ln_out.weight"], w["ln_out.bias"], 0, [], [], xx_out=xln)
-        if full_output:
+        if full_output or self._world > 1:
             out = self._mm_seq(xln, "head.weight")
+            if not full_output:
+                out = out[0]
         else:
             wq, mx, rx, my, ry = self._scales("head.weight")
             y = torch.zeros(wq.shape[1], dtype=torch.float32, device=self.device)
