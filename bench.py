@@ -156,6 +156,9 @@ def main():
     ap.add_argument("--shape", default=WORKLOAD)
     ap.add_argument("--prompt", type=int, default=PROMPT)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard", action="store_true",
+                    help="second multi-GPU mode: ONE model, every packed matrix split by output columns over the "
+                         "ranks with an NCCL all-gather after each matmul (strong scaling; use with --shape v4-14b)")
     ap.add_argument("--layers", type=int, default=0,
                     help="profiling aid: build only this many layers of the shape (the line is then not a bench result)")
     a = ap.parse_args()
@@ -192,10 +195,12 @@ def main():
         L = a.layers
     version = 6 if a.shape.startswith("v6") else 4
     ck = synth.make_checkpoint(version, L, D, Fn, V, seed=1002, device=dev)
-    model = RWKV(ck, f"cuda:{local_rank} fp16i8", verbose=False)
+    sharded = a.shard and world > 1
+    model = RWKV(ck, f"cuda:{local_rank} fp16i8", verbose=False,
+                 shard_rank=rank if sharded else 0, shard_world=world if sharded else 1)
     del ck
     torch.cuda.empty_cache()
-    prompt = synth.make_tokens(a.prompt, V, 2000 + rank)
+    prompt = synth.make_tokens(a.prompt, V, 2000 + (0 if sharded else rank))
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -259,7 +264,7 @@ def main():
     # ---- roofline of the dominant kernel (rank 0): each GEMV launch of a token, event-timed
     roof = None
     if rank == 0:
-        roof = gemv_roofline(model, dev)
+        roof = None if sharded else gemv_roofline(model, dev)
     cb = None
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
         cb = cpu_arm(steps=6, warmup=1, budget_s=25.0)
@@ -268,14 +273,16 @@ def main():
         n_mm = L * (7 if version == 4 else 8)
         launches_per_token = 2 if model._use_chain else L * 4 + 1
         line = {
-            "metric": METRIC, "value": world * a.steps / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+            "metric": METRIC, "value": (1 if sharded else world) * a.steps / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": dev_ms / a.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"rwkv{version}-7b-shape (L={L}, D={D}, ffn={Fn}, vocab={V}) 'cuda fp16i8', batch 1 per "
+            "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"parallelism": ("one model column-sharded over %d GPUs, all-gather after each matmul" % world) if sharded
+                                      else "independent streams, one per GPU, no collective",
+                       "workload": f"rwkv{a.shape} shape (L={L}, D={D}, ffn={Fn}, vocab={V}) 'cuda fp16i8', batch 1 per "
                                    f"GPU: {a.prompt}-token prefill then greedy decode; one independent stream per GPU",
                        "l2": "inputs larger than L2 (7.19 GB of packed weights streamed per step)",
                        "mm8_matmuls_per_token": n_mm + 1},
-            "e2e": {"value": world * a.steps / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 8,
+            "e2e": {"value": (1 if sharded else world) * a.steps / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 8,
                     "d2h_bytes_per_step": V * 4},
             "gpu_launches": launches_per_token * a.steps * 2,
             "prefill": {"tokens": a.prompt, "ms": prefill_ms, "tokens_per_s": a.prompt / (prefill_ms / 1e3)},

@@ -208,7 +208,9 @@ class RWKV:
                         raise ValueError(f"{x}: {w[x].shape[1]} columns are too few for {self._world} ranks")
                     w[x], w[x + "_mx"], w[x + "_rx"] = shard.column_shard(w[x], w[x + "_mx"], w[x + "_rx"],
                                                                          self._world, self._rank)
-                self._use_graph = False      # collectives between the launches: direct launches
+                # collectives between the launches: direct launches (capturing the NCCL all-gathers of a
+                # step into a CUDA graph did not return on the B200 pool; it is not attempted)
+                self._use_graph = False
                 torch.cuda.empty_cache()
             self._init_buffers()
         gc.collect()
@@ -431,7 +433,10 @@ class RWKV:
 
         def gather(pairs):
             for full, local in pairs:
-                full.copy_(shard.gather_columns(local, full.numel(), G))
+                if local.numel() * G == full.numel():        # even split: gather straight into place
+                    torch.distributed.all_gather_into_tensor(full, local)
+                else:
+                    full.copy_(shard.gather_columns(local, full.numel(), G))
 
         def run(problems):
             problems = [p for p in problems if p.M > 0]
