@@ -181,3 +181,58 @@ def test_config0_shape_greedy_vs_oracle():
     assert worst < TOL, worst
     assert forced_ok
     print(f"config0: max|dlogit|={worst:.2e}, min top-2 margin={min(margins):.2e}")
+
+
+def _golden_converted():
+    import os
+    return os.path.join(os.path.dirname(__file__), "golden", "ref_converted_v4.pth")
+
+
+def test_loads_checkpoint_converted_by_the_reference():
+    """A file the reference's loader converted for 'cuda fp16i8' loads here; its packed matrices are
+    the ones this runtime packs from the raw checkpoint, and the logits agree with the raw load."""
+    from chatrwkv_b200.model import RWKV
+    conv = RWKV(_golden_converted(), "cuda fp16i8", verbose=False)
+    raw, oracle = _models("v4")
+    for key, t in raw.w.items():
+        if torch.is_tensor(t) and t.dtype == torch.uint8:
+            assert torch.equal(conv.w[key], t), key
+            for s in ("_mx", "_rx", "_my", "_ry"):
+                assert torch.equal(conv.w[key + s].view(torch.int16), raw.w[key + s].view(torch.int16)), key + s
+    a, sa = conv.forward(TOKENS, None, full_output=True)
+    b, sb = raw.forward(TOKENS, None, full_output=True)
+    c, _ = oracle.forward(TOKENS, None, full_output=True)
+    assert (a - b).abs().max().item() < 5e-3          # emb differs by at most an fp16 ulp (CPU vs GPU LayerNorm)
+    assert (a.cpu() - c).abs().max().item() < TOL
+    o1, sa = conv.forward([TOKENS[0]], sa)
+    o2, sb = raw.forward([TOKENS[0]], sb)
+    assert (o1 - o2).abs().max().item() < 5e-3
+
+
+def test_convert_and_save_round_trip(tmp_path):
+    from chatrwkv_b200.model import RWKV
+    ck = synth.make_checkpoint(**TOY["v4"])
+    rawp = str(tmp_path / "raw.pth")
+    torch.save(ck, rawp)
+    out = str(tmp_path / "conv")
+    with pytest.raises(SystemExit):
+        RWKV(rawp, "cuda fp16i8", verbose=False, convert_and_save_and_exit=out)
+    saved = torch.load(out + ".pth", map_location="cpu")
+    ref = torch.load(_golden_converted(), map_location="cpu")
+    assert set(saved.keys()) == set(ref.keys())
+    for k, v in ref.items():
+        if not torch.is_tensor(v):
+            assert saved[k] == v, k
+        elif v.dtype == torch.uint8 or k.endswith(("_mx", "_rx", "_my", "_ry")):
+            assert saved[k].dtype == v.dtype and saved[k].shape == v.shape, k
+            assert torch.equal(saved[k].contiguous().view(torch.uint8), v.contiguous().view(torch.uint8)), k
+        else:
+            assert saved[k].dtype == v.dtype and saved[k].shape == v.shape, k
+            assert (saved[k].float() - v.float()).abs().max().item() <= 4e-3, k
+    a = RWKV(out, "cuda fp16i8", verbose=False)
+    b = RWKV(rawp, "cuda fp16i8", verbose=False)
+    la, _ = a.forward(TOKENS, None)
+    lb, _ = b.forward(TOKENS, None)
+    assert torch.equal(la, lb)
+    with pytest.raises(AssertionError):                 # the strategy recorded in the file must match
+        RWKV(out, "cuda:0 fp16i8", verbose=False)

@@ -79,3 +79,28 @@ def test_fp16_path_tracks_fp32_path():
         la, _ = a.forward(TOKENS, None)
         lb, _ = b.forward(TOKENS, None)
         assert (la - lb).abs().max() < 2e-2
+
+
+def test_reference_converted_checkpoint_matches_oracle_packing():
+    """Every packed matrix (and its four scale vectors) in the checkpoint the reference's own loader
+    converted for 'cuda fp16i8' equals the oracle's packing of the raw checkpoint, bit for bit."""
+    import os
+    path = os.path.join(os.path.dirname(__file__), "golden", "ref_converted_v4.pth")
+    conv = torch.load(path, map_location="cpu")
+    assert conv["_strategy"] == "cuda fp16i8" and conv["_rescale_layer"] == 6
+    ck = synth.make_checkpoint(**TOY["v4"])
+    n = 0
+    for key, t in conv.items():
+        if not (torch.is_tensor(t) and t.dtype == torch.uint8):
+            continue
+        w = ck[key].float()
+        layer = int(key.split(".")[1]) if key.startswith("blocks.") else 0
+        if "att.output" in key or "ffn.value" in key:
+            w = w / (2 ** (layer // 6))
+        q, mx, rx, my, ry = orc.quantize_weight(w.t(), torch.float16)
+        assert torch.equal(q, t), key
+        for name, v in (("_mx", mx), ("_rx", rx), ("_my", my), ("_ry", ry)):
+            ref = conv[key + name]
+            assert v.shape == ref.shape and torch.equal(v.view(torch.int16), ref.view(torch.int16)), (key, name)
+        n += 1
+    assert n == 8 * 7 + 1
