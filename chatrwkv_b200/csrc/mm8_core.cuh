@@ -55,7 +55,32 @@ struct Batch {
     float* partial;
     float* sums;        // [panel ticket][kMaxSplit][4]
     unsigned* counters;
+    int trace_id;       // launch number for the optional timeline below
 };
+
+// Optional per-CTA timeline for tuning (compiled in only with -DRWKV_MM8_TRACE): eight words per
+// CTA per launch -- %globaltimer at entry, ring issued, predecessor done, prologue done, stream
+// done, split reduction reached, exit; then the SM id.
+#ifdef RWKV_MM8_TRACE
+__device__ unsigned long long* g_mm8_trace = nullptr;
+int g_mm8_trace_next = 0;       // host: launches so far
+__device__ __forceinline__ void mm8_stamp(unsigned long long* row, int slot) {
+    if (row != nullptr) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        if (slot == 7) { unsigned s; asm volatile("mov.u32 %0, %smid;" : "=r"(s)); t = s; }
+        row[slot] = t;
+    }
+}
+// the row pointer is fetched once, at entry: a stamp is then one posted store
+#define MM8_TRACE_BEGIN(launch, cta)                                                                   \
+    unsigned long long* mm8_tr = (threadIdx.x == 0 && g_mm8_trace != nullptr && (cta) < 1024)         \
+                                     ? g_mm8_trace + ((long long)(launch) * 1024 + (cta)) * 8 : nullptr
+#define MM8_STAMP(launch, cta, slot) mm8_stamp(mm8_tr, slot)
+#else
+#define MM8_TRACE_BEGIN(launch, cta) do { } while (0)
+#define MM8_STAMP(launch, cta, slot) do { } while (0)
+#endif
 
 // byte i of `word` -> fp32 (2^23 + byte), then minus (2^23 + 128): exact (byte - 128).
 __device__ __forceinline__ uint32_t code_bits(uint32_t word, int i) {

@@ -29,6 +29,7 @@
 // Prologues (what x is) and epilogues (what happens to y) fuse the pointwise neighbours of
 // the matmuls in att_one / ffn_one (pkg/model.py:984-992, 1034-1055).
 #include "mm8_core.cuh"
+#include "mm8_cluster.cuh"
 
 namespace {
 
@@ -78,7 +79,11 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_one_kernel(const __grid_const
 #pragma unroll
         for (int g = 0; g < kDepth; ++g) issue_group(g);
     }
+    const int cta_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    MM8_TRACE_BEGIN(b.trace_id, cta_id);
+    MM8_STAMP(b.trace_id, cta_id, 0);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    MM8_STAMP(b.trace_id, cta_id, 2);
 
     // ---- prologue: x for this CTA's rows, x' = x * ry, and this slice's scalar sums --------
     float mean = 0.f, rstd = 0.f;
@@ -130,6 +135,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_one_kernel(const __grid_const
     sx = warp_sum(sx); sxr = warp_sum(sxr); sxmy = warp_sum(sxmy);
     if (lane == 0) { ssum[warp][0] = sx; ssum[warp][1] = sxr; ssum[warp][2] = sxmy; }
     __syncthreads();
+    MM8_STAMP(b.trace_id, cta_id, 3);
 
     // ---- main loop ---------------------------------------------------------------------------
     float acc[16];
@@ -159,6 +165,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_one_kernel(const __grid_const
         }
     }
 
+    MM8_STAMP(b.trace_id, cta_id, 4);
     // ---- CTA reduce: (8 warps x RPW row groups) -> 1.  Element (lane % LPR, i) of row group rg
     // sits at position i*LPR + lane%LPR so that stores and loads are conflict free; position p
     // holds column (p % LPR) * 16 + p / LPR of the panel.
@@ -191,6 +198,8 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_one_kernel(const __grid_const
     __syncthreads();
     if (tid == 0) s_ticket = atomicAdd(&b.counters[P.counter_off + panel], 1u);
     __syncthreads();
+    MM8_STAMP(b.trace_id, cta_id, 5);
+    MM8_STAMP(b.trace_id, cta_id, 7);
     if (s_ticket != unsigned(P.splits - 1)) return;
     __threadfence();
     if (tid == 0) b.counters[P.counter_off + panel] = 0u;   // ready for the next call
@@ -243,6 +252,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_one_kernel(const __grid_const
             store_epilogue<F>(P, k, val);
         }
     }
+    MM8_STAMP(b.trace_id, cta_id, 6);
 }
 
 int g_split_override = 0;
@@ -275,6 +285,12 @@ extern "C" int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, i
     if (rc != RWKV_OK) return rc;
     const int pw = plan.pw;
     const bool aligned = plan.aligned, packed = (g_variant & 4) == 0;
+    if (aligned && force_pw == 0 && g_split_override == 0) {
+        // K-splits of a panel as one thread-block cluster (mm8_cluster.cuh); falls through to the
+        // ticket kernel when the batch is not eligible.
+        const int crc = mm8_cluster_launch(plan.b, count, dtype, packed, static_cast<cudaStream_t>(stream));
+        if (crc != RWKV_ERR_UNSUPPORTED) return crc;
+    }
     void (*kern)(Batch) = nullptr;
 #define RWKV_PICK(FT)                                                                                        \
     if (!aligned) kern = pw == 512 ? mm8_one_kernel<FT, 32, false, false, 4>                                \
@@ -293,6 +309,10 @@ extern "C" int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, i
         cudaGetLastError();
         return RWKV_ERR_LAUNCH;
     }
+    plan.b.trace_id = 0;
+#ifdef RWKV_MM8_TRACE
+    plan.b.trace_id = g_mm8_trace_next++;
+#endif
     return rwkv_launch_pdl(kern, dim3(plan.gx, plan.gy, plan.gz), dim3(kThreads), size_t(smem),
                            static_cast<cudaStream_t>(stream), plan.b);
 }

@@ -483,7 +483,9 @@ class RWKV:
                 self._head_launch[cur] = self._launches_v4(cur)[-1]
             self._gemv(self._head_launch[cur])
         else:
-            for probs in self._launches_v4(cur):
+            if not hasattr(self, "_launch_cache"):
+                self._launch_cache = [self._launches_v4(0), self._launches_v4(1)]   # fixed buffers: built once
+            for probs in self._launch_cache[cur]:
                 self._gemv(probs)
 
     def chain_error(self):

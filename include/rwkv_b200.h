@@ -194,6 +194,14 @@ int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, int dtype,
  * columns, 0 = automatic); bit 2 switches the two-wide fp32 arithmetic off. */
 void rwkv_mm8_one_set_split(int split);
 void rwkv_mm8_one_set_variant(int variant);
+/* How the K-splits of a column panel meet.  By default (cluster_size 0) the splits of a panel
+ * are one thread-block cluster of up to 8 CTAs that adds its partial sums through distributed
+ * shared memory; matrices that kernel cannot take (unaligned rows, more than 16384 in-features)
+ * use global scratch and an atomic ticket.  cluster_size -1 forces the ticket kernel, 1/2/4/8
+ * force a cluster size; panel_width forces the panel width in columns (0 = automatic).  Forcing
+ * a split or a width with the two hooks above also selects the ticket kernel.  No counterpart in
+ * the reference. */
+void rwkv_mm8_one_set_cluster(int cluster_size, int panel_width);
 
 
 /* ---------------------------------------------------------------------------------------

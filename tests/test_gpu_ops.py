@@ -87,6 +87,30 @@ def test_mm8_one_matches_oracle(ops, N, M):
     assert mism < 0.05, mism
 
 
+@pytest.mark.parametrize("cluster,width", [(-1, 0), (1, 0), (2, 48), (4, 0), (8, 0), (8, 112), (8, 4096), (0, 16)])
+@pytest.mark.parametrize("N,M", [(4096, 4096), (768, 50277), (1000, 48), (16384, 1024), (3072, 768)])
+def test_mm8_one_split_reductions_agree(ops, N, M, cluster, width):
+    """The cluster kernel (every cluster size, odd panel widths) and the ticket kernel give the
+    oracle's result; a forced configuration is bit-reproducible."""
+    from chatrwkv_b200._lib import lib
+    from tests.util import packed_case
+    cpu, dev = packed_case(N, M, seed=N + 7 * M)
+    g = torch.Generator().manual_seed(3000 + N)
+    x = torch.randn(N, generator=g).half()
+    ref = orc.mm8_kernel(x, *cpu)
+    lib().rwkv_mm8_one_set_cluster(cluster, width)
+    try:
+        y = torch.zeros(M, dtype=torch.float32, device="cuda")
+        torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y)
+        y2 = torch.zeros(M, dtype=torch.float32, device="cuda")
+        torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y2)
+        torch.cuda.synchronize()
+    finally:
+        lib().rwkv_mm8_one_set_cluster(0, 0)
+    assert (y.cpu() - ref).abs().max().item() <= 2e-5 * max(ref.abs().max().item(), 1.0)
+    assert torch.equal(y, y2)
+
+
 def test_mm8_one_one_signed_input(ops):
     """x >= 0 (the FFN value matmul sees relu(k)^2): centred codes keep the error small."""
     from tests.util import packed_case
