@@ -328,7 +328,7 @@ def gemv_roofline(model, dev, reps=30):
         traffic = t["dram_bytes_per_algorithmic_byte"] * tot_b / n_launch
     except Exception:
         pass
-    return {"bound": "hbm", "kernel": "mm8_chain_kernel" if chain else "mm8_one_kernel", "achieved": achieved,
+    return {"bound": "hbm", "kernel": "mm8_chain_kernel" if chain else "mm8_cluster_kernel", "achieved": achieved,
             "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": how, "traffic": traffic,
             "launches_per_step": n_launch, "avg_launch_us": ms / n_launch * 1e3,
             "algorithmic_bytes_per_launch": tot_b / n_launch, "frac_of_8000": achieved / 8000.0,
