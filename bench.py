@@ -271,7 +271,7 @@ def main():
 
     if rank == 0:
         n_mm = L * (7 if version == 4 else 8)
-        launches_per_token = 2 if model._use_chain else L * 4 + 1
+        launches_per_token = 2 if model._use_chain else L * (4 if version == 4 else 9) + 1
         line = {
             "metric": METRIC, "value": (1 if sharded else world) * a.steps / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": dev_ms / a.steps, "higher_is_better": True,
@@ -280,7 +280,8 @@ def main():
                                       else "independent streams, one per GPU, no collective",
                        "workload": f"rwkv{a.shape} shape (L={L}, D={D}, ffn={Fn}, vocab={V}) 'cuda fp16i8', batch 1 per "
                                    f"GPU: {a.prompt}-token prefill then greedy decode; one independent stream per GPU",
-                       "l2": "inputs larger than L2 (7.19 GB of packed weights streamed per step)",
+                       "l2": "inputs larger than L2 (%.2f GB of packed weights streamed per step)" % (
+                           sum(t.numel() for t in model.w.values() if torch.is_tensor(t) and t.dtype == torch.uint8) / 1e9),
                        "mm8_matmuls_per_token": n_mm + 1},
             "e2e": {"value": (1 if sharded else world) * a.steps / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 8,
                     "d2h_bytes_per_step": V * 4},
@@ -302,20 +303,23 @@ def gemv_roofline(model, dev, reps=30):
     4M (mx, rx) + the output vector, summed over every matmul of the token."""
     import torch
     peak, how = measured_peaks()
-    launches = model._launches_v4(model._cur)
-    tot_b = 0
-    for probs in launches:
-        for p in probs:
-            out_b = 4 if p.epilogue in (0, 6) else 2
-            tot_b += p.N * p.M + 6 * p.N + 4 * p.M + out_b * p.M
+    v4 = model.version == 4
+    tot_b, n_mm8 = 0, 0
+    for name, t in model.w.items():         # every packed matrix is read once per token
+        if torch.is_tensor(t) and t.dtype == torch.uint8:
+            N, M = t.shape
+            tot_b += N * M + 6 * N + 4 * M + (4 if name == "head.weight" else 2) * M
+            n_mm8 += 1
+    launches = model._launches_v4(model._cur) if v4 else [None] * (model.args.n_layer * 4 + 1)
+    step_fn = model._step_one_v4 if v4 else model._step_one_v56
     chain = bool(model._use_chain)
     for _ in range(3):
-        model._step_one_v4(model._cur)          # reads the current state set, writes the other one
+        step_fn(model._cur)                     # reads the current state set, writes the other one
     torch.cuda.synchronize(dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(reps):
-        model._step_one_v4(model._cur)
+        step_fn(model._cur)
     e1.record()
     torch.cuda.synchronize(dev)
     ms = e0.elapsed_time(e1) / reps

@@ -1,0 +1,322 @@
+// One-token pieces of the RWKV-5.2 / RWKV-6 attention block that are not matmuls over packed
+// weights (att_one_v5_1 / att_one_v6_0, pkg/model.py:1157-1181, 1263-1298):
+//   * the RWKV-6 data-dependent token shift: LayerNorm, xxx = xx + (sx - xx) * x_maa,
+//     tanh(xxx @ tm_w1) (x) tm_w2 -> five mix offsets -> wx, kx, vx, rx, gx      (model.py:1264-1276)
+//   * the RWKV-6 decay: w = exp(-exp(time_decay + tanh(wx @ td_w1) @ td_w2))     (model.py:1286-1287)
+//   * the one-step WKV of v5/v6 on the [H, N, N] state, group-norm and the gate  (model.py:1289-1296)
+// The two low-rank products share one pair of kernels: "lora_a" (a [D] vector times a [D, R]
+// matrix, split over row slabs into fp32 partials) and "lora_b" (sum of the partials, tanh, the
+// grouped [R/G] x [D] second factor and the pointwise tail).  Every fp16 torch op of the
+// reference rounds once; r16() marks those places.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kT = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* sh8) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh8[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < int(blockDim.x >> 5); ++i) t += sh8[i];
+    return t;
+}
+
+// Programmatic dependent launch: let the successor be scheduled, pull what does not depend on the
+// predecessor toward L2, then wait for the predecessor.
+__device__ __forceinline__ void pdl_open() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void l2_line(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+struct LoraA {
+    int mode;               // 0: token shift from the residual stream; 1: the vector is given
+    int D, R, slab;         // in-features, out-features, rows per CTA
+    const __half* x;        // mode 0: residual stream [D]; mode 1: input vector [D]
+    const __half* ln_w;     // mode 0
+    const __half* ln_b;
+    const __half* state;    // mode 0: previous token's LayerNorm output
+    __half* new_state;      // mode 0: receives this token's LayerNorm output (may alias state)
+    const __half* maa_x;    // mode 0
+    const __half* w1;       // [D, R]
+    float* partial;         // [slabs][R]
+    __half* xx_out;         // mode 0: LayerNorm output [D]
+    __half* d_out;          // mode 0: sx - xx [D]
+};
+
+// grid = slabs, block = 256.  Needs D % 8 == 0 and D <= 8192 in mode 0 (the vector lives in registers).
+__global__ void __launch_bounds__(kT) lora_a_kernel(const LoraA a) {
+    extern __shared__ float smem[];             // vin[slab] | part[nrs][R]
+    __shared__ float sh8[kT / 32];
+    float* vin = smem;
+    float* part = smem + a.slab;
+    const int tid = threadIdx.x;
+    const int j0 = blockIdx.x * a.slab;
+    const int nrows = min(a.slab, a.D - j0);
+    pdl_open();
+    {   // this CTA's rows of w1: nrows * R halfs, contiguous
+        const char* base = reinterpret_cast<const char*>(a.w1 + (long long)j0 * a.R);
+        const long long bytes = (long long)nrows * a.R * 2;
+        for (long long o = (long long)tid * 128; o < bytes; o += (long long)kT * 128) l2_line(base + o);
+    }
+    pdl_wait();
+    if (a.mode == 0) {
+        uint4 xv4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int j8 = (tid + i * kT) * 8;
+            xv4[i] = j8 < a.D ? __ldcg(reinterpret_cast<const uint4*>(a.x) + (j8 >> 3)) : make_uint4(0, 0, 0, 0);
+        }
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2* h = reinterpret_cast<const __half2*>(&xv4[i]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h[e]); s += f.x + f.y; }
+        }
+        const float mean = block_sum(s, sh8) / float(a.D);
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if ((tid + i * kT) * 8 < a.D) {
+                const __half2* h = reinterpret_cast<const __half2*>(&xv4[i]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(h[e]);
+                    q = fmaf(f.x - mean, f.x - mean, q);
+                    q = fmaf(f.y - mean, f.y - mean, q);
+                }
+            }
+        }
+        const float rstd = rsqrtf(block_sum(q, sh8) / float(a.D) + 1e-5f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int j8 = (tid + i * kT) * 8;
+            const __half* hx = reinterpret_cast<const __half*>(&xv4[i]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int j = j8 + e;
+                if (j >= j0 && j < j0 + nrows) {
+                    const float xx = r16((__half2float(hx[e]) - mean) * rstd * __half2float(a.ln_w[j]) + __half2float(a.ln_b[j]));
+                    const float dd = r16(__half2float(__ldcg(a.state + j)) - xx);
+                    vin[j - j0] = r16(xx + r16(dd * __half2float(a.maa_x[j])));
+                    a.xx_out[j] = __float2half_rn(xx);
+                    a.d_out[j] = __float2half_rn(dd);
+                    a.new_state[j] = __float2half_rn(xx);
+                }
+            }
+        }
+    } else {
+        for (int l = tid; l < nrows; l += kT) vin[l] = __half2float(__ldcg(a.x + j0 + l));
+    }
+    __syncthreads();
+    const int cpp = min(a.R, kT);               // columns per pass
+    const int nrs = kT / cpp;                   // row splits
+    const int c0 = tid % cpp, rs = tid / cpp;
+    if (rs < nrs) {
+        for (int c = c0; c < a.R; c += cpp) {
+            float acc = 0.f;
+            const __half* wp = a.w1 + (long long)(j0 + rs) * a.R + c;
+#pragma unroll 16
+            for (int l = rs; l < nrows; l += nrs, wp += (long long)nrs * a.R) acc = fmaf(vin[l], __half2float(*wp), acc);
+            part[rs * a.R + c] = acc;
+        }
+    }
+    __syncthreads();
+    for (int c = tid; c < a.R; c += kT) {
+        float s = 0.f;
+        for (int q = 0; q < nrs; ++q) s += part[q * a.R + c];
+        a.partial[(long long)blockIdx.x * a.R + c] = s;
+    }
+}
+
+struct LoraB {
+    int mode;               // 0: five token-shift mixes; 1: decay
+    int D, R, G, slabs;     // G groups of R/G hidden units each
+    const float* partial;   // [slabs][R]
+    const __half* w2;       // [G][R/G][D]
+    const __half* xx;       // mode 0 [D]
+    const __half* dd;       // mode 0 [D]
+    const __half* maa[5];   // mode 0: w, k, v, r, g
+    __half* out[5];         // mode 0: wx, kx, vx, rx, gx
+    const float* decay;     // mode 1 [D]
+    float* w_out;           // mode 1 [D]: exp(-exp(decay + lora))
+};
+
+// grid = ceil(D / 32), block = 256; dynamic shared memory (R + 8 * G * 32) floats.  A CTA owns 32
+// columns d; thread (slice = tid / 32, col = tid % 32) multiplies the hidden units l = slice,
+// slice + 8, ... of every group into its column (all loads independent: one trip to memory), the
+// eight slices are added in order, and G * 32 threads finish.
+__global__ void __launch_bounds__(kT) lora_b_kernel(const LoraB b) {
+    extern __shared__ float h[];                // h[R] | acc[8][G][32]
+    float* accs = h + b.R;
+    const int tid = threadIdx.x;
+    pdl_open();
+    for (int row = tid; row < b.R; row += kT)   // this CTA's 64-byte piece of every row of w2
+        if (blockIdx.x * 32 < b.D) l2_line(b.w2 + (long long)row * b.D + blockIdx.x * 32);
+    pdl_wait();
+    for (int c = tid; c < b.R; c += kT) {
+        float s = 0.f;
+#pragma unroll 8
+        for (int p = 0; p < b.slabs; ++p) s += __ldcg(b.partial + (long long)p * b.R + c);
+        h[c] = r16(tanhf(r16(s)));
+    }
+    __syncthreads();
+    const int col = tid & 31, slice = tid >> 5;
+    const int d = blockIdx.x * 32 + col;
+    const int L = b.R / b.G;
+    for (int f = 0; f < b.G; ++f) {
+        float acc = 0.f;
+        if (d < b.D) {
+            const __half* wp = b.w2 + ((long long)f * L + slice) * b.D + d;
+#pragma unroll 8
+            for (int l = slice; l < L; l += 8, wp += 8LL * b.D) acc = fmaf(h[f * L + l], __half2float(*wp), acc);
+        }
+        accs[(slice * b.G + f) * 32 + col] = acc;
+    }
+    __syncthreads();
+    for (int t = tid; t < b.G * 32; t += kT) {
+        const int f = t >> 5, c = t & 31, dd_i = blockIdx.x * 32 + c;
+        if (dd_i >= b.D) continue;
+        float acc = 0.f;
+#pragma unroll
+        for (int sl = 0; sl < 8; ++sl) acc += accs[(sl * b.G + f) * 32 + c];
+        const float m = r16(acc);
+        if (b.mode == 0) {
+            const float xx = __half2float(__ldcg(b.xx + dd_i)), dd = __half2float(__ldcg(b.dd + dd_i));
+            b.out[f][dd_i] = __float2half_rn(r16(xx + r16(dd * r16(__half2float(b.maa[f][dd_i]) + m))));
+        } else {
+            b.w_out[dd_i] = expf(-expf(b.decay[dd_i] + m));
+        }
+    }
+}
+
+// One-step WKV of RWKV-5.2 / RWKV-6 for one token, then group-norm (eps 64e-5) and the gate.
+// State in the model's layout [H, key j, value i] (pkg/model.py:1461-1471).  grid = H, block = 256:
+// thread (q, i) covers the keys j = q, q + TPI, ... of value index i (TPI = 256 / N threads per i).
+__global__ void __launch_bounds__(kT) wkv56_one_kernel(int N, const __half* __restrict__ r, const __half* __restrict__ k,
+                                                      const __half* __restrict__ v, const float* __restrict__ w,
+                                                      const float* __restrict__ u, const float* s_in, float* s_out,
+                                                      const float* __restrict__ lnx_w, const float* __restrict__ lnx_b,
+                                                      const __half* __restrict__ g, __half* __restrict__ out) {
+    extern __shared__ float sm[];               // rr[N] kk[N] ww[N] uu[N] | acc[TPI][N]
+    __shared__ float sh8[kT / 32];
+    float* rr = sm; float* kk = sm + N; float* ww = sm + 2 * N; float* uu = sm + 3 * N; float* accs = sm + 4 * N;
+    const int hh = blockIdx.x, tid = threadIdx.x, c0 = hh * N;
+    pdl_open();
+    {   // the head's state (written a token ago)
+        const char* base = reinterpret_cast<const char*>(s_in + (long long)hh * N * N);
+        for (long long o = (long long)tid * 128; o < (long long)N * N * 4; o += (long long)kT * 128) l2_line(base + o);
+    }
+    pdl_wait();
+    for (int j = tid; j < N; j += kT) {
+        rr[j] = __half2float(__ldcg(r + c0 + j));
+        kk[j] = __half2float(__ldcg(k + c0 + j));
+        ww[j] = __ldcg(w + c0 + j);
+        uu[j] = u[c0 + j];
+    }
+    __syncthreads();
+    const int TPI = max(1, kT / N);
+    const int i = tid % N, q = tid / N;
+    float acc = 0.f;
+    if (q < TPI && tid < TPI * N) {
+        const float vi = __half2float(__ldcg(v + c0 + i));
+        const float* si = s_in + (long long)hh * N * N + i;
+        float* so = s_out + (long long)hh * N * N + i;
+#pragma unroll 16
+        for (int j = q; j < N; j += TPI) {
+            const float sv = __ldcg(si + (long long)j * N);
+            const float a = kk[j] * vi;
+            acc = fmaf(rr[j], fmaf(uu[j], a, sv), acc);
+            so[(long long)j * N] = fmaf(ww[j], sv, a);
+        }
+        accs[q * N + i] = acc;
+    }
+    __syncthreads();
+    // y[i] for i = tid < N; then the statistics of the head's N values
+    float y = 0.f;
+    if (tid < N) for (int t = 0; t < TPI; ++t) y += accs[t * N + tid];
+    const float mean = block_sum(tid < N ? y : 0.f, sh8) / float(N);
+    const float dv = tid < N ? y - mean : 0.f;
+    const float var = block_sum(dv * dv, sh8) / float(N);
+    if (tid < N) {
+        const int c = c0 + tid;
+        const float o = dv * rsqrtf(var + 64e-5f) * lnx_w[c] + lnx_b[c];
+        out[c] = __float2half_rn(r16(r16(o) * __half2float(__ldcg(g + c))));
+    }
+}
+
+}  // namespace
+
+static inline int lora_slab(int64_t D) { return D >= 2048 ? 64 : 32; }
+
+extern "C" size_t rwkv_v6_scratch_bytes(int64_t D, int64_t rank) {
+    if (D < 1 || rank < 1) return 0;
+    const int slab = lora_slab(D);
+    return size_t((D + slab - 1) / slab) * size_t(rank) * sizeof(float);
+}
+
+extern "C" int rwkv_v6_token_shift(int64_t D, int64_t Lm, const void* x, const void* state, void* new_state,
+                                   const void* ln_w, const void* ln_b,
+                                   const void* maa_x, const void* const* maa5, const void* tm_w1, const void* tm_w2,
+                                   float* scratch, size_t scratch_bytes, void* xx_out, void* d_out, void* const* out5,
+                                   void* stream) {
+    RWKV_CHECK_ARG(D >= 8 && D % 8 == 0 && D <= 8 * 4 * kT && Lm >= 1 && 5 * Lm <= 4096);
+    RWKV_CHECK_ARG(x && state && new_state && ln_w && ln_b && maa_x && maa5 && tm_w1 && tm_w2 && scratch && xx_out && d_out && out5);
+    RWKV_CHECK_ALIGN(x, 16);
+    const int R = int(5 * Lm);
+    const int slab = lora_slab(D);
+    const int slabs = int((D + slab - 1) / slab);
+    if (scratch_bytes < size_t(slabs) * R * sizeof(float)) return RWKV_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LoraA a = {};
+    a.mode = 0; a.D = int(D); a.R = R; a.slab = slab;
+    a.x = static_cast<const __half*>(x); a.ln_w = static_cast<const __half*>(ln_w); a.ln_b = static_cast<const __half*>(ln_b);
+    a.state = static_cast<const __half*>(state); a.new_state = static_cast<__half*>(new_state); a.maa_x = static_cast<const __half*>(maa_x);
+    a.w1 = static_cast<const __half*>(tm_w1); a.partial = scratch;
+    a.xx_out = static_cast<__half*>(xx_out); a.d_out = static_cast<__half*>(d_out);
+    const int nrs = kT / (R < kT ? R : kT);
+    if (int rc = rwkv_launch_pdl(lora_a_kernel, dim3(slabs), dim3(kT), (slab + nrs * R) * sizeof(float), st, a)) return rc;
+    LoraB b = {};
+    b.mode = 0; b.D = int(D); b.R = R; b.G = 5; b.slabs = slabs; b.partial = scratch;
+    b.w2 = static_cast<const __half*>(tm_w2); b.xx = a.xx_out; b.dd = a.d_out;
+    for (int f = 0; f < 5; ++f) {
+        RWKV_CHECK_ARG(maa5[f] && out5[f]);
+        b.maa[f] = static_cast<const __half*>(maa5[f]);
+        b.out[f] = static_cast<__half*>(out5[f]);
+    }
+    return rwkv_launch_pdl(lora_b_kernel, dim3(int((D + 31) / 32)), dim3(kT), (R + 8 * b.G * 32) * sizeof(float), st, b);
+}
+
+extern "C" int rwkv_v6_decay(int64_t D, int64_t Ld, const void* wx, const void* td_w1, const void* td_w2,
+                             const float* time_decay, float* scratch, size_t scratch_bytes, float* w_out, void* stream) {
+    RWKV_CHECK_ARG(D >= 1 && Ld >= 1 && Ld <= 4096);
+    RWKV_CHECK_ARG(wx && td_w1 && td_w2 && time_decay && scratch && w_out);
+    const int R = int(Ld);
+    const int slab = lora_slab(D);
+    const int slabs = int((D + slab - 1) / slab);
+    if (scratch_bytes < size_t(slabs) * R * sizeof(float)) return RWKV_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LoraA a = {};
+    a.mode = 1; a.D = int(D); a.R = R; a.slab = slab;
+    a.x = static_cast<const __half*>(wx); a.w1 = static_cast<const __half*>(td_w1); a.partial = scratch;
+    const int nrs = kT / (R < kT ? R : kT);
+    if (int rc = rwkv_launch_pdl(lora_a_kernel, dim3(slabs), dim3(kT), (slab + nrs * R) * sizeof(float), st, a)) return rc;
+    LoraB b = {};
+    b.mode = 1; b.D = int(D); b.R = R; b.G = 1; b.slabs = slabs; b.partial = scratch;
+    b.w2 = static_cast<const __half*>(td_w2); b.decay = time_decay; b.w_out = w_out;
+    return rwkv_launch_pdl(lora_b_kernel, dim3(int((D + 31) / 32)), dim3(kT), (R + 8 * b.G * 32) * sizeof(float), st, b);
+}
+
+extern "C" int rwkv_wkv56_one(int64_t H, int64_t N, const void* r, const void* k, const void* v, const float* w,
+                              const float* u, const float* state, float* new_state, const float* lnx_w,
+                              const float* lnx_b, const void* g, void* out, void* stream) {
+    RWKV_CHECK_ARG(H >= 1 && H <= 65535 && N >= 1 && N <= kT);
+    RWKV_CHECK_ARG(r && k && v && w && u && state && new_state && lnx_w && lnx_b && g && out);
+    const int TPI = kT / int(N) > 0 ? kT / int(N) : 1;
+    return rwkv_launch_pdl(wkv56_one_kernel, dim3(int(H)), dim3(kT), (4 * N + TPI * N) * sizeof(float),
+                           static_cast<cudaStream_t>(stream), int(N), static_cast<const __half*>(r),
+                           static_cast<const __half*>(k), static_cast<const __half*>(v), w, u, state, new_state, lnx_w, lnx_b,
+                           static_cast<const __half*>(g), static_cast<__half*>(out));
+}

@@ -14,7 +14,7 @@ constexpr int kPanelMin = 128;
 constexpr int kCounterBytes = 4096;  // panel tickets; the last two words belong to the chain kernel
 constexpr int kMaxTickets = kCounterBytes / 4 - 2;
 constexpr int kSumsBytes = (kCounterBytes / 4) * kMaxSplit * 4 * sizeof(float);  // [panel ticket][split][4]
-constexpr int kMaxProblems = 3;
+constexpr int kMaxProblems = 4;
 constexpr int kGroup = 4;            // rows drained per step
 constexpr int ring_bytes(int depth) { return kGroup * depth * kThreads * 16; }   // 64 KB at depth 4
 
@@ -176,6 +176,11 @@ __device__ __forceinline__ void store_epilogue_with(const Problem& P, int k, flo
     case RWKV_EPI_STORE_F32:
         static_cast<float*>(P.y)[k] = to_f32<F>(from_f32<F>(val));
         break;
+    case RWKV_EPI_SILU: {
+        float v = to_f32<F>(from_f32<F>(val));
+        static_cast<F*>(P.y)[k] = from_f32<F>(v / (1.0f + expf(-v)));
+        break;
+    }
     default: break;
     }
 }
@@ -257,7 +262,7 @@ static inline size_t mm8_ws_bytes_for(const int32_t* Ms, int count) {
 }
 
 static inline size_t mm8_batch_ws_bytes(const rwkv_mm8_problem* problems, int count) {
-    int32_t Ms[kMaxProblems] = {0, 0, 0};
+    int32_t Ms[kMaxProblems] = {0, 0, 0, 0};
     for (int i = 0; i < count && i < kMaxProblems; ++i) Ms[i] = problems[i].M;
     return mm8_ws_bytes_for(Ms, count < kMaxProblems ? count : kMaxProblems);
 }
@@ -282,7 +287,7 @@ static inline int mm8_plan(const rwkv_mm8_problem* problems, int count, int dtyp
         const rwkv_mm8_problem& q = problems[i];
         RWKV_CHECK_ARG(q.N >= 1 && q.M >= 1 && q.w_stride >= q.M);
         RWKV_CHECK_ARG(q.x && q.w && q.mx && q.rx && q.my && q.ry && q.y);
-        RWKV_CHECK_ARG(q.epilogue >= RWKV_EPI_ACC_F32 && q.epilogue <= RWKV_EPI_STORE_F32);
+        RWKV_CHECK_ARG(q.epilogue >= RWKV_EPI_ACC_F32 && q.epilogue <= RWKV_EPI_SILU);
         if (q.epilogue == RWKV_EPI_RESIDUAL || q.epilogue == RWKV_EPI_MUL_RESIDUAL) RWKV_CHECK_ARG(q.aux != nullptr);
         if (q.epilogue == RWKV_EPI_MUL_RESIDUAL) RWKV_CHECK_ARG(q.aux2 != nullptr);
         RWKV_CHECK_ARG(q.prologue >= RWKV_PRO_PLAIN && q.prologue <= RWKV_PRO_WKV4);

@@ -27,7 +27,8 @@ import torch
 import torch.nn.functional as F
 
 from . import _lib, ops, shard
-from ._lib import (EPI_MUL_RESIDUAL, EPI_RELU_SQ, EPI_RESIDUAL, EPI_SIGMOID, EPI_STORE, EPI_STORE_F32, check, lib)
+from ._lib import (EPI_MUL_RESIDUAL, EPI_RELU_SQ, EPI_RESIDUAL, EPI_SIGMOID, EPI_SILU, EPI_STORE, EPI_STORE_F32, check,
+                   lib)
 
 STRATEGY_REGEX = r"^(?:(?:^|->) *(?:cuda(?::[\d]+)?|cpu|mps|dml) (?:fp(?:16|32)|bf16)(?:i8|i4|i3)?(?: \*[\d]+\+?)? *)+$"
 _MATRIX_KEYS = ("key.weight", "value.weight", "receptance.weight", "gate.weight", "output.weight", "head.weight")
@@ -115,8 +116,6 @@ class RWKV:
             prxxx(f"Model detected: v{self.version:.1f}")
             if self.version not in (4, 5.2, 6):
                 raise NotImplementedError(f"RWKV v{self.version}: this runtime implements v4, v5.2 and v6")
-            if self.version != 4:
-                self._use_graph = False     # the v5/v6 one-step path still allocates per call
 
             self.strategy = [types.SimpleNamespace(device=str(dev) if ":" in m.group(1) else "cuda",
                                                    atype=torch.float16, wtype=torch.uint8, stream=False)
@@ -234,7 +233,8 @@ class RWKV:
         h = lambda n: torch.zeros(n, dtype=torch.float16, device=dev)
         self._b = types.SimpleNamespace(
             x=h(D), m0=h(D), m1=h(D), m2=h(D), m3=h(D), m4=h(D), r=h(a.n_att), k=h(a.n_att), v=h(a.n_att),
-            g=h(a.n_att), att=h(a.n_att), fk=h(Fn), fr=h(D), xln=h(D),
+            g=h(a.n_att), att=h(a.n_att), fk=h(Fn), fr=h(D), xln=h(D), dd=h(D),
+            wdec=torch.zeros(a.n_att, dtype=torch.float32, device=dev),
             logits=torch.zeros(self._full_m.get("head.weight", self.w["head.weight"].shape[1]), dtype=torch.float32,
                                device=dev),
             tok=torch.zeros(1, dtype=torch.int64, device=dev))
@@ -340,8 +340,10 @@ class RWKV:
             slot = self._tok_slot = (self._tok_slot + 1) % self._tok_host.numel()
             self._tok_host[slot] = token
             self._b.tok.copy_(self._tok_host[slot:slot + 1], non_blocking=True)
-        fused = self.version == 4
-        step = (self._step_one_v4_sharded if self._world > 1 else self._step_one_v4) if fused else self._step_one_generic
+        if self.version == 4:
+            step = self._step_one_v4_sharded if self._world > 1 else self._step_one_v4
+        else:
+            step = self._step_one_v56
         cur = self._cur
         if not self._use_graph:
             step(cur)
@@ -368,8 +370,7 @@ class RWKV:
                 step(cur)
         else:
             self._graphs[cur].replay()
-        if fused:
-            self._cur = 1 - cur
+        self._cur = 1 - cur
         return self._b.logits.clone(), list(self._st[self._cur])
 
     def _launches_v4(self, cur):
@@ -497,38 +498,80 @@ class RWKV:
                                               C.byref(e)), "mm8_chain_take_error")
         return e.value
 
-    def _step_one_generic(self, cur):
-        """RWKV-5.2 / RWKV-6 token: the sequence-form blocks with T = 1 on the resident state."""
-        b, w, a = self._b, self.w, self.args
-        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
-        st = self._st[cur]
+    def _plan_v56(self, cur):
+        """The launches of one RWKV-5.2 / RWKV-6 token (att_one_v5_1 / att_one_v6_0, ffn_one / ffn_one_v6,
+        model.py:984-1016, 1157-1181, 1263-1298) as a list of zero-argument callables over fixed buffers;
+        reads state set `cur`, writes the other one.  Nothing in it allocates, so it can be captured."""
+        import ctypes as C
+        b, w, a, L = self._b, self.w, self.args, lib()
+        sin, sout = self._st[cur], self._st[1 - cur]
+        P, ln = self._problem, ops.with_ln_mix
+        D, H = a.n_embd, a.n_head
+        N = a.n_att // H
+        v6 = self.version == 6
+        dev = self.device
+        stream = lambda: torch.cuda.current_stream(dev).cuda_stream
+        ptrs = lambda ts: (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+        if v6 and not hasattr(self, "_lora_ws"):
+            rank = max(w["blocks.0.att.time_maa_w1"].shape[1], w["blocks.0.att.time_decay_w1"].shape[1])
+            self._lora_ws = torch.zeros(max(16, L.rwkv_v6_scratch_bytes(D, rank)), dtype=torch.uint8, device=dev)
+        plan, keep = [], []
+        gemv = lambda probs: plan.append(lambda probs=probs: self._gemv(probs))
         for i in range(a.n_layer):
-            bb, ffn = f"blocks.{i}.", f"blocks.{i}.ffn."
-            self._att_one_v56(i)
-            ffn_state = st[i * 3 + 2]
-            mixes = [w[ffn + "time_maa_k"], w[ffn + "time_maa_r"]] if self.version == 6 else \
-                    [w[ffn + "time_mix_k"], w[ffn + "time_mix_r"]]
-            mode = 1 if self.version == 6 else 0
-            self._ln_mix(1, b.x, ffn_state, w[bb + "ln2.weight"], w[bb + "ln2.bias"], mode, mixes,
-                         [b.m0, b.m1], new_state=ffn_state)
-            self._gemv([self._problem(b.m1, ffn + "receptance.weight", b.fr, EPI_SIGMOID),
-                        self._problem(b.m0, ffn + "key.weight", b.fk, EPI_RELU_SQ)])
+            bb, att, ffn = f"blocks.{i}.", f"blocks.{i}.att.", f"blocks.{i}.ffn."
+            ln1 = (w[bb + "ln1.weight"], w[bb + "ln1.bias"])
+            ln2 = (w[bb + "ln2.weight"], w[bb + "ln2.bias"])
+            s = i * 3
+            u = w[att + "time_first"].reshape(-1)
+            if v6:
+                Lm = w[att + "time_maa_w1"].shape[1] // 5
+                Ld = w[att + "time_decay_w1"].shape[1]
+                maa5 = ptrs([w[att + "time_maa_" + n] for n in "wkvrg"])
+                out5 = ptrs([b.m0, b.m1, b.m2, b.m3, b.m4])
+                keep += [maa5, out5]
+                ws = self._lora_ws
+                plan.append(lambda i=i, s=s, att=att, ln1=ln1, Lm=Lm, maa5=maa5, out5=out5, ws=ws: check(
+                    L.rwkv_v6_token_shift(D, Lm, b.x.data_ptr(), sin[s].data_ptr(), sout[s].data_ptr(), ln1[0].data_ptr(),
+                                          ln1[1].data_ptr(), w[att + "time_maa_x"].data_ptr(), maa5,
+                                          w[att + "time_maa_w1"].data_ptr(), w[att + "time_maa_w2"].data_ptr(),
+                                          ws.data_ptr(), ws.numel(), b.xln.data_ptr(), b.dd.data_ptr(), out5, stream()),
+                    "v6_token_shift"))
+                plan.append(lambda att=att, Ld=Ld, ws=ws: check(
+                    L.rwkv_v6_decay(D, Ld, b.m0.data_ptr(), w[att + "time_decay_w1"].data_ptr(),
+                                    w[att + "time_decay_w2"].data_ptr(), w[att + "time_decay"].data_ptr(), ws.data_ptr(),
+                                    ws.numel(), b.wdec.data_ptr(), stream()), "v6_decay"))
+                gemv([P(b.m3, att + "receptance.weight", b.r, EPI_STORE), P(b.m1, att + "key.weight", b.k, EPI_STORE),
+                      P(b.m2, att + "value.weight", b.v, EPI_STORE), P(b.m4, att + "gate.weight", b.g, EPI_SILU)])
+                decay = b.wdec
+            else:
+                mix = lambda n: w[att + "time_mix_" + n]
+                gemv([ln(P(b.x, att + "receptance.weight", b.r, EPI_STORE), *ln1, 0, sin[s], mix("r"), sout[s]),
+                      ln(P(b.x, att + "key.weight", b.k, EPI_STORE), *ln1, 0, sin[s], mix("k")),
+                      ln(P(b.x, att + "value.weight", b.v, EPI_STORE), *ln1, 0, sin[s], mix("v")),
+                      ln(P(b.x, att + "gate.weight", b.g, EPI_SILU), *ln1, 0, sin[s], mix("g"))])
+                decay = w[att + "time_decay"].reshape(-1)
+            plan.append(lambda s=s, att=att, decay=decay, u=u: check(
+                L.rwkv_wkv56_one(H, N, b.r.data_ptr(), b.k.data_ptr(), b.v.data_ptr(), decay.data_ptr(), u.data_ptr(),
+                                 sin[s + 1].data_ptr(), sout[s + 1].data_ptr(), w[att + "ln_x.weight"].data_ptr(),
+                                 w[att + "ln_x.bias"].data_ptr(), b.g.data_ptr(), b.att.data_ptr(), stream()), "wkv56_one"))
+            gemv([P(b.att, att + "output.weight", b.x, EPI_RESIDUAL, aux=b.x)])
+            mode = 1 if v6 else 0
+            mk, mr = (w[ffn + "time_maa_k"], w[ffn + "time_maa_r"]) if v6 else (w[ffn + "time_mix_k"], w[ffn + "time_mix_r"])
+            gemv([ln(P(b.x, ffn + "receptance.weight", b.fr, EPI_SIGMOID), *ln2, mode, sin[s + 2], mr, sout[s + 2]),
+                  ln(P(b.x, ffn + "key.weight", b.fk, EPI_RELU_SQ), *ln2, mode, sin[s + 2], mk)])
             scale = 0.5 if (self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0) else 1.0
-            self._gemv([self._problem(b.fk, ffn + "value.weight", b.x, EPI_MUL_RESIDUAL, aux=b.x, aux2=b.fr,
-                                      out_scale=scale)])
-        self._gemv([ops.with_ln_mix(self._problem(b.x, "head.weight", b.logits, EPI_STORE_F32),
-                                    w["ln_out.weight"], w["ln_out.bias"], 2)])
+            gemv([P(b.fk, ffn + "value.weight", b.x, EPI_MUL_RESIDUAL, aux=b.x, aux2=b.fr, out_scale=scale)])
+        gemv([ln(P(b.x, "head.weight", b.logits, EPI_STORE_F32), w["ln_out.weight"], w["ln_out.bias"], 2)])
+        self._plan_keep = getattr(self, "_plan_keep", []) + keep
+        return plan
 
-    def _att_one_v56(self, i):
-        """att_one_v5_1 / att_one_v6_0 (model.py:1157-1181, 1263-1298) on the resident state."""
-        b, w, a, st = self._b, self.w, self.args, self._gstate
-        x = b.x.view(1, -1)
-        xs = [st[i * 3 + 0], st[i * 3 + 1]]
-        out = self._att_seq_v56(x, xs, i)
-        b.x.copy_(out.view(-1))
-        st[i * 3 + 0].copy_(xs[0])
-        if xs[1] is not st[i * 3 + 1]:
-            st[i * 3 + 1].copy_(xs[1])
+    def _step_one_v56(self, cur):
+        b, w = self._b, self.w
+        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
+        if not hasattr(self, "_plans56"):
+            self._plans56 = [self._plan_v56(0), self._plan_v56(1)]
+        for op in self._plans56[cur]:
+            op()
 
     # ----- sequence ------------------------------------------------------------------------
     def _mm_seq(self, x, name, out_dtype=None):

@@ -109,7 +109,7 @@ int rwkv_mm8_one_static(int64_t N, int64_t M, const void* x, const uint8_t* w, i
                         float* y, void* stream);
 
 /* ---------------------------------------------------------------------------------------
- * mm8_one with a fused epilogue, up to three matrices per launch — the building block of
+ * mm8_one with a fused epilogue, up to four matrices per launch — the building block of
  * the fused decode steps that replace att_one / ffn_one (pkg/model.py:984-992, 1034-1055)
  * and their v5/v6 forms (pkg/model.py:1007-1016, 1157-1181, 1263-1298).  `val` below is the
  * fp32 sum of mm8_one; r16() is one rounding to `dtype`, which is where the reference
@@ -120,6 +120,7 @@ int rwkv_mm8_one_static(int64_t N, int64_t M, const void* x, const uint8_t* w, i
  *   RWKV_EPI_RELU_SQ       y[k] = relu(r16(val))^2                      (pkg/model.py:990)
  *   RWKV_EPI_RESIDUAL      y[k] = (aux[k] + r16(val)) * out_scale       (pkg/model.py:1055, 1660-1662)
  *   RWKV_EPI_MUL_RESIDUAL  y[k] = (aux[k] + aux2[k]*r16(val)) * out_scale  (pkg/model.py:991-992)
+ *   RWKV_EPI_SILU          y[k] = silu(r16(val))                        (the v5/v6 gate, pkg/model.py:1170, 1284)
  *   RWKV_EPI_STORE_F32     y fp32:  y[k] = r16(val)   (the head: fp16-rounded logits returned
  *                          as fp32, pkg/model.py:1675-1677)
  * Every intermediate is rounded to `dtype` like the torch ops it replaces; out_scale is 1
@@ -132,7 +133,8 @@ enum {
     RWKV_EPI_RELU_SQ = 3,
     RWKV_EPI_RESIDUAL = 4,
     RWKV_EPI_MUL_RESIDUAL = 5,
-    RWKV_EPI_STORE_F32 = 6
+    RWKV_EPI_STORE_F32 = 6,
+    RWKV_EPI_SILU = 7
 };
 
 /* Prologues: what the activation vector x of a problem is.
@@ -185,7 +187,7 @@ typedef struct rwkv_mm8_problem {
     float* pp_out;
 } rwkv_mm8_problem;
 
-/* `problems` is a HOST array of 1..3 entries, read during the call. */
+/* `problems` is a HOST array of 1..4 entries, read during the call. */
 size_t rwkv_mm8_one_batch_workspace_bytes(const rwkv_mm8_problem* problems, int count);
 int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, int dtype,
                        void* workspace, size_t workspace_bytes, void* stream);
@@ -215,7 +217,7 @@ void rwkv_mm8_one_set_cluster(int cluster_size, int panel_width);
  *   rwkv_mm8_chain_table_bytes() size of the launch table (one record per launch and CTA).
  *   rwkv_mm8_chain_plan()        HOST-side: lays the launches out into `table_out` (host
  *                                memory).  problems = all launches' problems back to back,
- *                                counts[l] = problems of launch l (1..3).  `workspace` is the
+ *                                counts[l] = problems of launch l (1..4).  `workspace` is the
  *                                DEVICE scratch the kernel will use (its address is baked into
  *                                the table): rwkv_mm8_one_batch_workspace_bytes of the largest
  *                                launch, zero-initialised once.  Copy the table to the device.
@@ -317,6 +319,38 @@ int rwkv_ln_mix(int64_t T, int64_t D, const void* x, int64_t x_stride, const voi
 int rwkv_wkv4_one(int64_t C, const float* t_decay, const float* t_first, const void* r,
                   const void* k, const void* v, float* aa, float* bb, float* pp, void* out,
                   void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * One-token pieces of att_one_v5_1 / att_one_v6_0 that are not packed matmuls (fp16
+ * activations; pkg/model.py:1157-1181, 1263-1298).  They allocate nothing.
+ *
+ * rwkv_v6_token_shift (model.py:1264-1276):
+ *   xx = layer_norm(x; ln_w, ln_b);  dd = state - xx;  new_state <- xx   (new_state may alias state)
+ *   m[0..4] = tanh((xx + dd*maa_x) @ tm_w1 [D, 5*Lm]) viewed [5, Lm], times tm_w2 [5, Lm, D]
+ *   out5[f] = xx + dd * (maa5[f] + m[f])        f = w, k, v, r, g
+ * xx_out and d_out receive xx and dd.  maa5 / out5: HOST arrays of five device pointers.
+ * scratch: rwkv_v6_scratch_bytes(D, 5*Lm) bytes (D, Ld for the decay).  D % 8 == 0, D <= 8192.
+ *
+ * rwkv_v6_decay (model.py:1286-1287):
+ *   w_out = exp(-exp(time_decay + tanh(wx @ td_w1 [D, Ld]) @ td_w2 [Ld, D]))      fp32 [D]
+ *
+ * rwkv_wkv56_one (model.py:1174-1179, 1289-1294): for each head, with fp16-rounded r, k, v,
+ *   out_i = sum_j r_j (u_j k_j v_i + S[j][i]);  S'[j][i] = w_j S[j][i] + k_j v_i
+ * with S = state and S' = new_state (may alias) in the model's layout [H, N(key), N(value)], then group_norm over each head
+ * (eps 64e-5, fp32 lnx_w / lnx_b), cast to fp16 and times the gate g.  w, u: fp32 [H*N]
+ * (RWKV-5.2: exp(-exp(time_decay)); RWKV-6: rwkv_v6_decay's output).  N <= 256.
+ * ------------------------------------------------------------------------------------- */
+size_t rwkv_v6_scratch_bytes(int64_t D, int64_t rank);
+int rwkv_v6_token_shift(int64_t D, int64_t Lm, const void* x, const void* state, void* new_state,
+                        const void* ln_w, const void* ln_b,
+                        const void* maa_x, const void* const* maa5, const void* tm_w1, const void* tm_w2,
+                        float* scratch, size_t scratch_bytes, void* xx_out, void* d_out, void* const* out5,
+                        void* stream);
+int rwkv_v6_decay(int64_t D, int64_t Ld, const void* wx, const void* td_w1, const void* td_w2,
+                  const float* time_decay, float* scratch, size_t scratch_bytes, float* w_out, void* stream);
+int rwkv_wkv56_one(int64_t H, int64_t N, const void* r, const void* k, const void* v, const float* w,
+                   const float* u, const float* state, float* new_state, const float* lnx_w,
+                   const float* lnx_b, const void* g, void* out, void* stream);
 
 #ifdef __cplusplus
 }
