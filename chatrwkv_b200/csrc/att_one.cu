@@ -40,7 +40,7 @@ struct LoraA {
     __half* new_state;      // mode 0: receives this token's LayerNorm output (may alias state)
     const __half* maa_x;    // mode 0
     const __half* w1;       // [D, R]
-    float* partial;         // [slabs][R]
+    float* partial;         // [R][slabs]
     __half* xx_out;         // mode 0: LayerNorm output [D]
     __half* d_out;          // mode 0: sx - xx [D]
 };
@@ -90,21 +90,35 @@ __global__ void __launch_bounds__(kT) lora_a_kernel(const LoraA a) {
             }
         }
         const float rstd = rsqrtf(block_sum(q, sh8) / float(a.D) + 1e-5f);
+        // rows of this slab, eight at a time (slabs start and end on multiples of 8): every operand
+        // is fetched with one 16-byte load before anything is stored
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int j8 = (tid + i * kT) * 8;
-            const __half* hx = reinterpret_cast<const __half*>(&xv4[i]);
+            if (j8 >= j0 && j8 < j0 + nrows) {
+                const uint4 s4 = __ldcg(reinterpret_cast<const uint4*>(a.state) + (j8 >> 3));
+                const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(a.ln_w) + (j8 >> 3));
+                const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(a.ln_b) + (j8 >> 3));
+                const uint4 m4 = __ldg(reinterpret_cast<const uint4*>(a.maa_x) + (j8 >> 3));
+                const __half* hx = reinterpret_cast<const __half*>(&xv4[i]);
+                const __half* hs = reinterpret_cast<const __half*>(&s4);
+                const __half* hw = reinterpret_cast<const __half*>(&w4);
+                const __half* hb = reinterpret_cast<const __half*>(&b4);
+                const __half* hm = reinterpret_cast<const __half*>(&m4);
+                uint4 xo, dq;
+                __half* ho = reinterpret_cast<__half*>(&xo);
+                __half* hd = reinterpret_cast<__half*>(&dq);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const int j = j8 + e;
-                if (j >= j0 && j < j0 + nrows) {
-                    const float xx = r16((__half2float(hx[e]) - mean) * rstd * __half2float(a.ln_w[j]) + __half2float(a.ln_b[j]));
-                    const float dd = r16(__half2float(__ldcg(a.state + j)) - xx);
-                    vin[j - j0] = r16(xx + r16(dd * __half2float(a.maa_x[j])));
-                    a.xx_out[j] = __float2half_rn(xx);
-                    a.d_out[j] = __float2half_rn(dd);
-                    a.new_state[j] = __float2half_rn(xx);
+                for (int e = 0; e < 8; ++e) {
+                    const float xx = r16((__half2float(hx[e]) - mean) * rstd * __half2float(hw[e]) + __half2float(hb[e]));
+                    const float dd = r16(__half2float(hs[e]) - xx);
+                    vin[j8 + e - j0] = r16(xx + r16(dd * __half2float(hm[e])));
+                    ho[e] = __float2half_rn(xx);
+                    hd[e] = __float2half_rn(dd);
                 }
+                reinterpret_cast<uint4*>(a.xx_out)[j8 >> 3] = xo;
+                reinterpret_cast<uint4*>(a.d_out)[j8 >> 3] = dq;
+                reinterpret_cast<uint4*>(a.new_state)[j8 >> 3] = xo;
             }
         }
     } else {
@@ -118,8 +132,14 @@ __global__ void __launch_bounds__(kT) lora_a_kernel(const LoraA a) {
         for (int c = c0; c < a.R; c += cpp) {
             float acc = 0.f;
             const __half* wp = a.w1 + (long long)(j0 + rs) * a.R + c;
-#pragma unroll 16
-            for (int l = rs; l < nrows; l += nrs, wp += (long long)nrs * a.R) acc = fmaf(vin[l], __half2float(*wp), acc);
+            const long long stp = (long long)nrs * a.R;
+            for (int l = rs; l < nrows; l += 16 * nrs, wp += 16 * stp) {       // 16 loads in flight, then the sums
+                __half wv[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) wv[u] = (l + u * nrs < nrows) ? __ldg(wp + u * stp) : __half(0.f);
+#pragma unroll
+                for (int u = 0; u < 16; ++u) if (l + u * nrs < nrows) acc = fmaf(vin[l + u * nrs], __half2float(wv[u]), acc);
+            }
             part[rs * a.R + c] = acc;
         }
     }
@@ -127,14 +147,14 @@ __global__ void __launch_bounds__(kT) lora_a_kernel(const LoraA a) {
     for (int c = tid; c < a.R; c += kT) {
         float s = 0.f;
         for (int q = 0; q < nrs; ++q) s += part[q * a.R + c];
-        a.partial[(long long)blockIdx.x * a.R + c] = s;
+        a.partial[(long long)c * gridDim.x + blockIdx.x] = s;     // [R][slabs]
     }
 }
 
 struct LoraB {
     int mode;               // 0: five token-shift mixes; 1: decay
     int D, R, G, slabs;     // G groups of R/G hidden units each
-    const float* partial;   // [slabs][R]
+    const float* partial;   // [R][slabs]
     const __half* w2;       // [G][R/G][D]
     const __half* xx;       // mode 0 [D]
     const __half* dd;       // mode 0 [D]
@@ -144,50 +164,80 @@ struct LoraB {
     float* w_out;           // mode 1 [D]: exp(-exp(decay + lora))
 };
 
-// grid = ceil(D / 32), block = 256; dynamic shared memory (R + 8 * G * 32) floats.  A CTA owns 32
-// columns d; thread (slice = tid / 32, col = tid % 32) multiplies the hidden units l = slice,
-// slice + 8, ... of every group into its column (all loads independent: one trip to memory), the
-// eight slices are added in order, and G * 32 threads finish.
+// grid = ceil(D / 64), block = 256; dynamic shared memory (R + 32 * G * 64) floats.  A CTA owns 64
+// columns; thread (slice = tid / 8, chunk = tid % 8) multiplies the hidden units l = slice,
+// slice + 32, ... of every group into eight adjacent columns (16-byte loads, all independent:
+// one trip to memory), the 32 slices are added in order, and G * 64 threads-worth of outputs finish.
+// Needs D % 8 == 0 and a 16-byte aligned w2.
 __global__ void __launch_bounds__(kT) lora_b_kernel(const LoraB b) {
-    extern __shared__ float h[];                // h[R] | acc[8][G][32]
+    extern __shared__ float h[];                // h[R] | accs[32][G][64]
     float* accs = h + b.R;
     const int tid = threadIdx.x;
+    const int chunk = tid & 7, slice = tid >> 3;
+    const int d0 = blockIdx.x * 64 + chunk * 8;
+    const int L = b.R / b.G;
     pdl_open();
-    for (int row = tid; row < b.R; row += kT)   // this CTA's 64-byte piece of every row of w2
-        if (blockIdx.x * 32 < b.D) l2_line(b.w2 + (long long)row * b.D + blockIdx.x * 32);
+    for (int row = tid; row < b.R; row += kT)   // this CTA's 128-byte piece of every row of w2
+        l2_line(b.w2 + (long long)row * b.D + blockIdx.x * 64);
     pdl_wait();
     for (int c = tid; c < b.R; c += kT) {
+        const float* pp = b.partial + (long long)c * b.slabs;
         float s = 0.f;
-#pragma unroll 8
-        for (int p = 0; p < b.slabs; ++p) s += __ldcg(b.partial + (long long)p * b.R + c);
+        for (int p = 0; p < b.slabs; p += 16) {
+            float pv[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) pv[u] = p + u < b.slabs ? __ldcg(pp + p + u) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) s += pv[u];
+        }
         h[c] = r16(tanhf(r16(s)));
     }
     __syncthreads();
-    const int col = tid & 31, slice = tid >> 5;
-    const int d = blockIdx.x * 32 + col;
-    const int L = b.R / b.G;
-    for (int f = 0; f < b.G; ++f) {
-        float acc = 0.f;
-        if (d < b.D) {
-            const __half* wp = b.w2 + ((long long)f * L + slice) * b.D + d;
-#pragma unroll 8
-            for (int l = slice; l < L; l += 8, wp += 8LL * b.D) acc = fmaf(h[f * L + l], __half2float(*wp), acc);
+    for (int f0 = 0; f0 < b.G; f0 += 5) {       // up to five groups at a time: their loads first
+        float acc[5][8];
+#pragma unroll
+        for (int g = 0; g < 5; ++g)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+        for (int l = slice; l < L; l += 32) {
+            uint4 wv[5];
+#pragma unroll
+            for (int g = 0; g < 5; ++g)
+                wv[g] = (f0 + g < b.G && d0 < b.D) ? __ldg(reinterpret_cast<const uint4*>(b.w2 + ((long long)(f0 + g) * L + l) * b.D + d0))
+                                                   : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int g = 0; g < 5; ++g) {
+                if (f0 + g < b.G) {
+                    const float hv = h[(f0 + g) * L + l];
+                    const __half2* w2h = reinterpret_cast<const __half2*>(&wv[g]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 wf = __half22float2(w2h[e]);
+                        acc[g][2 * e] = fmaf(hv, wf.x, acc[g][2 * e]);
+                        acc[g][2 * e + 1] = fmaf(hv, wf.y, acc[g][2 * e + 1]);
+                    }
+                }
+            }
         }
-        accs[(slice * b.G + f) * 32 + col] = acc;
+#pragma unroll
+        for (int g = 0; g < 5; ++g)
+            if (f0 + g < b.G)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) accs[(slice * b.G + f0 + g) * 64 + chunk * 8 + e] = acc[g][e];
     }
     __syncthreads();
-    for (int t = tid; t < b.G * 32; t += kT) {
-        const int f = t >> 5, c = t & 31, dd_i = blockIdx.x * 32 + c;
-        if (dd_i >= b.D) continue;
+    for (int t = tid; t < b.G * 64; t += kT) {
+        const int f = t >> 6, c = t & 63, d = blockIdx.x * 64 + c;
+        if (d >= b.D) continue;
         float acc = 0.f;
-#pragma unroll
-        for (int sl = 0; sl < 8; ++sl) acc += accs[(sl * b.G + f) * 32 + c];
+#pragma unroll 8
+        for (int sl = 0; sl < 32; ++sl) acc += accs[(sl * b.G + f) * 64 + c];
         const float m = r16(acc);
         if (b.mode == 0) {
-            const float xx = __half2float(__ldcg(b.xx + dd_i)), dd = __half2float(__ldcg(b.dd + dd_i));
-            b.out[f][dd_i] = __float2half_rn(r16(xx + r16(dd * r16(__half2float(b.maa[f][dd_i]) + m))));
+            const float xx = __half2float(__ldcg(b.xx + d)), dd = __half2float(__ldcg(b.dd + d));
+            b.out[f][d] = __float2half_rn(r16(xx + r16(dd * r16(__half2float(b.maa[f][d]) + m))));
         } else {
-            b.w_out[dd_i] = expf(-expf(b.decay[dd_i] + m));
+            b.w_out[d] = expf(-expf(b.decay[d] + m));
         }
     }
 }
@@ -224,12 +274,19 @@ __global__ void __launch_bounds__(kT) wkv56_one_kernel(int N, const __half* __re
         const float vi = __half2float(__ldcg(v + c0 + i));
         const float* si = s_in + (long long)hh * N * N + i;
         float* so = s_out + (long long)hh * N * N + i;
-#pragma unroll 16
-        for (int j = q; j < N; j += TPI) {
-            const float sv = __ldcg(si + (long long)j * N);
-            const float a = kk[j] * vi;
-            acc = fmaf(rr[j], fmaf(uu[j], a, sv), acc);
-            so[(long long)j * N] = fmaf(ww[j], sv, a);
+        for (int jb = q; jb < N; jb += 16 * TPI) {      // 16 state values in flight, then the updates
+            float sv[16];
+#pragma unroll
+            for (int t = 0; t < 16; ++t) sv[t] = jb + t * TPI < N ? __ldcg(si + (long long)(jb + t * TPI) * N) : 0.f;
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+                const int j = jb + t * TPI;
+                if (j < N) {
+                    const float a = kk[j] * vi;
+                    acc = fmaf(rr[j], fmaf(uu[j], a, sv[t]), acc);
+                    so[(long long)j * N] = fmaf(ww[j], sv[t], a);
+                }
+            }
         }
         accs[q * N + i] = acc;
     }
@@ -249,7 +306,7 @@ __global__ void __launch_bounds__(kT) wkv56_one_kernel(int N, const __half* __re
 
 }  // namespace
 
-static inline int lora_slab(int64_t D) { return D >= 2048 ? 64 : 32; }
+static inline int lora_slab(int64_t D) { return D >= 4096 ? 128 : (D >= 1024 ? 64 : 32); }
 
 extern "C" size_t rwkv_v6_scratch_bytes(int64_t D, int64_t rank) {
     if (D < 1 || rank < 1) return 0;
@@ -262,9 +319,10 @@ extern "C" int rwkv_v6_token_shift(int64_t D, int64_t Lm, const void* x, const v
                                    const void* maa_x, const void* const* maa5, const void* tm_w1, const void* tm_w2,
                                    float* scratch, size_t scratch_bytes, void* xx_out, void* d_out, void* const* out5,
                                    void* stream) {
-    RWKV_CHECK_ARG(D >= 8 && D % 8 == 0 && D <= 8 * 4 * kT && Lm >= 1 && 5 * Lm <= 4096);
+    RWKV_CHECK_ARG(D >= 8 && D % 8 == 0 && D <= 8 * 4 * kT && Lm >= 1 && 5 * Lm <= 1024);
     RWKV_CHECK_ARG(x && state && new_state && ln_w && ln_b && maa_x && maa5 && tm_w1 && tm_w2 && scratch && xx_out && d_out && out5);
-    RWKV_CHECK_ALIGN(x, 16);
+    RWKV_CHECK_ALIGN(x, 16); RWKV_CHECK_ALIGN(state, 16); RWKV_CHECK_ALIGN(new_state, 16); RWKV_CHECK_ALIGN(ln_w, 16);
+    RWKV_CHECK_ALIGN(ln_b, 16); RWKV_CHECK_ALIGN(maa_x, 16); RWKV_CHECK_ALIGN(tm_w2, 16); RWKV_CHECK_ALIGN(xx_out, 16); RWKV_CHECK_ALIGN(d_out, 16);
     const int R = int(5 * Lm);
     const int slab = lora_slab(D);
     const int slabs = int((D + slab - 1) / slab);
@@ -286,12 +344,13 @@ extern "C" int rwkv_v6_token_shift(int64_t D, int64_t Lm, const void* x, const v
         b.maa[f] = static_cast<const __half*>(maa5[f]);
         b.out[f] = static_cast<__half*>(out5[f]);
     }
-    return rwkv_launch_pdl(lora_b_kernel, dim3(int((D + 31) / 32)), dim3(kT), (R + 8 * b.G * 32) * sizeof(float), st, b);
+    return rwkv_launch_pdl(lora_b_kernel, dim3(int((D + 63) / 64)), dim3(kT), (R + 32 * b.G * 64) * sizeof(float), st, b);
 }
 
 extern "C" int rwkv_v6_decay(int64_t D, int64_t Ld, const void* wx, const void* td_w1, const void* td_w2,
                              const float* time_decay, float* scratch, size_t scratch_bytes, float* w_out, void* stream) {
-    RWKV_CHECK_ARG(D >= 1 && Ld >= 1 && Ld <= 4096);
+    RWKV_CHECK_ARG(D >= 8 && D % 8 == 0 && Ld >= 1 && Ld <= 4096);
+    RWKV_CHECK_ALIGN(td_w2, 16);
     RWKV_CHECK_ARG(wx && td_w1 && td_w2 && time_decay && scratch && w_out);
     const int R = int(Ld);
     const int slab = lora_slab(D);
@@ -306,7 +365,7 @@ extern "C" int rwkv_v6_decay(int64_t D, int64_t Ld, const void* wx, const void* 
     LoraB b = {};
     b.mode = 1; b.D = int(D); b.R = R; b.G = 1; b.slabs = slabs; b.partial = scratch;
     b.w2 = static_cast<const __half*>(td_w2); b.decay = time_decay; b.w_out = w_out;
-    return rwkv_launch_pdl(lora_b_kernel, dim3(int((D + 31) / 32)), dim3(kT), (R + 8 * b.G * 32) * sizeof(float), st, b);
+    return rwkv_launch_pdl(lora_b_kernel, dim3(int((D + 63) / 64)), dim3(kT), (R + 32 * b.G * 64) * sizeof(float), st, b);
 }
 
 extern "C" int rwkv_wkv56_one(int64_t H, int64_t N, const void* r, const void* k, const void* v, const float* w,
