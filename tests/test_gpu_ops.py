@@ -270,3 +270,94 @@ def test_mm8_seq_tensor_core_path(ops, T, N, M):
     finally:
         _lib.lib().rwkv_mm8_seq_set_path(0)
     assert ((y.float() - y2.float()).abs() <= y2.float().abs() * 2 ** -9 + 2e-4).all()
+
+
+# ------------------------------------------------------------------- RWKV-5/6 one-token pieces
+def _h(t):
+    return t.half()
+
+
+@pytest.mark.parametrize("D,Lm,Ld", [(4096, 32, 64), (512, 8, 16), (64, 4, 8)])
+def test_v6_token_shift_and_decay(ops, D, Lm, Ld):
+    """rwkv_v6_token_shift / rwkv_v6_decay against the lines of att_one_v6_0 they replace
+    (pkg/model.py:1264-1276, 1286-1287), evaluated on the CPU with fp16 tensors."""
+    import ctypes as C
+    import torch.nn.functional as F
+    from chatrwkv_b200._lib import check, lib
+    g = torch.Generator().manual_seed(D + Lm)
+    rn = lambda *s, sc=1.0: torch.randn(*s, generator=g) * sc
+    x, sx = _h(rn(D)), _h(rn(D))
+    ln_w, ln_b = _h(1 + rn(D, sc=0.1)), _h(rn(D, sc=0.1))
+    maa_x = _h(torch.rand(D, generator=g))
+    maa = [_h(torch.rand(D, generator=g)) for _ in range(5)]
+    w1, w2 = _h(rn(D, 5 * Lm, sc=0.05)), _h(rn(5, Lm, D, sc=0.05))
+    dw1, dw2 = _h(rn(D, Ld, sc=0.05)), _h(rn(Ld, D, sc=0.05))
+    decay = torch.rand(D, generator=g) * 6 - 5
+    # reference (fp32 accumulation inside the fp16 matmuls, one rounding per op)
+    xx = F.layer_norm(x.float(), (D,), ln_w.float(), ln_b.float()).half()
+    dd = sx - xx
+    xxx = xx + dd * maa_x
+    hid = torch.tanh((xxx.float() @ w1.float()).half()).view(5, 1, Lm)
+    m = torch.bmm(hid.float(), w2.float()).half().view(5, D)
+    ref5 = [xx + dd * (maa[f] + m[f]) for f in range(5)]
+    t1 = torch.tanh((ref5[0].float() @ dw1.float()).half())
+    ref_w = torch.exp(-torch.exp(decay + (t1.float() @ dw2.float()).half().float()))
+
+    dev = lambda t: t.cuda().contiguous()
+    dx, dsx, dlw, dlb, dmx = dev(x), dev(sx), dev(ln_w), dev(ln_b), dev(maa_x)
+    dmaa = [dev(t) for t in maa]
+    dw = [dev(w1), dev(w2), dev(dw1), dev(dw2)]
+    out5 = [torch.zeros(D, dtype=torch.float16, device="cuda") for _ in range(5)]
+    xx_o, dd_o, ns = (torch.zeros(D, dtype=torch.float16, device="cuda") for _ in range(3))
+    ws = torch.zeros(lib().rwkv_v6_scratch_bytes(D, max(5 * Lm, Ld)), dtype=torch.uint8, device="cuda")
+    arr = lambda ts: (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+    st = torch.cuda.current_stream().cuda_stream
+    check(lib().rwkv_v6_token_shift(D, Lm, dx.data_ptr(), dsx.data_ptr(), ns.data_ptr(), dlw.data_ptr(), dlb.data_ptr(),
+                                    dmx.data_ptr(), arr(dmaa), dw[0].data_ptr(), dw[1].data_ptr(), ws.data_ptr(), ws.numel(),
+                                    xx_o.data_ptr(), dd_o.data_ptr(), arr(out5), st), "v6_token_shift")
+    w_out = torch.zeros(D, dtype=torch.float32, device="cuda")
+    check(lib().rwkv_v6_decay(D, Ld, out5[0].data_ptr(), dw[2].data_ptr(), dw[3].data_ptr(), dev(decay).data_ptr(),
+                              ws.data_ptr(), ws.numel(), w_out.data_ptr(), st), "v6_decay")
+    torch.cuda.synchronize()
+    assert (xx_o.cpu().float() - xx.float()).abs().max() <= 4e-3          # one fp16 ulp at |x| < 4
+    assert torch.equal(ns, xx_o)
+    assert (dd_o.cpu().float() - dd.float()).abs().max() <= 8e-3
+    for f in range(5):
+        assert (out5[f].cpu().float() - ref5[f].float()).abs().max() <= 2e-2, f
+    assert (w_out.cpu() - ref_w).abs().max() <= 5e-3
+
+
+@pytest.mark.parametrize("H,N", [(64, 64), (4, 16), (3, 32), (2, 128)])
+def test_wkv56_one(ops, H, N):
+    """rwkv_wkv56_one against att_one_v6_0's state update, group-norm and gate (pkg/model.py:1289-1296)."""
+    import torch.nn.functional as F
+    from chatrwkv_b200._lib import check, lib
+    g = torch.Generator().manual_seed(H * 1000 + N)
+    C_ = H * N
+    r, k, v, gate = (_h(torch.randn(C_, generator=g)) for _ in range(4))
+    w = torch.exp(-torch.exp(torch.rand(C_, generator=g) * 6 - 5))
+    u = torch.rand(C_, generator=g) * 2 - 1
+    S = torch.randn(H, N, N, generator=g)
+    lw, lb = 1 + torch.randn(C_, generator=g) * 0.1, torch.randn(C_, generator=g) * 0.1
+    rr, kk, vv = r.float().view(H, 1, N), k.float().view(H, N, 1), v.float().view(H, 1, N)
+    a = kk @ vv
+    out = rr @ (u.view(H, N, 1) * a + S)
+    S_new = a + w.view(H, N, 1) * S
+    out = F.group_norm(out.flatten().unsqueeze(0), num_groups=H, weight=lw, bias=lb, eps=64e-5).squeeze(0)
+    ref = out.half() * gate
+    d = lambda t: t.cuda().contiguous()
+    dS, dS2 = d(S), torch.zeros(H, N, N, device="cuda")
+    y = torch.zeros(C_, dtype=torch.float16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    args = [d(r), d(k), d(v), d(w), d(u)]
+    dl = [d(lw), d(lb), d(gate)]
+    check(lib().rwkv_wkv56_one(H, N, *[t.data_ptr() for t in args], dS.data_ptr(), dS2.data_ptr(), dl[0].data_ptr(),
+                               dl[1].data_ptr(), dl[2].data_ptr(), y.data_ptr(), st), "wkv56_one")
+    torch.cuda.synchronize()
+    torch.testing.assert_close(dS2.cpu(), S_new, rtol=1e-5, atol=1e-5)
+    assert (y.cpu().float() - ref.float()).abs().max() <= 2e-2
+    # in place (new_state aliases state)
+    check(lib().rwkv_wkv56_one(H, N, *[t.data_ptr() for t in args], dS.data_ptr(), dS.data_ptr(), dl[0].data_ptr(),
+                               dl[1].data_ptr(), dl[2].data_ptr(), y.data_ptr(), st), "wkv56_one")
+    torch.cuda.synchronize()
+    assert torch.equal(dS, dS2)
