@@ -204,6 +204,37 @@ __device__ __forceinline__ float block_sum256(float v, float* sh8) {
     return t;
 }
 
+// Copy n elements of ES bytes, starting at element `first` of `src_base`, to shared memory:
+// 16-byte cp.async where the source is aligned (the caller commits), plain loads otherwise.
+template <int ES>
+__device__ __forceinline__ void stage_vec(uint8_t* dst, const void* src_base, int first, int n, int tid) {
+    if (src_base == nullptr || n <= 0) return;
+    const uint8_t* src = static_cast<const uint8_t*>(src_base) + (long long)first * ES;
+    const int bytes = n * ES;
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        const int full = bytes >> 4;
+        const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+        for (int c = tid; c < full; c += kThreads) cp_async16(d + c * 16, src + c * 16);
+        done = full * 16;
+    }
+    for (int o = done + tid * ES; o < bytes; o += kThreads * ES) {
+        if (ES == 2) *reinterpret_cast<uint16_t*>(dst + o) = __ldcg(reinterpret_cast<const uint16_t*>(src + o));
+        else *reinterpret_cast<uint32_t*>(dst + o) = __ldcg(reinterpret_cast<const uint32_t*>(src + o));
+    }
+}
+
+// Ask L2 for the lines of n elements of ES bytes from element `first` on (no data returns: the
+// loads that follow the wait on the preceding kernel then find them on chip).
+template <int ES>
+__device__ __forceinline__ void l2_prefetch(const void* src_base, int first, int n, int tid) {
+    if (src_base == nullptr || n <= 0) return;
+    const uint8_t* src = static_cast<const uint8_t*>(src_base) + (long long)first * ES;
+    const uint8_t* line0 = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(src) & ~uintptr_t(127));
+    const int lines = int((src + (long long)n * ES - line0 + 127) >> 7);
+    for (int l = tid; l < lines; l += kThreads) asm volatile("prefetch.global.L2 [%0];" ::"l"(line0 + l * 128));
+}
+
 // The activation x[j] this problem multiplies with, for row j, after the fused prologue.
 // LayerNorm statistics (mean, rstd) are computed once per CTA by the caller.
 template <typename F>
