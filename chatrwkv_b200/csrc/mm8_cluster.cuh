@@ -49,7 +49,8 @@ template <typename F> constexpr int stage_bytes() { return 2 * kStageRows * int(
 constexpr int kClusterSmem = 104 * 1024;     // also caps residency at two CTAs per SM
 static_assert(ring_bytes(kDepthC) + stage_bytes<float>() <= kClusterSmem, "stage area does not fit");
 
-template <typename F, bool PACKED>
+// MODE: 0 = scalar fp32, 1 = two-wide fp32 instructions, 2 = 16-bit fixed-point activations and dp2a
+template <typename F, int MODE>
 __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_constant__ ClusterBatch b) {
     asm volatile("griddepcontrol.launch_dependents;");
     MM8_TRACE_BEGIN(b.trace_id, blockIdx.x);
@@ -282,22 +283,50 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
 
     // ---- main loop ---------------------------------------------------------------------------
     float acc[16];
+    if (MODE == 2) {
+        // integer form: x' as 16-bit fixed point, two rows per step (mm8_core.cuh)
+        const float inv_scale = quantize_pairs(xs, nrows, rpp, nsteps, sh8);
+        const int* xp = reinterpret_cast<const int*>(xs);
+        int iacc[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-    for (int g = 0; g < ngroups; ++g) {
-        cp_async_wait<kDepthC - 1>();
-        uint4 v[kGroup];
+        for (int i = 0; i < 16; ++i) iacc[i] = 0;
+        int sq = 0;
+        for (int g = 0; g < ngroups; ++g) {
+            cp_async_wait<kDepthC - 1>();
+            uint4 v[kGroup];
 #pragma unroll
-        for (int u = 0; u < kGroup; ++u)
-            v[u] = *reinterpret_cast<const uint4*>(ring + tid * 16 + ((g % kDepthC) * kGroup + u) * (kThreads * 16));
-        if (active) {
+            for (int u = 0; u < kGroup; ++u)
+                v[u] = *reinterpret_cast<const uint4*>(ring + tid * 16 + ((g % kDepthC) * kGroup + u) * (kThreads * 16));
+            if (active) {
 #pragma unroll
-            for (int u = 0; u < kGroup; ++u) {
-                const int r = sub + (g * kGroup + u) * rpp;
-                if (r < nrows) fma16<PACKED>(acc, v[u], xs[r]);
+                for (int pr = 0; pr < kGroup / 2; ++pr) {
+                    const int xq = xp[(g * (kGroup / 2) + pr) * rpp + sub];      // 0 for rows past the end
+                    dot16_q(iacc, v[2 * pr], v[2 * pr + 1], xq);
+                    sq = dp2a_lo(xq, 0x00000101u, sq);
+                }
             }
+            issue_group(g + kDepthC);
         }
-        issue_group(g + kDepthC);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = float(iacc[i] - 128 * sq) * inv_scale;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+        for (int g = 0; g < ngroups; ++g) {
+            cp_async_wait<kDepthC - 1>();
+            uint4 v[kGroup];
+#pragma unroll
+            for (int u = 0; u < kGroup; ++u)
+                v[u] = *reinterpret_cast<const uint4*>(ring + tid * 16 + ((g % kDepthC) * kGroup + u) * (kThreads * 16));
+            if (active) {
+#pragma unroll
+                for (int u = 0; u < kGroup; ++u) {
+                    const int r = sub + (g * kGroup + u) * rpp;
+                    if (r < nrows) fma16<MODE == 1>(acc, v[u], xs[r]);
+                }
+            }
+            issue_group(g + kDepthC);
+        }
     }
     cp_async_wait<0>();
     MM8_STAMP(b.trace_id, blockIdx.x, 4);
@@ -401,7 +430,7 @@ static inline int cluster_slots(K kern, int S, int smem) {
 
 // Launch the validated problems of `plan_b` (mm8_plan filled them in) on the cluster kernel.
 // RWKV_ERR_UNSUPPORTED: this batch is not eligible and the caller should use the ticket kernel.
-static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, bool packed, cudaStream_t st) {
+static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, int mode, cudaStream_t st) {
     if (g_cluster_size < 0) return RWKV_ERR_UNSUPPORTED;
     ClusterBatch cb;
     memset(&cb, 0, sizeof(cb));
@@ -424,8 +453,8 @@ static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, 
     if ((((max_n + S - 1) / S + 7) & ~7) > kMaxRowsPerCta) return RWKV_ERR_UNSUPPORTED;
 
     void (*kern)(ClusterBatch) = nullptr;
-    if (dtype == RWKV_F16) kern = packed ? mm8_cluster_kernel<__half, true> : mm8_cluster_kernel<__half, false>;
-    else kern = packed ? mm8_cluster_kernel<float, true> : mm8_cluster_kernel<float, false>;
+    if (dtype == RWKV_F16) kern = mode == 2 ? mm8_cluster_kernel<__half, 2> : mode == 1 ? mm8_cluster_kernel<__half, 1> : mm8_cluster_kernel<__half, 0>;
+    else kern = mode == 2 ? mm8_cluster_kernel<float, 2> : mode == 1 ? mm8_cluster_kernel<float, 1> : mm8_cluster_kernel<float, 0>;
     const int smem = kClusterSmem;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
         cudaGetLastError();

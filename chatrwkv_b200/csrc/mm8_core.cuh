@@ -133,6 +133,83 @@ __device__ __forceinline__ void fma16(float (&acc)[16], const uint4& v, float xv
     }
 }
 
+// Integer form of the same product: two rows at a time.  xq packs the two rows' activations as
+// signed 16-bit fixed point (row a low, row b high); va / vb are the rows' 16 weight bytes.  Per
+// word, two byte permutes interleave the rows ({a0 b0 a1 b1}, {a2 b2 a3 b3}) and four dp2a add
+// xa*wa + xb*wb for one column each: 6 integer instructions for 8 bytes instead of 16 for the
+// fp32 form.  acc[] are exact 32-bit sums of q*w with w the unsigned byte; the caller subtracts
+// 128 times the sum of its q.
+__device__ __forceinline__ int dp2a_lo(int a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp2a_hi(int a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ void dot16_q(int (&acc)[16], const uint4& va, const uint4& vb, int xq) {
+    const uint32_t wa[4] = {va.x, va.y, va.z, va.w};
+    const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const uint32_t plo = __byte_perm(wa[q], wb[q], 0x5140);
+        const uint32_t phi = __byte_perm(wa[q], wb[q], 0x7362);
+        acc[q * 4 + 0] = dp2a_lo(xq, plo, acc[q * 4 + 0]);
+        acc[q * 4 + 1] = dp2a_hi(xq, plo, acc[q * 4 + 1]);
+        acc[q * 4 + 2] = dp2a_lo(xq, phi, acc[q * 4 + 2]);
+        acc[q * 4 + 3] = dp2a_hi(xq, phi, acc[q * 4 + 3]);
+    }
+}
+
+// Turn the CTA's x' (fp32, `nrows` values in xs) into packed 16-bit pairs IN PLACE: entry
+// p * rpp + sub holds rows sub + 2p*rpp (low) and sub + (2p+1)*rpp (high), the two rows that the
+// thread with row offset `sub` multiplies in its p-th pair; rows past nrows are 0.  Returns
+// 1/scale (value = q / scale); the quantisation range is the largest that keeps a thread's
+// 32-bit sums of `nsteps` products q * 255 from overflowing (32767 up to 257 steps).
+__device__ __forceinline__ float quantize_pairs(float* xs, int nrows, int rpp, int nsteps, float* sh8) {
+    const int tid = threadIdx.x;
+    float m = 0.f;
+    for (int l = tid; l < nrows; l += kThreads) m = fmaxf(m, fabsf(xs[l]));
+    m = warp_max(m);
+    __syncthreads();
+    if ((tid & 31) == 0) sh8[tid >> 5] = m;
+    __syncthreads();
+    m = 0.f;
+#pragma unroll
+    for (int i = 0; i < kWarps; ++i) m = fmaxf(m, sh8[i]);
+    const int qmax = min(32767, 0x7fffffff / (255 * max(nsteps, 1)));
+    const bool finite = m < 3.0e38f;            // false for inf and NaN
+    const float scale = (finite && m > 0.f) ? float(qmax) / m : 0.f;
+    const int entries = ((nsteps + kGroup - 1) / kGroup) * (kGroup / 2) * rpp;   // whole ring groups; <= 1536
+    float fa[6], fb[6];
+#pragma unroll
+    for (int i = 0; i < 6; ++i) {
+        const int idx = tid + i * kThreads;
+        fa[i] = fb[i] = 0.f;
+        if (idx < entries) {
+            const int p = idx / rpp, sb = idx - p * rpp;
+            const int ra = sb + 2 * p * rpp, rb = ra + rpp;
+            if (ra < nrows) fa[i] = xs[ra];
+            if (rb < nrows) fb[i] = xs[rb];
+        }
+    }
+    __syncthreads();
+    int* xp = reinterpret_cast<int*>(xs);
+#pragma unroll
+    for (int i = 0; i < 6; ++i) {
+        const int idx = tid + i * kThreads;
+        if (idx < entries) {
+            const int qa = __float2int_rn(fa[i] * scale), qb = __float2int_rn(fb[i] * scale);
+            xp[idx] = (qa & 0xffff) | (qb << 16);
+        }
+    }
+    __syncthreads();
+    if (!finite) return __int_as_float(0x7fc00000);      // non-finite activations: NaN results, as in fp32
+    return m > 0.f ? m / float(qmax) : 0.f;
+}
+
 // Loads of activations and state go to L2 (ld.global.cg): inside the persistent chain kernel
 // they may have been written by another SM a moment ago, and L1 is not coherent.
 template <typename F>

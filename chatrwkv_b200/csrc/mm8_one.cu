@@ -80,6 +80,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_one_kernel(const __grid_const
         for (int g = 0; g < kDepth; ++g) issue_group(g);
     }
     const int cta_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    (void)cta_id;
     MM8_TRACE_BEGIN(b.trace_id, cta_id);
     MM8_STAMP(b.trace_id, cta_id, 0);
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -262,7 +263,8 @@ int g_variant = 0;
 
 extern "C" void rwkv_mm8_one_set_split(int split) { g_split_override = split; }
 // bits 0-1: panel width (0 = automatic, 1 = 512, 2 = 256, 3 = 128 columns); bit 2: scalar fp32
-// arithmetic instead of the two-wide instructions
+// arithmetic; bit 3: two-wide fp32 arithmetic in the cluster kernel (its default is the 16-bit
+// fixed-point form)
 extern "C" void rwkv_mm8_one_set_variant(int variant) { g_variant = variant; }
 
 extern "C" size_t rwkv_mm8_one_workspace_bytes(int64_t N, int64_t M) {
@@ -285,10 +287,11 @@ extern "C" int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, i
     if (rc != RWKV_OK) return rc;
     const int pw = plan.pw;
     const bool aligned = plan.aligned, packed = (g_variant & 4) == 0;
-    if (aligned && force_pw == 0 && g_split_override == 0) {
+    if (aligned && (g_variant & 3) == 0 && g_split_override == 0) {
         // K-splits of a panel as one thread-block cluster (mm8_cluster.cuh); falls through to the
         // ticket kernel when the batch is not eligible.
-        const int crc = mm8_cluster_launch(plan.b, count, dtype, packed, static_cast<cudaStream_t>(stream));
+        const int crc = mm8_cluster_launch(plan.b, count, dtype, (g_variant & 4) ? 0 : (g_variant & 8) ? 1 : 2,
+                                           static_cast<cudaStream_t>(stream));
         if (crc != RWKV_ERR_UNSUPPORTED) return crc;
     }
     void (*kern)(Batch) = nullptr;

@@ -63,28 +63,42 @@ def test_quantize_rescale_keeps_codes(ops):
 MM8_SHAPES = [(4096, 4096), (768, 3072), (3072, 768), (64, 300), (768, 50277), (1000, 48), (40, 1000), (5120, 5120)]
 
 
+# The default kernel feeds the activations to the integer dot-product instructions as 16-bit fixed
+# point (exact integer sums, one scale per CTA): per output an error of at most
+# 2^-16 max|x*ry| sum|w-128|, in practice ~4e-5 of the output's RMS -- a tenth of the fp16 rounding
+# that follows.  `rwkv_mm8_one_set_variant(8)` selects the fp32 form, which is held to fp32 round-off.
+MM8_ARITH = [(0, 2.5e-4, 0.15), (8, 2e-5, 0.05)]
+
+
+@pytest.mark.parametrize("variant,tol,max_mismatch", MM8_ARITH)
 @pytest.mark.parametrize("N,M", MM8_SHAPES)
-def test_mm8_one_matches_oracle(ops, N, M):
+def test_mm8_one_matches_oracle(ops, N, M, variant, tol, max_mismatch):
+    from chatrwkv_b200._lib import lib
     from tests.util import packed_case
     cpu, dev = packed_case(N, M, seed=N + 7 * M)
     g = torch.Generator().manual_seed(3000 + N)
     x = torch.randn(N, generator=g).half()
     ref = orc.mm8_kernel(x, *cpu)
-    y = torch.zeros(M, dtype=torch.float32, device="cuda")
-    torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y)
+    lib().rwkv_mm8_one_set_variant(variant)
+    try:
+        y = torch.zeros(M, dtype=torch.float32, device="cuda")
+        torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y)
+        # deterministic: same bits on a second call; accumulates into y
+        y2 = torch.zeros(M, dtype=torch.float32, device="cuda")
+        torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y2)
+        y3 = torch.full((M,), 3.0, dtype=torch.float32, device="cuda")
+        torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y3)
+        torch.cuda.synchronize()
+    finally:
+        lib().rwkv_mm8_one_set_variant(0)
     err = (y.cpu() - ref).abs().max().item()
     scale = ref.abs().max().item()
-    assert err <= 2e-5 * max(scale, 1.0), (err, scale)
-    # deterministic: same bits on a second call; accumulates into y
-    y2 = torch.zeros(M, dtype=torch.float32, device="cuda")
-    torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y2)
+    assert err <= tol * max(scale, 1.0), (err, scale)
     assert torch.equal(y, y2)
-    y3 = torch.full((M,), 3.0, dtype=torch.float32, device="cuda")
-    torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y3)
     assert torch.allclose(y3, y + 3.0, rtol=0, atol=1e-5)
-    # the rounding the wrapper applies (fp32 -> fp16) agrees with the oracle but for ties
+    # the rounding the wrapper applies (fp32 -> fp16) agrees with the oracle but for near-ties
     mism = (y.half().cpu() != ref.half()).float().mean().item()
-    assert mism < 0.05, mism
+    assert mism < max_mismatch, mism
 
 
 @pytest.mark.parametrize("cluster,width", [(-1, 0), (1, 0), (2, 48), (4, 0), (8, 0), (8, 112), (8, 4096), (0, 16)])
@@ -107,7 +121,7 @@ def test_mm8_one_split_reductions_agree(ops, N, M, cluster, width):
         torch.cuda.synchronize()
     finally:
         lib().rwkv_mm8_one_set_cluster(0, 0)
-    assert (y.cpu() - ref).abs().max().item() <= 2e-5 * max(ref.abs().max().item(), 1.0)
+    assert (y.cpu() - ref).abs().max().item() <= (2e-5 if cluster == -1 else 2.5e-4) * max(ref.abs().max().item(), 1.0)
     assert torch.equal(y, y2)
 
 
@@ -121,7 +135,7 @@ def test_mm8_one_one_signed_input(ops):
     ref = orc.mm8_kernel(x, *cpu)
     y = torch.zeros(M, dtype=torch.float32, device="cuda")
     torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y)
-    assert (y.cpu() - ref).abs().max().item() <= 3e-5 * ref.abs().max().item()
+    assert (y.cpu() - ref).abs().max().item() <= 2.5e-4 * ref.abs().max().item()
 
 
 def test_mm8_one_unpadded_and_fp32(ops):
