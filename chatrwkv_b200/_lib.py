@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "librwkv_b200.so")
 OK = 0
 F32, F16, BF16 = 0, 1, 2
 PRO_PLAIN, PRO_LN_MIX, PRO_WKV4 = 0, 1, 2
+ERR_UNSUPPORTED = -5
 EPI_ACC_F32, EPI_STORE, EPI_SIGMOID, EPI_RELU_SQ, EPI_RESIDUAL, EPI_MUL_RESIDUAL, EPI_STORE_F32, EPI_SILU = range(8)
 
 
@@ -66,6 +67,7 @@ SIGNATURES = {
     "rwkv_ln_mix": (_i32, [_i64, _i64, _vp, _i64, _vp, _vp, _vp, _i32, _i32, C.POINTER(_vp), _i64, C.POINTER(_vp), _i64, _vp, _i64, _vp, _vp]),
     "rwkv_wkv4_one": (_i32, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "rwkv_v6_scratch_bytes": (_sz, [_i64, _i64]),
+    "rwkv_v6_att_pre": (_i32, [_i64, _i64, _i64] + [_vp] * 17),
     "rwkv_v6_token_shift": (_i32, [_i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _vp]),
     "rwkv_v6_decay": (_i32, [_i64, _i64, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp]),
     "rwkv_wkv56_one": (_i32, [_i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -8,7 +8,11 @@
 // matrix, split over row slabs into fp32 partials) and "lora_b" (sum of the partials, tanh, the
 // grouped [R/G] x [D] second factor and the pointwise tail).  Every fp16 torch op of the
 // reference rounds once; r16() marks those places.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -304,6 +308,261 @@ __global__ void __launch_bounds__(kT) wkv56_one_kernel(int N, const __half* __re
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The token shift AND the decay of one RWKV-6 layer in ONE launch: a single cluster of 8 CTAs.
+// Four dependent low-rank products need three all-to-all exchanges of a few hundred numbers;
+// inside a cluster those are hardware barriers plus distributed-shared-memory loads (about a
+// microsecond), while as separate launches every step paid a kernel boundary.  CTA r owns rows
+// (and, for the second factors, columns) [r * rows, (r + 1) * rows) of the D channels, so the
+// vector a stage needs is the one the same CTA produced in the stage before.  The other SMs
+// stay free for the matmul launch that follows and is already filling its weight ring.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPT = 512;
+
+struct AttPre {
+    int D, Lm, Ld, rows;
+    const __half *x, *ln_w, *ln_b, *state, *maa_x, *w1, *w2, *dw1, *dw2;
+    const __half* maa[5];
+    const float* decay;
+    __half *new_state, *xx_out, *d_out;
+    __half* out[5];
+    float* w_out;
+};
+
+__device__ __forceinline__ float block_sum512(float v, float* sh16) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh16[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPT / 32; ++i) t += sh16[i];
+    return t;
+}
+
+// part[c] = sum over this CTA's rows l of vin[l] * W[l][c]   (W row-major [nrows][R], R % 8 == 0)
+__device__ __forceinline__ void slab_gemv(const float* vin, int nrows, const __half* W, int R, float* red, float* part) {
+    const int tid = threadIdx.x;
+    const int cc = R >> 3, nrg = kPT / cc, rg = tid / cc, c = tid - rg * cc;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    if (rg < nrg) {
+        for (int l0 = rg; l0 < nrows; l0 += 8 * nrg) {
+            uint4 wv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int l = l0 + u * nrg;
+                wv[u] = l < nrows ? __ldg(reinterpret_cast<const uint4*>(W + (long long)l * R) + c) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int l = l0 + u * nrg;
+                if (l < nrows) {
+                    const float hv = vin[l];
+                    const __half2* w2h = reinterpret_cast<const __half2*>(&wv[u]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 wf = __half22float2(w2h[e]);
+                        acc[2 * e] = fmaf(hv, wf.x, acc[2 * e]);
+                        acc[2 * e + 1] = fmaf(hv, wf.y, acc[2 * e + 1]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) red[rg * R + c * 8 + e] = acc[e];
+    }
+    __syncthreads();
+    for (int c2 = tid; c2 < R; c2 += kPT) {
+        float s = 0.f;
+        for (int q = 0; q < nrg; ++q) s += red[q * R + c2];
+        part[c2] = s;
+    }
+}
+
+// For this CTA's columns d = j0 + l (l < ncols, ncols % 8 == 0) and every group f < G:
+// fin(f, l, r16(sum over the group's hidden units u of h[f*L + u] * W2[f*L + u][d])).
+template <typename Fin>
+__device__ __forceinline__ void cols_gemv(const float* h, int G, int L, const __half* W2, int D, int j0, int ncols, Fin fin) {
+    const int tid = threadIdx.x, rs = tid & 7;
+    const int nch = ncols >> 3;
+    for (int cb = 0; cb < nch; cb += kPT / 8) {
+        const int c = cb + (tid >> 3);
+        const bool on = c < nch;
+        for (int f = 0; f < G; ++f) {
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+            if (on) {
+                for (int l0 = rs; l0 < L; l0 += 64) {
+                    uint4 wv[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int l = l0 + 8 * u;
+                        wv[u] = l < L ? __ldg(reinterpret_cast<const uint4*>(W2 + ((long long)f * L + l) * D + j0) + c) : make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int l = l0 + 8 * u;
+                        if (l < L) {
+                            const float hv = h[f * L + l];
+                            const __half2* w2h = reinterpret_cast<const __half2*>(&wv[u]);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 wf = __half22float2(w2h[e]);
+                                acc[2 * e] = fmaf(hv, wf.x, acc[2 * e]);
+                                acc[2 * e + 1] = fmaf(hv, wf.y, acc[2 * e + 1]);
+                            }
+                        }
+                    }
+                }
+            }
+            float mine = 0.f;                   // the eight lanes of a chunk add up, lane rs keeps column rs
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float v = acc[e];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                if (e == rs) mine = v;
+            }
+            if (on) fin(f, c * 8 + rs, r16(mine));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kPT) v6_att_pre_kernel(const AttPre a) {
+    extern __shared__ __align__(16) float sm[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = int(cluster.block_rank());
+    const int tid = threadIdx.x;
+    const int R1 = 5 * a.Lm, R3 = a.Ld;
+    const int Rm = max(R1, R3);
+    float* vin = sm;                            // [rows]   xxx, later wx, of this CTA's channels
+    float* xxs = vin + a.rows;                  // [rows]   LayerNorm output
+    float* dds = xxs + a.rows;                  // [rows]   sx - xx
+    float* part1 = dds + a.rows;                // [R1]     this CTA's share of xxx @ w1     (read by the cluster)
+    float* part3 = part1 + R1;                  // [R3]     this CTA's share of wx @ dw1      (read by the cluster)
+    float* h = part3 + R3;                      // [Rm]     tanh of the summed shares
+    float* red = h + Rm;                        // [4096]   row-group sums
+    __shared__ float sh16[kPT / 32];
+    const int j0 = rank * a.rows;
+    const int nrows = max(0, min(a.D, j0 + a.rows) - j0);     // multiple of 8
+
+    pdl_open();
+    {   // weights of this CTA, toward L2: its rows of w1 / dw1, its 16-byte column pieces of w2 / dw2
+        const char* b1 = reinterpret_cast<const char*>(a.w1 + (long long)j0 * R1);
+        for (long long o = (long long)tid * 128; o < (long long)nrows * R1 * 2; o += (long long)kPT * 128) l2_line(b1 + o);
+        const char* b3 = reinterpret_cast<const char*>(a.dw1 + (long long)j0 * R3);
+        for (long long o = (long long)tid * 128; o < (long long)nrows * R3 * 2; o += (long long)kPT * 128) l2_line(b3 + o);
+        const int lines = (nrows * 2 + 127) / 128;
+        for (int i = tid; i < (R1 + R3) * lines; i += kPT) {
+            const int row = i / lines, ln = i - row * lines;
+            const __half* base = row < R1 ? a.w2 + (long long)row * a.D : a.dw2 + (long long)(row - R1) * a.D;
+            l2_line(reinterpret_cast<const char*>(base + j0) + ln * 128);
+        }
+    }
+    pdl_wait();
+
+    // ---- LayerNorm of the whole vector; xx, dd, xxx for this CTA's channels (model.py:1264-1267)
+    {
+        uint4 xv4[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int j8 = (tid + i * kPT) * 8;
+            xv4[i] = j8 < a.D ? __ldcg(reinterpret_cast<const uint4*>(a.x) + (j8 >> 3)) : make_uint4(0, 0, 0, 0);
+        }
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const __half2* hh = reinterpret_cast<const __half2*>(&xv4[i]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(hh[e]); s += f.x + f.y; }
+        }
+        const float mean = block_sum512(s, sh16) / float(a.D);
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if ((tid + i * kPT) * 8 < a.D) {
+                const __half2* hh = reinterpret_cast<const __half2*>(&xv4[i]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(hh[e]);
+                    q = fmaf(f.x - mean, f.x - mean, q);
+                    q = fmaf(f.y - mean, f.y - mean, q);
+                }
+            }
+        }
+        const float rstd = rsqrtf(block_sum512(q, sh16) / float(a.D) + 1e-5f);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int j8 = (tid + i * kPT) * 8;
+            if (j8 >= j0 && j8 < j0 + nrows) {
+                const uint4 s4 = __ldcg(reinterpret_cast<const uint4*>(a.state) + (j8 >> 3));
+                const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(a.ln_w) + (j8 >> 3));
+                const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(a.ln_b) + (j8 >> 3));
+                const uint4 m4 = __ldg(reinterpret_cast<const uint4*>(a.maa_x) + (j8 >> 3));
+                const __half* hx = reinterpret_cast<const __half*>(&xv4[i]);
+                const __half* hs = reinterpret_cast<const __half*>(&s4);
+                const __half* hw = reinterpret_cast<const __half*>(&w4);
+                const __half* hb = reinterpret_cast<const __half*>(&b4);
+                const __half* hm = reinterpret_cast<const __half*>(&m4);
+                uint4 xo, dq;
+                __half* ho = reinterpret_cast<__half*>(&xo);
+                __half* hd = reinterpret_cast<__half*>(&dq);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float xx = r16((__half2float(hx[e]) - mean) * rstd * __half2float(hw[e]) + __half2float(hb[e]));
+                    const float dd = r16(__half2float(hs[e]) - xx);
+                    const int l = j8 + e - j0;
+                    vin[l] = r16(xx + r16(dd * __half2float(hm[e])));
+                    xxs[l] = xx;
+                    dds[l] = dd;
+                    ho[e] = __float2half_rn(xx);
+                    hd[e] = __float2half_rn(dd);
+                }
+                reinterpret_cast<uint4*>(a.xx_out)[j8 >> 3] = xo;
+                reinterpret_cast<uint4*>(a.d_out)[j8 >> 3] = dq;
+                reinterpret_cast<uint4*>(a.new_state)[j8 >> 3] = xo;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- xxx @ w1 -> tanh -> five offsets -> wx, kx, vx, rx, gx (model.py:1268-1276) ----------
+    slab_gemv(vin, nrows, a.w1 + (long long)j0 * R1, R1, red, part1);
+    cluster.sync();
+    for (int c = tid; c < R1; c += kPT) {
+        float s = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) s += cluster.map_shared_rank(part1, q)[c];
+        h[c] = r16(tanhf(r16(s)));
+    }
+    __syncthreads();
+    cols_gemv(h, 5, a.Lm, a.w2, a.D, j0, nrows, [&](int f, int l, float m) {
+        const float v = r16(xxs[l] + r16(dds[l] * r16(__half2float(a.maa[f][j0 + l]) + m)));
+        a.out[f][j0 + l] = __float2half_rn(v);
+        if (f == 0) vin[l] = v;                 // wx: the input of the decay product
+    });
+    __syncthreads();
+
+    // ---- w = exp(-exp(time_decay + tanh(wx @ dw1) @ dw2)) (model.py:1286-1287) ---------------
+    slab_gemv(vin, nrows, a.dw1 + (long long)j0 * R3, R3, red, part3);
+    cluster.sync();
+    for (int c = tid; c < R3; c += kPT) {
+        float s = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) s += cluster.map_shared_rank(part3, q)[c];
+        h[c] = r16(tanhf(r16(s)));
+    }
+    __syncthreads();
+    cols_gemv(h, 1, a.Ld, a.dw2, a.D, j0, nrows, [&](int, int l, float m) {
+        a.w_out[j0 + l] = expf(-expf(a.decay[j0 + l] + m));
+    });
+    cluster.sync();                             // nobody leaves while its shares are being read
+}
+
 }  // namespace
 
 static inline int lora_slab(int64_t D) { return D >= 4096 ? 128 : (D >= 1024 ? 64 : 32); }
@@ -378,4 +637,60 @@ extern "C" int rwkv_wkv56_one(int64_t H, int64_t N, const void* r, const void* k
                            static_cast<cudaStream_t>(stream), int(N), static_cast<const __half*>(r),
                            static_cast<const __half*>(k), static_cast<const __half*>(v), w, u, state, new_state, lnx_w, lnx_b,
                            static_cast<const __half*>(g), static_cast<__half*>(out));
+}
+
+// Token shift + decay of one RWKV-6 layer in one single-cluster launch (see v6_att_pre_kernel).
+// RWKV_ERR_UNSUPPORTED when the shapes do not fit it (ranks not multiples of 8, D > 8192): the
+// caller then uses rwkv_v6_token_shift followed by rwkv_v6_decay, which compute the same values.
+extern "C" int rwkv_v6_att_pre(int64_t D, int64_t Lm, int64_t Ld, const void* x, const void* state, void* new_state,
+                               const void* ln_w, const void* ln_b, const void* maa_x, const void* const* maa5,
+                               const void* tm_w1, const void* tm_w2, const void* td_w1, const void* td_w2,
+                               const float* time_decay, void* xx_out, void* d_out, void* const* out5, float* w_out,
+                               void* stream) {
+    RWKV_CHECK_ARG(D >= 8 && D % 8 == 0 && Lm >= 1 && Ld >= 1);
+    RWKV_CHECK_ARG(x && state && new_state && ln_w && ln_b && maa_x && maa5 && tm_w1 && tm_w2 && td_w1 && td_w2 &&
+                   time_decay && xx_out && d_out && out5 && w_out);
+    if (D > 8 * 2 * kPT || (5 * Lm) % 8 != 0 || Ld % 8 != 0 || 5 * Lm > 1024 || Ld > 1024) return RWKV_ERR_UNSUPPORTED;
+    const void* al[] = {x, state, new_state, ln_w, ln_b, maa_x, tm_w1, tm_w2, td_w1, td_w2, xx_out, d_out};
+    for (const void* p : al) RWKV_CHECK_ALIGN(p, 16);
+    AttPre a = {};
+    a.D = int(D); a.Lm = int(Lm); a.Ld = int(Ld);
+    a.rows = int(((D + 7) / 8 + 7) / 8 * 8);
+    a.x = static_cast<const __half*>(x); a.ln_w = static_cast<const __half*>(ln_w); a.ln_b = static_cast<const __half*>(ln_b);
+    a.state = static_cast<const __half*>(state); a.maa_x = static_cast<const __half*>(maa_x);
+    a.w1 = static_cast<const __half*>(tm_w1); a.w2 = static_cast<const __half*>(tm_w2);
+    a.dw1 = static_cast<const __half*>(td_w1); a.dw2 = static_cast<const __half*>(td_w2);
+    a.decay = time_decay;
+    a.new_state = static_cast<__half*>(new_state); a.xx_out = static_cast<__half*>(xx_out); a.d_out = static_cast<__half*>(d_out);
+    a.w_out = w_out;
+    for (int f = 0; f < 5; ++f) {
+        RWKV_CHECK_ARG(maa5[f] && out5[f]);
+        a.maa[f] = static_cast<const __half*>(maa5[f]);
+        a.out[f] = static_cast<__half*>(out5[f]);
+    }
+    const int R1 = int(5 * Lm), R3 = int(Ld);
+    const size_t smem = size_t(3 * a.rows + R1 + R3 + (R1 > R3 ? R1 : R3) + 4096) * sizeof(float);
+    if (smem > 48 * 1024) return RWKV_ERR_UNSUPPORTED;
+    static int use_pdl = -1;
+    if (use_pdl < 0) {
+        const char* e = getenv("RWKV_B200_PDL");
+        use_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(8);
+    cfg.blockDim = dim3(kPT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 8;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, v6_att_pre_kernel, a);
+    if (e != cudaSuccess) { cudaGetLastError(); return RWKV_ERR_LAUNCH; }
+    return RWKV_OK;
 }

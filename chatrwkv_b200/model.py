@@ -530,16 +530,26 @@ class RWKV:
                 out5 = ptrs([b.m0, b.m1, b.m2, b.m3, b.m4])
                 keep += [maa5, out5]
                 ws = self._lora_ws
-                plan.append(lambda i=i, s=s, att=att, ln1=ln1, Lm=Lm, maa5=maa5, out5=out5, ws=ws: check(
-                    L.rwkv_v6_token_shift(D, Lm, b.x.data_ptr(), sin[s].data_ptr(), sout[s].data_ptr(), ln1[0].data_ptr(),
+                if (5 * Lm) % 8 == 0 and Ld % 8 == 0 and D <= 8192:
+                    # token shift and decay as one single-cluster launch
+                    plan.append(lambda s=s, att=att, ln1=ln1, Lm=Lm, Ld=Ld, maa5=maa5, out5=out5: check(
+                        L.rwkv_v6_att_pre(D, Lm, Ld, b.x.data_ptr(), sin[s].data_ptr(), sout[s].data_ptr(), ln1[0].data_ptr(),
                                           ln1[1].data_ptr(), w[att + "time_maa_x"].data_ptr(), maa5,
                                           w[att + "time_maa_w1"].data_ptr(), w[att + "time_maa_w2"].data_ptr(),
-                                          ws.data_ptr(), ws.numel(), b.xln.data_ptr(), b.dd.data_ptr(), out5, stream()),
-                    "v6_token_shift"))
-                plan.append(lambda att=att, Ld=Ld, ws=ws: check(
-                    L.rwkv_v6_decay(D, Ld, b.m0.data_ptr(), w[att + "time_decay_w1"].data_ptr(),
-                                    w[att + "time_decay_w2"].data_ptr(), w[att + "time_decay"].data_ptr(), ws.data_ptr(),
-                                    ws.numel(), b.wdec.data_ptr(), stream()), "v6_decay"))
+                                          w[att + "time_decay_w1"].data_ptr(), w[att + "time_decay_w2"].data_ptr(),
+                                          w[att + "time_decay"].data_ptr(), b.xln.data_ptr(), b.dd.data_ptr(), out5,
+                                          b.wdec.data_ptr(), stream()), "v6_att_pre"))
+                else:
+                    plan.append(lambda s=s, att=att, ln1=ln1, Lm=Lm, maa5=maa5, out5=out5, ws=ws: check(
+                        L.rwkv_v6_token_shift(D, Lm, b.x.data_ptr(), sin[s].data_ptr(), sout[s].data_ptr(), ln1[0].data_ptr(),
+                                              ln1[1].data_ptr(), w[att + "time_maa_x"].data_ptr(), maa5,
+                                              w[att + "time_maa_w1"].data_ptr(), w[att + "time_maa_w2"].data_ptr(),
+                                              ws.data_ptr(), ws.numel(), b.xln.data_ptr(), b.dd.data_ptr(), out5, stream()),
+                        "v6_token_shift"))
+                    plan.append(lambda att=att, Ld=Ld, ws=ws: check(
+                        L.rwkv_v6_decay(D, Ld, b.m0.data_ptr(), w[att + "time_decay_w1"].data_ptr(),
+                                        w[att + "time_decay_w2"].data_ptr(), w[att + "time_decay"].data_ptr(), ws.data_ptr(),
+                                        ws.numel(), b.wdec.data_ptr(), stream()), "v6_decay"))
                 gemv([P(b.m3, att + "receptance.weight", b.r, EPI_STORE), P(b.m1, att + "key.weight", b.k, EPI_STORE),
                       P(b.m2, att + "value.weight", b.v, EPI_STORE), P(b.m4, att + "gate.weight", b.g, EPI_SILU)])
                 decay = b.wdec

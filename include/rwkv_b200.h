@@ -339,8 +339,18 @@ int rwkv_wkv4_one(int64_t C, const float* t_decay, const float* t_first, const v
  * with S = state and S' = new_state (may alias) in the model's layout [H, N(key), N(value)], then group_norm over each head
  * (eps 64e-5, fp32 lnx_w / lnx_b), cast to fp16 and times the gate g.  w, u: fp32 [H*N]
  * (RWKV-5.2: exp(-exp(time_decay)); RWKV-6: rwkv_v6_decay's output).  N <= 256.
+ *
+ * rwkv_v6_att_pre: rwkv_v6_token_shift followed by rwkv_v6_decay (of out5[0] = wx) as ONE launch
+ * of a single 8-CTA cluster that exchanges the low-rank intermediates through distributed shared
+ * memory; same values, no scratch.  Returns RWKV_ERR_UNSUPPORTED (and launches nothing) unless
+ * 5*Lm and Ld are multiples of 8 and D <= 8192: callers then use the two calls above.
  * ------------------------------------------------------------------------------------- */
 size_t rwkv_v6_scratch_bytes(int64_t D, int64_t rank);
+int rwkv_v6_att_pre(int64_t D, int64_t Lm, int64_t Ld, const void* x, const void* state, void* new_state,
+                    const void* ln_w, const void* ln_b, const void* maa_x, const void* const* maa5,
+                    const void* tm_w1, const void* tm_w2, const void* td_w1, const void* td_w2,
+                    const float* time_decay, void* xx_out, void* d_out, void* const* out5, float* w_out,
+                    void* stream);
 int rwkv_v6_token_shift(int64_t D, int64_t Lm, const void* x, const void* state, void* new_state,
                         const void* ln_w, const void* ln_b,
                         const void* maa_x, const void* const* maa5, const void* tm_w1, const void* tm_w2,

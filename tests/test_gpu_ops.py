@@ -291,6 +291,11 @@ def _h(t):
     return t.half()
 
 
+def _lib_unsupported():
+    from chatrwkv_b200 import _lib
+    return _lib.ERR_UNSUPPORTED
+
+
 @pytest.mark.parametrize("D,Lm,Ld", [(4096, 32, 64), (512, 8, 16), (64, 4, 8)])
 def test_v6_token_shift_and_decay(ops, D, Lm, Ld):
     """rwkv_v6_token_shift / rwkv_v6_decay against the lines of att_one_v6_0 they replace
@@ -339,6 +344,26 @@ def test_v6_token_shift_and_decay(ops, D, Lm, Ld):
     for f in range(5):
         assert (out5[f].cpu().float() - ref5[f].float()).abs().max() <= 2e-2, f
     assert (w_out.cpu() - ref_w).abs().max() <= 5e-3
+    # the single-launch form computes the same values (or declines shapes it does not take)
+    out5b = [torch.zeros(D, dtype=torch.float16, device="cuda") for _ in range(5)]
+    xx_b, dd_b, ns_b = (torch.zeros(D, dtype=torch.float16, device="cuda") for _ in range(3))
+    w_b = torch.zeros(D, dtype=torch.float32, device="cuda")
+    rc = lib().rwkv_v6_att_pre(D, Lm, Ld, dx.data_ptr(), dsx.data_ptr(), ns_b.data_ptr(), dlw.data_ptr(), dlb.data_ptr(),
+                               dmx.data_ptr(), arr(dmaa), dw[0].data_ptr(), dw[1].data_ptr(), dw[2].data_ptr(),
+                               dw[3].data_ptr(), dev(decay).data_ptr(), xx_b.data_ptr(), dd_b.data_ptr(), arr(out5b),
+                               w_b.data_ptr(), st)
+    torch.cuda.synchronize()
+    if (5 * Lm) % 8 == 0 and Ld % 8 == 0:
+        assert rc == 0
+        # (LayerNorm statistics are summed by 512 instead of 256 threads: fp32 round-off, at most an fp16 ulp)
+        assert (xx_b.float() - xx_o.float()).abs().max() <= 4e-3 and (dd_b.float() - dd_o.float()).abs().max() <= 8e-3
+        assert torch.equal(ns_b, xx_b)
+        for f in range(5):
+            assert (out5b[f].cpu().float() - ref5[f].float()).abs().max() <= 2e-2, f
+            assert (out5b[f].float() - out5[f].float()).abs().max() <= 8e-3, f
+        assert (w_b.cpu() - ref_w).abs().max() <= 5e-3
+    else:
+        assert rc == _lib_unsupported()
 
 
 @pytest.mark.parametrize("H,N", [(64, 64), (4, 16), (3, 32), (2, 128)])
