@@ -285,27 +285,45 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
     float acc[16];
     if (MODE == 2) {
         // integer form: x' as 16-bit fixed point, two rows per step (mm8_core.cuh)
-        const float inv_scale = quantize_pairs(xs, nrows, rpp, nsteps, sh8);
-        const int* xp = reinterpret_cast<const int*>(xs);
+        const float inv_scale = quantize_pairs(xs, nrows, rpp, cpr, sub, ch, active, ngroups * (kGroup / 2), nsteps, sh8);
         int iacc[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) iacc[i] = 0;
         int sq = 0;
+        // running state instead of per-iteration index arithmetic: the ring position being drained,
+        // this thread's next pair of activations, and the rows of the group to fetch next
+        const int cnt = (active && sub < nrows) ? (nrows - sub + rpp - 1) / rpp : 0;     // rows of this thread
+        const int* xq_ptr = reinterpret_cast<const int*>(xs) + sub;
+        const uint8_t* wn = wp + (long long)(kDepthC * kGroup) * step;
+        const long long step2 = 2 * step, step3 = 3 * step;
+        int inext = kDepthC * kGroup;
+        uint32_t rd = 0;
         for (int g = 0; g < ngroups; ++g) {
             cp_async_wait<kDepthC - 1>();
+            const uint8_t* rb = ring + tid * 16 + rd;
             uint4 v[kGroup];
 #pragma unroll
-            for (int u = 0; u < kGroup; ++u)
-                v[u] = *reinterpret_cast<const uint4*>(ring + tid * 16 + ((g % kDepthC) * kGroup + u) * (kThreads * 16));
+            for (int u = 0; u < kGroup; ++u) v[u] = *reinterpret_cast<const uint4*>(rb + u * (kThreads * 16));
             if (active) {
-#pragma unroll
-                for (int pr = 0; pr < kGroup / 2; ++pr) {
-                    const int xq = xp[(g * (kGroup / 2) + pr) * rpp + sub];      // 0 for rows past the end
-                    dot16_q(iacc, v[2 * pr], v[2 * pr + 1], xq);
-                    sq = dp2a_lo(xq, 0x00000101u, sq);
-                }
+                const int xq0 = xq_ptr[0], xq1 = xq_ptr[rpp];                   // 0 for rows past the end
+                xq_ptr += 2 * rpp;
+                dot16_q(iacc, v[0], v[1], xq0);
+                dot16_q(iacc, v[2], v[3], xq1);
+                sq = dp2a_lo(xq0, 0x00000101u, sq);
+                sq = dp2a_lo(xq1, 0x00000101u, sq);
             }
-            issue_group(g + kDepthC);
+            {   // refill the position just drained with group g + kDepthC
+                const uint32_t dst = slot0 + rd;
+                if (inext < cnt) cp_async16(dst, wn);
+                if (inext + 1 < cnt) cp_async16(dst + kThreads * 16, wn + step);
+                if (inext + 2 < cnt) cp_async16(dst + 2 * kThreads * 16, wn + step2);
+                if (inext + 3 < cnt) cp_async16(dst + 3 * kThreads * 16, wn + step3);
+                cp_async_commit();
+                wn += 4 * step;
+                inext += kGroup;
+            }
+            rd += kGroup * kThreads * 16;
+            if (rd == uint32_t(kDepthC * kGroup * kThreads * 16)) rd = 0;
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) acc[i] = float(iacc[i] - 128 * sq) * inv_scale;

@@ -165,10 +165,13 @@ __device__ __forceinline__ void dot16_q(int (&acc)[16], const uint4& va, const u
 
 // Turn the CTA's x' (fp32, `nrows` values in xs) into packed 16-bit pairs IN PLACE: entry
 // p * rpp + sub holds rows sub + 2p*rpp (low) and sub + (2p+1)*rpp (high), the two rows that the
-// thread with row offset `sub` multiplies in its p-th pair; rows past nrows are 0.  Returns
-// 1/scale (value = q / scale); the quantisation range is the largest that keeps a thread's
-// 32-bit sums of `nsteps` products q * 255 from overflowing (32767 up to 257 steps).
-__device__ __forceinline__ float quantize_pairs(float* xs, int nrows, int rpp, int nsteps, float* sh8) {
+// thread with row offset `sub` multiplies in its p-th pair; rows past nrows are 0.  `npairs` pairs
+// per row offset (whole ring groups).  The thread with chunk index `ch` (of `cpr`) makes the pairs
+// p = ch, ch + cpr, ... of its own row offset, at most 8 of them.  Returns 1/scale (value = q /
+// scale); the quantisation range is the largest that keeps a thread's 32-bit sums of `nsteps`
+// products q * 255 from overflowing (32767 up to 257 steps).
+__device__ __forceinline__ float quantize_pairs(float* xs, int nrows, int rpp, int cpr, int sub, int ch, bool active,
+                                                int npairs, int nsteps, float* sh8) {
     const int tid = threadIdx.x;
     float m = 0.f;
     for (int l = tid; l < nrows; l += kThreads) m = fmaxf(m, fabsf(xs[l]));
@@ -182,15 +185,13 @@ __device__ __forceinline__ float quantize_pairs(float* xs, int nrows, int rpp, i
     const int qmax = min(32767, 0x7fffffff / (255 * max(nsteps, 1)));
     const bool finite = m < 3.0e38f;            // false for inf and NaN
     const float scale = (finite && m > 0.f) ? float(qmax) / m : 0.f;
-    const int entries = ((nsteps + kGroup - 1) / kGroup) * (kGroup / 2) * rpp;   // whole ring groups; <= 1536
-    float fa[6], fb[6];
+    float fa[8], fb[8];
 #pragma unroll
-    for (int i = 0; i < 6; ++i) {
-        const int idx = tid + i * kThreads;
+    for (int i = 0; i < 8; ++i) {
+        const int p = ch + i * cpr;
         fa[i] = fb[i] = 0.f;
-        if (idx < entries) {
-            const int p = idx / rpp, sb = idx - p * rpp;
-            const int ra = sb + 2 * p * rpp, rb = ra + rpp;
+        if (active && p < npairs) {
+            const int ra = sub + 2 * p * rpp, rb = ra + rpp;
             if (ra < nrows) fa[i] = xs[ra];
             if (rb < nrows) fb[i] = xs[rb];
         }
@@ -198,11 +199,11 @@ __device__ __forceinline__ float quantize_pairs(float* xs, int nrows, int rpp, i
     __syncthreads();
     int* xp = reinterpret_cast<int*>(xs);
 #pragma unroll
-    for (int i = 0; i < 6; ++i) {
-        const int idx = tid + i * kThreads;
-        if (idx < entries) {
+    for (int i = 0; i < 8; ++i) {
+        const int p = ch + i * cpr;
+        if (active && p < npairs) {
             const int qa = __float2int_rn(fa[i] * scale), qb = __float2int_rn(fb[i] * scale);
-            xp[idx] = (qa & 0xffff) | (qb << 16);
+            xp[p * rpp + sub] = (qa & 0xffff) | (qb << 16);
         }
     }
     __syncthreads();
