@@ -36,6 +36,19 @@ class Mm8Problem(C.Structure):
     ]
 
 
+class Mm8Exchange(C.Structure):
+    """rwkv_mm8_exchange: where a column-sharded launch also stores its results (the other ranks'
+    buffers) and the arrival words it waits on and publishes."""
+    _fields_ = [
+        ("peer_y", (C.c_void_p * 7) * 4),
+        ("arrived", C.c_void_p), ("peer_arrived", C.c_void_p * 7),
+        ("done_counter", C.c_void_p), ("error", C.c_void_p),
+        ("wait_seq", C.c_uint32), ("signal_seq", C.c_uint32),
+        ("world", C.c_int32), ("rank", C.c_int32),
+    ]
+
+
+PEER_HANDLE_BYTES = 64
 _vp, _i64, _i32, _sz, _f = C.c_void_p, C.c_int64, C.c_int, C.c_size_t, C.c_float
 
 # name -> (restype, argtypes); every symbol include/rwkv_b200.h declares.
@@ -49,6 +62,13 @@ SIGNATURES = {
     "rwkv_mm8_one_static": (_i32, [_i64, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _vp]),
     "rwkv_mm8_one_batch_workspace_bytes": (_sz, [C.POINTER(Mm8Problem), _i32]),
     "rwkv_mm8_one_batch": (_i32, [C.POINTER(Mm8Problem), _i32, _i32, _vp, _sz, _vp]),
+    "rwkv_mm8_one_batch_exchange": (_i32, [C.POINTER(Mm8Problem), _i32, C.POINTER(Mm8Exchange), _i32, _vp, _sz, _vp]),
+    "rwkv_peer_alloc": (_i32, [_sz, C.POINTER(_vp)]),
+    "rwkv_peer_free": (_i32, [_vp]),
+    "rwkv_peer_export": (_i32, [_vp, _vp]),
+    "rwkv_peer_open": (_i32, [_vp, C.POINTER(_vp)]),
+    "rwkv_peer_close": (_i32, [_vp]),
+    "rwkv_peer_wait": (_i32, [_vp, _i32, C.c_uint32, _vp, _vp]),
     "rwkv_mm8_one_set_split": (None, [_i32]),
     "rwkv_mm8_one_set_variant": (None, [_i32]),
     "rwkv_mm8_one_set_cluster": (None, [_i32, _i32]),

@@ -41,6 +41,7 @@ constexpr int kExtraRows = 1024;                     // rows whose LayerNorm / W
 constexpr int kEpiCols = 512;                        // columns a CTA finishes
 constexpr int kEpiConst = 2 * kEpiCols * 2;          // rx, mx (fp16) of one phase
 constexpr int kMaxPanel = 2048;                      // the column sums share the 8 KB of x'
+constexpr int kChainRows = 2048;                     // rows per CTA (the stage buffers are laid out for this)
 constexpr unsigned kSpinLimit = 1u << 22;
 
 // What a cluster does in one phase; written by the host, copied in 16-byte chunks.
@@ -115,7 +116,7 @@ __device__ __forceinline__ void stage_constants(const ClusterPhase& r, const Geo
     if (!r.active) return;
     const Problem& P = r.P;
     stage_vec<2>(stage, P.ry, g.j0, g.nrows, tid);
-    stage_vec<2>(stage + 2 * kMaxRowsPerCta, P.my, g.j0, g.nrows, tid);
+    stage_vec<2>(stage + 2 * kChainRows, P.my, g.j0, g.nrows, tid);
     if (g.nrows <= kExtraRows) {
         uint8_t* ex = stage + kExtraOff;
         if (P.prologue == RWKV_PRO_LN_MIX) {
@@ -184,7 +185,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_chain_kernel(const uint8_t* _
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;                                                    // [slot][thread] 16 B
     uint8_t* recs = smem + kOffRecs;                                         // 3 phase records
-    __shared__ float xs[kMaxRowsPerCta];                                     // x' of this CTA's rows; later its column sums
+    __shared__ float xs[kChainRows];                                         // x' of this CTA's rows; later its column sums
     __shared__ float ssum[kWarps][3];
     __shared__ float sh8[kWarps];
     __shared__ float tot3[4];
@@ -243,7 +244,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_chain_kernel(const uint8_t* _
         }
         uint8_t* stage = stage_of(ph);
         const F* s_ry = reinterpret_cast<const F*>(stage);
-        const F* s_my = s_ry + kMaxRowsPerCta;
+        const F* s_my = s_ry + kChainRows;
         const uint8_t* s_extra = stage + kExtraOff;
         const F* s_rx = reinterpret_cast<const F*>(epic_of(ph));
         const F* s_mx = s_rx + kEpiCols;
@@ -340,7 +341,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_chain_kernel(const uint8_t* _
                 sxmy = fmaf(xv, __half2float(s_my[l]), sxmy);
             }
         } else if (R.active) {
-            constexpr int RPT = kMaxRowsPerCta / kThreads;
+            constexpr int RPT = kChainRows / kThreads;
             float xr[RPT];
 #pragma unroll
             for (int i = 0; i < RPT; ++i) {
@@ -538,7 +539,7 @@ extern "C" int rwkv_mm8_chain_plan(const rwkv_mm8_problem* problems, const int32
                 return RWKV_ERR_UNSUPPORTED;
             P.rows_per_cta = ((P.N + kS - 1) / kS + 7) & ~7;
             P.splits = kS;
-            if (P.rows_per_cta > kMaxRowsPerCta) return RWKV_ERR_UNSUPPORTED;
+            if (P.rows_per_cta > kChainRows) return RWKV_ERR_UNSUPPORTED;
             if (P.prologue == RWKV_PRO_LN_MIX && P.mode != 2 && reinterpret_cast<uintptr_t>(P.p2) % 16 != 0) return RWKV_ERR_ALIGNMENT;
             total_cols += P.M;
         }

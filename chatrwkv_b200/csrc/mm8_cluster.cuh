@@ -41,17 +41,36 @@ struct ClusterBatch {
 //                         -- only when the CTA has at most 1024 rows, else read from global memory
 //   [.., +4*512*sF)       rx, mx, aux, aux2 of the columns this CTA finishes (at most 512)
 // Everything that is a model constant is copied here BEFORE the wait on the preceding kernel.
-constexpr int kStageRows = kMaxRowsPerCta;
 constexpr int kStageExtraRows = 1024;
 constexpr int kStageExtraBytes = 8192;
 constexpr int kStageEpiCols = 512;
-template <typename F> constexpr int stage_bytes() { return 2 * kStageRows * int(sizeof(F)) + kStageExtraBytes + 4 * kStageEpiCols * int(sizeof(F)); }
-constexpr int kClusterSmem = 104 * 1024;     // also caps residency at two CTAs per SM
-static_assert(ring_bytes(kDepthC) + stage_bytes<float>() <= kClusterSmem, "stage area does not fit");
+template <typename F, int ROWS> constexpr int stage_bytes() { return 2 * ROWS * int(sizeof(F)) + kStageExtraBytes + 4 * kStageEpiCols * int(sizeof(F)); }
+// dynamic shared memory: what caps residency at two CTAs per SM, less when x' needs more static room
+template <int ROWS> constexpr int cluster_smem() { return ROWS <= kMaxRowsPerCta ? 104 * 1024 : 102 * 1024; }
+
+// Multi-GPU form (one model split by output columns over the ranks, one process per GPU): the
+// epilogue stores every result into the same place of every other rank's activation buffer as
+// well (plain stores to peer memory over NVLink), the last CTA of the launch to finish then writes
+// the launch's sequence number into each rank's arrival word for this rank, and the prologue of
+// the NEXT launch waits (bounded) until every rank's word has reached the number it needs.  The
+// all-gather that a column-sharded matmul needs thus happens inside the matmul kernels: no
+// collective call, no extra launch, transfers overlap the tail of the stream tile by tile.
+struct Exchange {
+    void* peer_y[kMaxProblems][7];
+    unsigned* arrived;           // this rank's arrival words [world]
+    unsigned* peer_arrived[7];   // on each other rank: its arrival word for this rank
+    unsigned* done_counter;
+    unsigned* error;
+    unsigned wait_seq, signal_seq;
+    int world, rank, n_peers;
+};
+struct NoExchange { int unused; };
+constexpr unsigned kPeerSpinLimit = 1u << 21;
 
 // MODE: 0 = scalar fp32, 1 = two-wide fp32 instructions, 2 = 16-bit fixed-point activations and dp2a
-template <typename F, int MODE>
-__global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_constant__ ClusterBatch b) {
+template <typename F, int MODE, typename EX, int ROWS>
+__global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_constant__ ClusterBatch b, const __grid_constant__ EX ex) {
+    constexpr bool kExch = sizeof(EX) > sizeof(NoExchange);
     asm volatile("griddepcontrol.launch_dependents;");
     MM8_TRACE_BEGIN(b.trace_id, blockIdx.x);
     cg::cluster_group cluster = cg::this_cluster();
@@ -69,7 +88,8 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
     const int PWc = cpr * 16;
 
     extern __shared__ __align__(128) uint8_t ring[];    // [slot][thread] 16 B; later the reduce buffers
-    __shared__ float xs[kMaxRowsPerCta];
+    static_assert(ring_bytes(kDepthC) + stage_bytes<F, ROWS>() <= cluster_smem<ROWS>(), "stage area does not fit");
+    __shared__ float xs[ROWS];
     __shared__ float ssum[kWarps][3];
     __shared__ float sh8[kWarps];
     __shared__ float tot3[4];                            // this CTA's scalar sums (read by the cluster)
@@ -96,8 +116,8 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
 
     uint8_t* stage = ring + ring_bytes(kDepthC);
     F* s_ry = reinterpret_cast<F*>(stage);
-    F* s_my = s_ry + kStageRows;
-    uint8_t* s_extra = stage + 2 * kStageRows * sizeof(F);
+    F* s_my = s_ry + ROWS;
+    uint8_t* s_extra = stage + 2 * ROWS * sizeof(F);
     F* s_rx = reinterpret_cast<F*>(s_extra + kStageExtraBytes);
     F* s_mx = s_rx + kStageEpiCols;
     F* s_aux = s_mx + kStageEpiCols;
@@ -145,6 +165,20 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
     MM8_STAMP(b.trace_id, blockIdx.x, 0);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     MM8_STAMP(b.trace_id, blockIdx.x, 2);
+    if constexpr (kExch) {
+        // the other ranks' slices of this launch's inputs: wait for their arrival words (bounded)
+        if (ex.wait_seq != 0 && tid < ex.world) {
+            unsigned it = 0;
+            while (true) {
+                unsigned v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ex.arrived + tid) : "memory");
+                if (int(v - ex.wait_seq) >= 0) break;
+                if (++it >= kPeerSpinLimit) { atomicExch(ex.error, 1u); break; }
+                __nanosleep(64);
+            }
+        }
+        __syncthreads();
+    }
 
     // ---- prologue: one trip to L2 for what earlier kernels wrote, then x' = x * ry ----------
     const bool writer = panel == 0;
@@ -246,7 +280,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
         }
     } else {
         // all loads of a thread first (independent: one trip), then the arithmetic
-        constexpr int RPT = kMaxRowsPerCta / kThreads;   // rows per thread: 8
+        constexpr int RPT = ROWS / kThreads;             // rows per thread: 8 or 10
         float xr[RPT];
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
@@ -285,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
     float acc[16];
     if (MODE == 2) {
         // integer form: x' as 16-bit fixed point, two rows per step (mm8_core.cuh)
-        const float inv_scale = quantize_pairs(xs, nrows, rpp, cpr, sub, ch, active, ngroups * (kGroup / 2), nsteps, sh8);
+        const float inv_scale = quantize_pairs<ROWS <= 2048 ? 8 : 10>(xs, nrows, rpp, cpr, sub, ch, active, ngroups * (kGroup / 2), nsteps, sh8);
         int iacc[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) iacc[i] = 0;
@@ -412,6 +446,29 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
         }
         const float val = fmaf(rxk, s, fmaf(rxk * 128.5f, txr, fmaf(mxk, tx, txmy)));
         store_epilogue_with<F>(P, k, val, auxv, aux2v);
+        if constexpr (kExch) {                   // the same value into every other rank's buffer
+            if (P.epilogue == RWKV_EPI_STORE_F32) {
+                const float o = static_cast<const float*>(P.y)[k];
+                for (int pr = 0; pr < ex.n_peers; ++pr) static_cast<float*>(ex.peer_y[z][pr])[k] = o;
+            } else {
+                const F o = static_cast<const F*>(P.y)[k];
+                for (int pr = 0; pr < ex.n_peers; ++pr) static_cast<F*>(ex.peer_y[z][pr])[k] = o;
+            }
+        }
+    }
+    if constexpr (kExch) {
+        __threadfence_system();                  // this thread's peer stores, before the CTA reports
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned t = atomicAdd(ex.done_counter, 1u);
+            if (t == gridDim.x - 1) {            // last CTA of the launch: everything is out
+                atomicExch(ex.done_counter, 0u);
+                __threadfence_system();
+                for (int pr = 0; pr < ex.n_peers; ++pr)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ex.peer_arrived[pr]), "r"(ex.signal_seq) : "memory");
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ex.arrived + ex.rank), "r"(ex.signal_seq) : "memory");
+            }
+        }
     }
     cluster.sync();                              // nobody leaves while its shared memory is being read
     MM8_STAMP(b.trace_id, blockIdx.x, 6);
@@ -448,7 +505,7 @@ static inline int cluster_slots(K kern, int S, int smem) {
 
 // Launch the validated problems of `plan_b` (mm8_plan filled them in) on the cluster kernel.
 // RWKV_ERR_UNSUPPORTED: this batch is not eligible and the caller should use the ticket kernel.
-static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, int mode, cudaStream_t st) {
+static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, int mode, const Exchange* exch, cudaStream_t st) {
     if (g_cluster_size < 0) return RWKV_ERR_UNSUPPORTED;
     ClusterBatch cb;
     memset(&cb, 0, sizeof(cb));
@@ -468,17 +525,30 @@ static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, 
     int S = g_cluster_size > 0 ? g_cluster_size : kMaxClusterSize;
     if (S != 1 && S != 2 && S != 4 && S != 8) return RWKV_ERR_UNSUPPORTED;
     if (g_cluster_size == 0) while (S > 1 && min_n < S * 64) S >>= 1;
-    if ((((max_n + S - 1) / S + 7) & ~7) > kMaxRowsPerCta) return RWKV_ERR_UNSUPPORTED;
-
-    void (*kern)(ClusterBatch) = nullptr;
-    if (dtype == RWKV_F16) kern = mode == 2 ? mm8_cluster_kernel<__half, 2> : mode == 1 ? mm8_cluster_kernel<__half, 1> : mm8_cluster_kernel<__half, 0>;
-    else kern = mode == 2 ? mm8_cluster_kernel<float, 2> : mode == 1 ? mm8_cluster_kernel<float, 1> : mm8_cluster_kernel<float, 0>;
-    const int smem = kClusterSmem;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    const int rows_needed = ((max_n + S - 1) / S + 7) & ~7;
+    if (rows_needed > kWideRowsPerCta) return RWKV_ERR_UNSUPPORTED;
+    // more than 2048 rows per CTA (20480 in-features): the build with the larger x' buffer, fp16 / integer only
+    // Once a launch has needed it, every later launch of the process uses that build too: launches
+    // that alternate between the two builds (different shared-memory footprints) lost their overlap
+    // (14B shape: 241 tok/s alternating, 305 with the wide build throughout).
+    static bool wide_seen = false;
+    if (rows_needed > kMaxRowsPerCta) wide_seen = true;
+    const bool wide = wide_seen && dtype == RWKV_F16 && mode == 2;
+    if (rows_needed > kMaxRowsPerCta && !wide) return RWKV_ERR_UNSUPPORTED;
+    if ((exch != nullptr || wide) && (dtype != RWKV_F16 || mode != 2)) return RWKV_ERR_UNSUPPORTED;
+    constexpr int RN = kMaxRowsPerCta, RW = kWideRowsPerCta;
+    void (*kern)(ClusterBatch, NoExchange) = nullptr;
+    void (*kern_x)(ClusterBatch, Exchange) = wide ? mm8_cluster_kernel<__half, 2, Exchange, RW> : mm8_cluster_kernel<__half, 2, Exchange, RN>;
+    if (wide) kern = mm8_cluster_kernel<__half, 2, NoExchange, RW>;
+    else if (dtype == RWKV_F16) kern = mode == 2 ? mm8_cluster_kernel<__half, 2, NoExchange, RN> : mode == 1 ? mm8_cluster_kernel<__half, 1, NoExchange, RN> : mm8_cluster_kernel<__half, 0, NoExchange, RN>;
+    else kern = mode == 2 ? mm8_cluster_kernel<float, 2, NoExchange, RN> : mode == 1 ? mm8_cluster_kernel<float, 1, NoExchange, RN> : mm8_cluster_kernel<float, 0, NoExchange, RN>;
+    const int smem = wide ? cluster_smem<RW>() : cluster_smem<RN>();
+    if ((exch ? cudaFuncSetAttribute(kern_x, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+              : cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) {
         cudaGetLastError();
         return RWKV_ERR_UNSUPPORTED;
     }
-    const int slots = cluster_slots(kern, S, smem);
+    const int slots = exch ? cluster_slots(kern_x, S, smem) : cluster_slots(kern, S, smem);
     if (slots <= 0) return RWKV_ERR_UNSUPPORTED;
 
     // Panel width: the narrowest multiple of 16 columns with which one wave of clusters covers
@@ -533,7 +603,7 @@ static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, 
 #ifdef RWKV_MM8_TRACE
     cb.trace_id = g_mm8_trace_next++;
 #endif
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, cb);
+    cudaError_t e = exch ? cudaLaunchKernelEx(&cfg, kern_x, cb, *exch) : cudaLaunchKernelEx(&cfg, kern, cb, NoExchange{0});
     if (e != cudaSuccess) { cudaGetLastError(); return RWKV_ERR_LAUNCH; }
     return RWKV_OK;
 }

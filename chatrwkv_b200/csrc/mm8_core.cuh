@@ -9,6 +9,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxRowsPerCta = 2048; // x' slice kept in shared memory
+constexpr int kWideRowsPerCta = 2560; // the cluster kernel's second build: 20480 in-features (14B shape) / 8 splits
 constexpr int kMaxSplit = 64;
 constexpr int kPanelMin = 128;
 constexpr int kCounterBytes = 4096;  // panel tickets; the last two words belong to the chain kernel
@@ -167,9 +168,10 @@ __device__ __forceinline__ void dot16_q(int (&acc)[16], const uint4& va, const u
 // p * rpp + sub holds rows sub + 2p*rpp (low) and sub + (2p+1)*rpp (high), the two rows that the
 // thread with row offset `sub` multiplies in its p-th pair; rows past nrows are 0.  `npairs` pairs
 // per row offset (whole ring groups).  The thread with chunk index `ch` (of `cpr`) makes the pairs
-// p = ch, ch + cpr, ... of its own row offset, at most 8 of them.  Returns 1/scale (value = q /
+// p = ch, ch + cpr, ... of its own row offset, at most NP of them.  Returns 1/scale (value = q /
 // scale); the quantisation range is the largest that keeps a thread's 32-bit sums of `nsteps`
 // products q * 255 from overflowing (32767 up to 257 steps).
+template <int NP>   // pairs per thread at most: 8 up to 2048 rows per CTA, 10 up to 2560
 __device__ __forceinline__ float quantize_pairs(float* xs, int nrows, int rpp, int cpr, int sub, int ch, bool active,
                                                 int npairs, int nsteps, float* sh8) {
     const int tid = threadIdx.x;
@@ -185,9 +187,9 @@ __device__ __forceinline__ float quantize_pairs(float* xs, int nrows, int rpp, i
     const int qmax = min(32767, 0x7fffffff / (255 * max(nsteps, 1)));
     const bool finite = m < 3.0e38f;            // false for inf and NaN
     const float scale = (finite && m > 0.f) ? float(qmax) / m : 0.f;
-    float fa[8], fb[8];
+    float fa[NP], fb[NP];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < NP; ++i) {
         const int p = ch + i * cpr;
         fa[i] = fb[i] = 0.f;
         if (active && p < npairs) {
@@ -199,7 +201,7 @@ __device__ __forceinline__ float quantize_pairs(float* xs, int nrows, int rpp, i
     __syncthreads();
     int* xp = reinterpret_cast<int*>(xs);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < NP; ++i) {
         const int p = ch + i * cpr;
         if (active && p < npairs) {
             const int qa = __float2int_rn(fa[i] * scale), qb = __float2int_rn(fb[i] * scale);

@@ -279,6 +279,11 @@ extern "C" size_t rwkv_mm8_one_batch_workspace_bytes(const rwkv_mm8_problem* pro
 
 extern "C" int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, int dtype,
                                   void* workspace, size_t workspace_bytes, void* stream) {
+    return rwkv_mm8_one_batch_exchange(problems, count, nullptr, dtype, workspace, workspace_bytes, stream);
+}
+
+extern "C" int rwkv_mm8_one_batch_exchange(const rwkv_mm8_problem* problems, int count, const rwkv_mm8_exchange* exchange,
+                                           int dtype, void* workspace, size_t workspace_bytes, void* stream) {
     LaunchPlan plan;
     static const int max_rows[3] = {kMaxRowsPerCta, kMaxRowsPerCta, kMaxRowsPerCta};
     const int force_pw = (g_variant & 3) != 0 ? (1024 >> (g_variant & 3)) : 0;
@@ -287,13 +292,35 @@ extern "C" int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, i
     if (rc != RWKV_OK) return rc;
     const int pw = plan.pw;
     const bool aligned = plan.aligned, packed = (g_variant & 4) == 0;
+    Exchange ex;
+    const Exchange* exp = nullptr;
+    if (exchange != nullptr) {
+        // results also go to the other ranks; only the cluster kernel does that
+        const rwkv_mm8_exchange& q = *exchange;
+        RWKV_CHECK_ARG(q.world >= 2 && q.world <= 8 && q.rank >= 0 && q.rank < q.world);
+        RWKV_CHECK_ARG(q.arrived && q.done_counter && q.error && q.signal_seq != 0);
+        memset(&ex, 0, sizeof(ex));
+        ex.n_peers = q.world - 1;
+        for (int pr = 0; pr < ex.n_peers; ++pr) {
+            RWKV_CHECK_ARG(q.peer_arrived[pr] != nullptr);
+            ex.peer_arrived[pr] = q.peer_arrived[pr];
+            for (int z = 0; z < count; ++z) {
+                RWKV_CHECK_ARG(q.peer_y[z][pr] != nullptr && problems[z].epilogue != RWKV_EPI_ACC_F32);
+                ex.peer_y[z][pr] = q.peer_y[z][pr];
+            }
+        }
+        ex.arrived = q.arrived; ex.done_counter = q.done_counter; ex.error = q.error;
+        ex.wait_seq = q.wait_seq; ex.signal_seq = q.signal_seq; ex.world = q.world; ex.rank = q.rank;
+        exp = &ex;
+    }
     if (aligned && (g_variant & 3) == 0 && g_split_override == 0) {
         // K-splits of a panel as one thread-block cluster (mm8_cluster.cuh); falls through to the
         // ticket kernel when the batch is not eligible.
-        const int crc = mm8_cluster_launch(plan.b, count, dtype, (g_variant & 4) ? 0 : (g_variant & 8) ? 1 : 2,
+        const int crc = mm8_cluster_launch(plan.b, count, dtype, (g_variant & 4) ? 0 : (g_variant & 8) ? 1 : 2, exp,
                                            static_cast<cudaStream_t>(stream));
         if (crc != RWKV_ERR_UNSUPPORTED) return crc;
     }
+    if (exp != nullptr) return RWKV_ERR_UNSUPPORTED;
     void (*kern)(Batch) = nullptr;
 #define RWKV_PICK(FT)                                                                                        \
     if (!aligned) kern = pw == 512 ? mm8_one_kernel<FT, 32, false, false, 4>                                \

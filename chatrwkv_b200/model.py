@@ -238,6 +238,19 @@ class RWKV:
             logits=torch.zeros(self._full_m.get("head.weight", self.w["head.weight"].shape[1]), dtype=torch.float32,
                                device=dev),
             tok=torch.zeros(1, dtype=torch.int64, device=dev))
+        # Column-sharded decode: the gathered activation buffers live in a region that the other
+        # ranks have mapped, and the matmul kernels store their column slices into every rank's copy
+        # (RWKV_B200_SHARD_EXCHANGE=nccl keeps the all-gather calls between the launches instead).
+        self._peer = None
+        if self._world > 1 and os.environ.get("RWKV_B200_SHARD_EXCHANGE", "peer") == "peer" and \
+                torch.distributed.get_backend() == "nccl":
+            bb = self._b
+            fields = [("x", torch.float16, D), ("r", torch.float16, a.n_att), ("k", torch.float16, a.n_att),
+                      ("v", torch.float16, a.n_att), ("fr", torch.float16, D), ("fk", torch.float16, Fn),
+                      ("logits", torch.float32, bb.logits.numel())]
+            self._peer = shard.PeerRegion(fields, dev, self._world, self._rank)
+            for name, _, _ in fields:
+                setattr(bb, name, self._peer.view(name))
         self._tok_host = torch.zeros(256, dtype=torch.int64).pin_memory()   # ring of H2D staging slots
         self._tok_slot = 0
         self._ws = torch.zeros(96 << 20, dtype=torch.uint8, device=dev)
@@ -268,8 +281,8 @@ class RWKV:
         wq, mx, rx, my, ry = self._scales(name)
         return ops.make_problem(x, wq, mx, rx, my, ry, y, epi, aux, aux2, out_scale)
 
-    def _gemv(self, problems):
-        ops.mm8_one_batch(problems, torch.float16, self.device, self._ws)
+    def _gemv(self, problems, exchange=None):
+        ops.mm8_one_batch(problems, torch.float16, self.device, self._ws, exchange)
 
     def _ln_mix(self, T, x, sx, ln_w, ln_b, mode, mixes, outs, xx_out=None, new_state=None, mix_stride=0):
         D = self.args.n_embd
@@ -341,7 +354,8 @@ class RWKV:
             self._tok_host[slot] = token
             self._b.tok.copy_(self._tok_host[slot:slot + 1], non_blocking=True)
         if self.version == 4:
-            step = self._step_one_v4_sharded if self._world > 1 else self._step_one_v4
+            step = (self._step_one_v4_peer if self._peer is not None else self._step_one_v4_sharded) \
+                if self._world > 1 else self._step_one_v4
         else:
             step = self._step_one_v56
         cur = self._cur
@@ -468,6 +482,49 @@ class RWKV:
         ll = loc("logits", b.logits.numel(), torch.float32)
         run([ln(P(b.x, "head.weight", ll, EPI_STORE_F32), w["ln_out.weight"], w["ln_out.bias"], 2)])
         gather([(b.logits, ll)])
+
+    def _step_one_v4_peer(self, cur):
+        """One RWKV-4 token with every matmul split by output columns over the ranks and NO
+        collective call: each launch stores its column slice into every rank's copy of the
+        activation buffer (peer stores over NVLink from the epilogue) and the next launch waits on
+        per-rank arrival words (csrc/mm8_cluster.cuh, Exchange).  Same four launches per layer as
+        `_launches_v4`; every rank keeps the full recurrent state."""
+        b, w, a, pr = self._b, self.w, self.args, self._peer
+        G, R = self._world, self._rank
+        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
+        sin, sout = self._st[cur], self._st[1 - cur]
+        P, ln, wk = self._problem, ops.with_ln_mix, ops.with_wkv4
+        D, Fn = a.n_embd, a.n_ffn
+        ld, hd = shard.column_range(D, G, R)
+        la, ha = shard.column_range(a.n_att, G, R)
+        lf, hf = shard.column_range(Fn, G, R)
+        lv, hv = shard.column_range(b.logits.numel(), G, R)
+        for i in range(a.n_layer):
+            bb, att, ffn = f"blocks.{i}.", f"blocks.{i}.att.", f"blocks.{i}.ffn."
+            ln1 = (w[bb + "ln1.weight"], w[bb + "ln1.bias"])
+            ln2 = (w[bb + "ln2.weight"], w[bb + "ln2.bias"])
+            s = i * 5
+            self._gemv([ln(P(b.x, att + "receptance.weight", b.r[la:ha], EPI_SIGMOID), *ln1, 0, sin[s], w[att + "time_mix_r"], sout[s]),
+                        ln(P(b.x, att + "key.weight", b.k[la:ha], EPI_STORE), *ln1, 0, sin[s], w[att + "time_mix_k"]),
+                        ln(P(b.x, att + "value.weight", b.v[la:ha], EPI_STORE), *ln1, 0, sin[s], w[att + "time_mix_v"])],
+                       pr.exchange([("r", la), ("k", la), ("v", la)], wait=i > 0))
+            self._gemv([wk(P(b.r, att + "output.weight", b.x[ld:hd], EPI_RESIDUAL, aux=b.x[ld:hd]), b.k, b.v,
+                           w[att + "time_decay"], w[att + "time_first"], sin[s + 1:s + 4], sout[s + 1:s + 4])],
+                       pr.exchange([("x", ld)], wait=True))
+            self._gemv([ln(P(b.x, ffn + "receptance.weight", b.fr[ld:hd], EPI_SIGMOID), *ln2, 0, sin[s + 4], w[ffn + "time_mix_r"], sout[s + 4]),
+                        ln(P(b.x, ffn + "key.weight", b.fk[lf:hf], EPI_RELU_SQ), *ln2, 0, sin[s + 4], w[ffn + "time_mix_k"])],
+                       pr.exchange([("fr", ld), ("fk", lf)], wait=True))
+            scale = 0.5 if (self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0) else 1.0
+            self._gemv([P(b.fk, ffn + "value.weight", b.x[ld:hd], EPI_MUL_RESIDUAL, aux=b.x[ld:hd], aux2=b.fr[ld:hd],
+                          out_scale=scale)], pr.exchange([("x", ld)], wait=True))
+        self._gemv([ln(P(b.x, "head.weight", b.logits[lv:hv], EPI_STORE_F32), w["ln_out.weight"], w["ln_out.bias"], 2)],
+                   pr.exchange([("logits", lv)], wait=True))
+        pr.wait_all(torch.cuda.current_stream(self.device).cuda_stream)      # every rank's logits slice is here
+
+    def peer_error(self):
+        """1 if a wait on another rank's arrival word gave up since the last call (results were
+        then undefined); synchronises the device."""
+        return self._peer.take_error() if self._peer is not None else 0
 
     def _step_one_v4(self, cur):
         b, w = self._b, self.w

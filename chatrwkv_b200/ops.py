@@ -246,11 +246,18 @@ def with_wkv4(p, k, v, t_decay, t_first, state_in, state_out):
     return p
 
 
-def mm8_one_batch(problems, dtype, device, ws=None):
-    """One launch for 1..3 GEMVs with fused epilogues.  `ws`: zero-initialised uint8 scratch
-    owned by the caller (needed under stream capture); default: the per-stream workspace."""
+def mm8_one_batch(problems, dtype, device, ws=None, exchange=None):
+    """One launch for 1..4 GEMVs with fused epilogues.  `ws`: zero-initialised uint8 scratch
+    owned by the caller (needed under stream capture); default: the per-stream workspace.
+    `exchange` (an `_lib.Mm8Exchange`): column-sharded launch that also stores its results into
+    the other ranks' buffers (shard.PeerRegion.exchange)."""
+    import ctypes as C
     n = len(problems)
     arr = (Mm8Problem * n)(*problems)
     if ws is None:
         ws = workspace(device, lib().rwkv_mm8_one_batch_workspace_bytes(arr, n))
-    check(lib().rwkv_mm8_one_batch(arr, n, _DT[dtype], ws.data_ptr(), ws.numel(), _stream(device)), "mm8_one_batch")
+    if exchange is None:
+        check(lib().rwkv_mm8_one_batch(arr, n, _DT[dtype], ws.data_ptr(), ws.numel(), _stream(device)), "mm8_one_batch")
+    else:
+        check(lib().rwkv_mm8_one_batch_exchange(arr, n, C.byref(exchange), _DT[dtype], ws.data_ptr(), ws.numel(),
+                                                _stream(device)), "mm8_one_batch_exchange")

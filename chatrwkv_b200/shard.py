@@ -74,3 +74,106 @@ def gather_columns(local, M, world, group=None):
         return out.reshape(world * mw)[:M]
     perm = list(range(1, len(lead) + 1)) + [0, len(lead) + 1]
     return out.permute(*perm).reshape(*lead, world * mw)[..., :M]
+
+
+class _RawCuda:
+    """A span of device memory owned elsewhere, presented through __cuda_array_interface__."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class PeerRegion:
+    """One region of device memory per rank, laid out identically everywhere and mapped by every
+    other rank (CUDA IPC over NVLink): the activation buffers of the column-sharded decode and
+    the arrival words of its launches.  `fields` = [(name, dtype, numel)].  `view(name)` is this
+    rank's tensor, `peer_ptr(name, other)` the address of the same buffer on rank `other`.
+
+    The matmul kernels store into the peers' regions themselves (rwkv_mm8_one_batch_exchange);
+    torch.distributed is used once, here, to pass the 64-byte handles around."""
+
+    FLAG_WORDS = 64
+
+    def __init__(self, fields, device, world, rank, group=None):
+        import ctypes as C
+        from . import _lib
+        L = _lib.lib()
+        self.world, self.rank, self.device = world, rank, device
+        self.offsets, off = {}, 0
+        for name, dtype, numel in fields:
+            self.offsets[name] = (off, dtype, numel)
+            off += (numel * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256
+        self.flag_off = off
+        off += self.FLAG_WORDS * 4
+        self.nbytes = (off + 255) // 256 * 256
+        with torch.cuda.device(device):
+            p = C.c_void_p()
+            _lib.check(L.rwkv_peer_alloc(self.nbytes, C.byref(p)), "peer_alloc")
+            self.base = p.value
+            handle = (C.c_ubyte * _lib.PEER_HANDLE_BYTES)()
+            _lib.check(L.rwkv_peer_export(self.base, handle), "peer_export")
+            mine = torch.tensor(list(handle), dtype=torch.uint8, device=device)
+            allh = torch.empty(world * _lib.PEER_HANDLE_BYTES, dtype=torch.uint8, device=device)
+            dist.all_gather_into_tensor(allh, mine, group=group)
+            allh = allh.cpu().view(world, -1)
+            self.bases = []
+            for r in range(world):
+                if r == rank:
+                    self.bases.append(self.base)
+                    continue
+                h = (C.c_ubyte * _lib.PEER_HANDLE_BYTES)(*allh[r].tolist())
+                q = C.c_void_p()
+                _lib.check(L.rwkv_peer_open(h, C.byref(q)), "peer_open")
+                self.bases.append(q.value)
+            self._bytes = torch.as_tensor(_RawCuda(self.base, self.nbytes), device=device)
+        dist.barrier(group=group)
+        self.others = [r for r in range(world) if r != rank]
+        self.seq = 0
+
+    def view(self, name):
+        off, dtype, numel = self.offsets[name]
+        es = torch.empty((), dtype=dtype).element_size()
+        return self._bytes[off:off + numel * es].view(dtype)
+
+    def peer_ptr(self, name, other, elem_offset=0):
+        off, dtype, _ = self.offsets[name]
+        return self.bases[other] + off + elem_offset * torch.empty((), dtype=dtype).element_size()
+
+    # arrival words: word r of a rank = sequence number of the last launch of rank r whose results
+    # have all arrived there; word FLAG_WORDS-2 = done counter, FLAG_WORDS-1 = error
+    def arrived_ptr(self, on_rank, word=0):
+        return self.bases[on_rank] + self.flag_off + 4 * word
+
+    def exchange(self, y_names_and_offsets, wait):
+        """The rwkv_mm8_exchange of the next launch.  `y_names_and_offsets`: per problem
+        (buffer name, element offset of its y inside the buffer); `wait`: whether the launch's
+        inputs include results of the previous launch of the other ranks."""
+        from . import _lib
+        e = _lib.Mm8Exchange()
+        for z, (name, eo) in enumerate(y_names_and_offsets):
+            for i, r in enumerate(self.others):
+                e.peer_y[z][i] = self.peer_ptr(name, r, eo)
+        e.arrived = self.arrived_ptr(self.rank)
+        for i, r in enumerate(self.others):
+            e.peer_arrived[i] = self.arrived_ptr(r, self.rank)
+        e.done_counter = self.arrived_ptr(self.rank, self.FLAG_WORDS - 2)
+        e.error = self.arrived_ptr(self.rank, self.FLAG_WORDS - 1)
+        e.wait_seq = self.seq if wait else 0
+        self.seq += 1
+        e.signal_seq = self.seq
+        e.world, e.rank = self.world, self.rank
+        return e
+
+    def wait_all(self, stream):
+        """Enqueue a wait until the results of every rank's last launch have arrived here."""
+        from . import _lib
+        _lib.check(_lib.lib().rwkv_peer_wait(self.arrived_ptr(self.rank), self.world, self.seq,
+                                             self.arrived_ptr(self.rank, self.FLAG_WORDS - 1), stream), "peer_wait")
+
+    def take_error(self):
+        torch.cuda.synchronize(self.device)
+        w = self._bytes[self.flag_off:self.flag_off + 4 * self.FLAG_WORDS].view(torch.int32)
+        e = int(w[self.FLAG_WORDS - 1].item())
+        if e:
+            w[self.FLAG_WORDS - 1] = 0
+        return e

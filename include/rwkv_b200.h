@@ -191,6 +191,38 @@ typedef struct rwkv_mm8_problem {
 size_t rwkv_mm8_one_batch_workspace_bytes(const rwkv_mm8_problem* problems, int count);
 int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, int dtype,
                        void* workspace, size_t workspace_bytes, void* stream);
+/* ---------------------------------------------------------------------------------------
+ * Column-sharded decode over several GPUs (one process per GPU; no counterpart in the reference,
+ * whose only multi-device feature places whole layers, pkg/model.py:684-749).  Every rank holds
+ * the columns [lo, hi) of each packed matrix and a full copy of every activation buffer in a
+ * region of device memory that the other ranks have mapped (rwkv_peer_*).  A launch made with
+ * rwkv_mm8_one_batch_exchange stores its results into its own buffers AND into the same place of
+ * every other rank's (peer_y), then publishes `signal_seq` in each rank's arrival word for this
+ * rank; before touching its inputs it waits (bounded, ~0.1 s) until all `world` arrival words of
+ * its own rank have reached `wait_seq` (0: no wait).  Sequence numbers grow by one per launch and
+ * must be the same on every rank.  RWKV_ERR_UNSUPPORTED if the launch cannot use the cluster
+ * kernel (fp16, aligned rows, integer arithmetic).  Not for stream capture: the numbers change
+ * per call.
+ * ------------------------------------------------------------------------------------- */
+#define RWKV_PEER_HANDLE_BYTES 64
+typedef struct {
+    void* peer_y[4][7];        /* [problem][other rank]: that rank's address of problem.y */
+    uint32_t* arrived;         /* this rank's arrival words, one per rank [world] */
+    uint32_t* peer_arrived[7]; /* on each other rank: the address of ITS arrival word for this rank */
+    uint32_t* done_counter;    /* one zeroed word of this rank's memory (left zero) */
+    uint32_t* error;           /* one word of this rank's memory; set to 1 when a wait gives up */
+    uint32_t wait_seq, signal_seq;
+    int32_t world, rank;
+} rwkv_mm8_exchange;
+int rwkv_mm8_one_batch_exchange(const rwkv_mm8_problem* problems, int count, const rwkv_mm8_exchange* exchange,
+                                int dtype, void* workspace, size_t workspace_bytes, void* stream);
+int rwkv_peer_alloc(size_t bytes, void** ptr_out);          /* zeroed device memory that can be exported */
+int rwkv_peer_free(void* ptr);
+int rwkv_peer_export(const void* ptr, void* handle_out);    /* RWKV_PEER_HANDLE_BYTES bytes for another process */
+int rwkv_peer_open(const void* handle, void** ptr_out);     /* map another process's region (peer access over NVLink) */
+int rwkv_peer_close(void* ptr);
+int rwkv_peer_wait(const uint32_t* arrived, int world, uint32_t seq, uint32_t* error, void* stream);
+
 /* Tuning hooks (process-wide, not thread-safe).  split: force the number of K-splits
  * (0 = automatic).  variant: bits 0-1 force the panel width (1 = 512, 2 = 256, 3 = 128
  * columns, 0 = automatic); bit 2 switches the two-wide fp32 arithmetic off. */

@@ -1,5 +1,6 @@
-"""Column-sharded RWKV-4 on two GPUs (one process per GPU, NCCL all-gather of the output
-slices) against the single-GPU model: same logits up to the fp32 summation order."""
+"""Column-sharded RWKV-4 on two GPUs (one process per GPU) against the single-GPU model: same
+logits up to the fp32 summation order.  Two ways of exchanging the output slices: peer stores from
+the matmul epilogue with arrival words (the default) and NCCL all-gather calls between launches."""
 import copy
 import os
 
@@ -11,7 +12,8 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, ret, mode):
+    os.environ["RWKV_B200_SHARD_EXCHANGE"] = mode
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -23,6 +25,7 @@ def _worker(rank, world, port, ret):
         ck = synth.make_checkpoint(4, n_layer=7, n_embd=256, n_ffn=1024, vocab=1000, seed=3)
         toks = synth.make_tokens(10, 1000, 4)
         m = RWKV(copy.deepcopy(ck), f"cuda:{rank} fp16i8", verbose=False, shard_rank=rank, shard_world=world)
+        assert (m._peer is not None) == (mode == "peer")
         outs = []
         lg, st = m.forward(toks[:6], None)
         outs.append(lg.cpu())
@@ -37,16 +40,19 @@ def _worker(rank, world, port, ret):
                 lg, st = ref.forward([t], st)
                 worst = max(worst, (lg.cpu() - outs[i + 1]).abs().max().item())
             ret["worst"] = worst
+        ret[f"peer_error{rank}"] = m.peer_error()
         dist.barrier()
     finally:
         dist.destroy_process_group()
 
 
-def test_two_gpu_column_sharded_matches_single_gpu():
+@pytest.mark.parametrize("mode", ["peer", "nccl"])
+def test_two_gpu_column_sharded_matches_single_gpu(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    port = 29600 + (os.getpid() % 2000)
+    port = 29600 + (os.getpid() % 2000) + (7 if mode == "nccl" else 0)
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
+        mp.spawn(_worker, args=(2, port, ret, mode), nprocs=2, join=True)
         assert ret["worst"] < 4e-3, ret["worst"]
+        assert ret["peer_error0"] == 0 and ret["peer_error1"] == 0
