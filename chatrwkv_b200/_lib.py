@@ -42,7 +42,7 @@ class Mm8Exchange(C.Structure):
     _fields_ = [
         ("peer_y", (C.c_void_p * 7) * 4),
         ("arrived", C.c_void_p), ("peer_arrived", C.c_void_p * 7),
-        ("done_counter", C.c_void_p), ("error", C.c_void_p),
+        ("done_counter", C.c_void_p), ("error", C.c_void_p), ("seq_base", C.c_void_p),
         ("wait_seq", C.c_uint32), ("signal_seq", C.c_uint32),
         ("world", C.c_int32), ("rank", C.c_int32),
     ]
@@ -68,7 +68,8 @@ SIGNATURES = {
     "rwkv_peer_export": (_i32, [_vp, _vp]),
     "rwkv_peer_open": (_i32, [_vp, C.POINTER(_vp)]),
     "rwkv_peer_close": (_i32, [_vp]),
-    "rwkv_peer_wait": (_i32, [_vp, _i32, C.c_uint32, _vp, _vp]),
+    "rwkv_peer_wait": (_i32, [_vp, _i32, C.c_uint32, _vp, _vp, _vp]),
+    "rwkv_peer_advance": (_i32, [_vp, C.c_uint32, _vp]),
     "rwkv_mm8_one_set_split": (None, [_i32]),
     "rwkv_mm8_one_set_variant": (None, [_i32]),
     "rwkv_mm8_one_set_cluster": (None, [_i32, _i32]),

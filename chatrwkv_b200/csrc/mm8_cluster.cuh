@@ -61,6 +61,7 @@ struct Exchange {
     unsigned* peer_arrived[7];   // on each other rank: its arrival word for this rank
     unsigned* done_counter;
     unsigned* error;
+    const unsigned* seq_base;    // added to wait_seq / signal_seq (device word; lets a captured graph be replayed)
     unsigned wait_seq, signal_seq;
     int world, rank, n_peers;
 };
@@ -168,14 +169,16 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
     if constexpr (kExch) {
         // the other ranks' slices of this launch's inputs: wait for their arrival words (bounded)
         if (ex.wait_seq != 0 && tid < ex.world) {
+            const unsigned want = ex.wait_seq + (ex.seq_base ? __ldcg(ex.seq_base) : 0u);
             unsigned it = 0;
             while (true) {
                 unsigned v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ex.arrived + tid) : "memory");
-                if (int(v - ex.wait_seq) >= 0) break;
+                asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ex.arrived + tid) : "memory");
+                if (int(v - want) >= 0) break;
                 if (++it >= kPeerSpinLimit) { atomicExch(ex.error, 1u); break; }
-                __nanosleep(64);
+                __nanosleep(32);
             }
+            __threadfence_system();              // acquire: what the ranks stored before their words is visible
         }
         __syncthreads();
     }
@@ -446,27 +449,44 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
         }
         const float val = fmaf(rxk, s, fmaf(rxk * 128.5f, txr, fmaf(mxk, tx, txmy)));
         store_epilogue_with<F>(P, k, val, auxv, aux2v);
-        if constexpr (kExch) {                   // the same value into every other rank's buffer
-            if (P.epilogue == RWKV_EPI_STORE_F32) {
-                const float o = static_cast<const float*>(P.y)[k];
-                for (int pr = 0; pr < ex.n_peers; ++pr) static_cast<float*>(ex.peer_y[z][pr])[k] = o;
-            } else {
-                const F o = static_cast<const F*>(P.y)[k];
-                for (int pr = 0; pr < ex.n_peers; ++pr) static_cast<F*>(ex.peer_y[z][pr])[k] = o;
-            }
-        }
     }
     if constexpr (kExch) {
-        __threadfence_system();                  // this thread's peer stores, before the CTA reports
+        // The last CTA of the launch to finish forwards the launch's results to the other ranks:
+        // wide stores over NVLink, ONE system-scope fence, then the arrival words.  (A fence per
+        // CTA, with every CTA storing its own columns remotely, cost ~12 us per launch.)
+        __shared__ unsigned s_last;
         __syncthreads();
         if (tid == 0) {
-            const unsigned t = atomicAdd(ex.done_counter, 1u);
-            if (t == gridDim.x - 1) {            // last CTA of the launch: everything is out
+            __threadfence();                     // this CTA's results, before it reports
+            s_last = atomicAdd(ex.done_counter, 1u) == gridDim.x - 1 ? 1u : 0u;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();                     // every CTA's results are visible here
+            for (int zz = 0; zz < kMaxProblems && b.panel_start[zz] < b.panel_start[kMaxProblems]; ++zz) {
+                if (b.panel_start[zz + 1] == b.panel_start[zz]) continue;
+                const Problem& Q = b.p[zz];
+                const int es = Q.epilogue == RWKV_EPI_STORE_F32 ? 4 : int(sizeof(F));
+                const long long bytes = (long long)Q.M * es;
+                const char* src = static_cast<const char*>(Q.y);
+                const bool vec = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+                const long long nv = vec ? bytes >> 4 : 0;
+                for (int pr = 0; pr < ex.n_peers; ++pr) {
+                    char* dst = static_cast<char*>(ex.peer_y[zz][pr]);          // same offset on the peer: same alignment
+                    for (long long i = tid; i < nv; i += kThreads)
+                        reinterpret_cast<uint4*>(dst)[i] = __ldcg(reinterpret_cast<const uint4*>(src) + i);
+                    for (long long o = nv * 16 + 2 * tid; o < bytes; o += 2 * kThreads)
+                        *reinterpret_cast<uint16_t*>(dst + o) = __ldcg(reinterpret_cast<const uint16_t*>(src + o));
+                }
+            }
+            __syncthreads();
+            if (tid == 0) {
                 atomicExch(ex.done_counter, 0u);
-                __threadfence_system();
+                __threadfence_system();          // the forwarded results, system-wide, before the words
+                const unsigned sig = ex.signal_seq + (ex.seq_base ? __ldcg(ex.seq_base) : 0u);
                 for (int pr = 0; pr < ex.n_peers; ++pr)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ex.peer_arrived[pr]), "r"(ex.signal_seq) : "memory");
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ex.arrived + ex.rank), "r"(ex.signal_seq) : "memory");
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ex.peer_arrived[pr]), "r"(sig) : "memory");
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ex.arrived + ex.rank), "r"(sig) : "memory");
             }
         }
     }

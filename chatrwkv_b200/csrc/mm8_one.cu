@@ -310,6 +310,7 @@ extern "C" int rwkv_mm8_one_batch_exchange(const rwkv_mm8_problem* problems, int
             }
         }
         ex.arrived = q.arrived; ex.done_counter = q.done_counter; ex.error = q.error;
+        ex.seq_base = q.seq_base;
         ex.wait_seq = q.wait_seq; ex.signal_seq = q.signal_seq; ex.world = q.world; ex.rank = q.rank;
         exp = &ex;
     }

@@ -10,9 +10,10 @@ namespace {
 constexpr unsigned kWaitSpinLimit = 1u << 21;
 
 // One warp: lane r waits (bounded) until arrival word r has reached `seq`.
-__global__ void peer_wait_kernel(const unsigned* arrived, int world, unsigned seq, unsigned* error) {
+__global__ void peer_wait_kernel(const unsigned* arrived, int world, unsigned seq, const unsigned* seq_base, unsigned* error) {
     const int r = threadIdx.x;
     if (r < world) {
+        if (seq_base != nullptr) seq += __ldcg(seq_base);
         unsigned it = 0;
         while (true) {
             unsigned v;
@@ -23,6 +24,8 @@ __global__ void peer_wait_kernel(const unsigned* arrived, int world, unsigned se
         }
     }
 }
+
+__global__ void peer_advance_kernel(unsigned* seq_base, unsigned add) { *seq_base += add; }
 
 }  // namespace
 
@@ -65,9 +68,18 @@ extern "C" int rwkv_peer_close(void* ptr) {
     return RWKV_OK;
 }
 
-// Enqueue a wait (bounded; sets *error on giving up) until every rank's arrival word has reached seq.
-extern "C" int rwkv_peer_wait(const uint32_t* arrived, int world, uint32_t seq, uint32_t* error, void* stream) {
+// Enqueue a wait (bounded; sets *error on giving up) until every rank's arrival word has reached
+// seq (+ *seq_base when given).
+extern "C" int rwkv_peer_wait(const uint32_t* arrived, int world, uint32_t seq, const uint32_t* seq_base, uint32_t* error,
+                              void* stream) {
     RWKV_CHECK_ARG(arrived != nullptr && error != nullptr && world >= 1 && world <= 32);
-    peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(arrived, world, seq, error);
+    peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(arrived, world, seq, seq_base, error);
+    return rwkv_launch_status();
+}
+
+// *seq_base += add, in stream order (one per token of a replayed graph).
+extern "C" int rwkv_peer_advance(uint32_t* seq_base, uint32_t add, void* stream) {
+    RWKV_CHECK_ARG(seq_base != nullptr);
+    peer_advance_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(seq_base, add);
     return rwkv_launch_status();
 }

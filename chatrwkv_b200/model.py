@@ -207,9 +207,11 @@ class RWKV:
                         raise ValueError(f"{x}: {w[x].shape[1]} columns are too few for {self._world} ranks")
                     w[x], w[x + "_mx"], w[x + "_rx"] = shard.column_shard(w[x], w[x + "_mx"], w[x + "_rx"],
                                                                          self._world, self._rank)
-                # collectives between the launches: direct launches (capturing the NCCL all-gathers of a
-                # step into a CUDA graph did not return on the B200 pool; it is not attempted)
-                self._use_graph = False
+                # NCCL all-gathers between the launches: direct launches only (capturing them into a CUDA
+                # graph did not return on the B200 pool; it is not attempted).  The peer-store exchange
+                # has no collective call and is captured like the single-GPU step.
+                self._use_graph = self._use_graph and os.environ.get("RWKV_B200_SHARD_EXCHANGE", "peer") == "peer" \
+                    and torch.distributed.get_backend() == "nccl"
                 torch.cuda.empty_cache()
             self._init_buffers()
         gc.collect()
@@ -491,6 +493,8 @@ class RWKV:
         `_launches_v4`; every rank keeps the full recurrent state."""
         b, w, a, pr = self._b, self.w, self.args, self._peer
         G, R = self._world, self._rank
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        pr.begin_token(4 * a.n_layer + 1, stream)
         torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
         sin, sout = self._st[cur], self._st[1 - cur]
         P, ln, wk = self._problem, ops.with_ln_mix, ops.with_wkv4
@@ -519,7 +523,7 @@ class RWKV:
                           out_scale=scale)], pr.exchange([("x", ld)], wait=True))
         self._gemv([ln(P(b.x, "head.weight", b.logits[lv:hv], EPI_STORE_F32), w["ln_out.weight"], w["ln_out.bias"], 2)],
                    pr.exchange([("logits", lv)], wait=True))
-        pr.wait_all(torch.cuda.current_stream(self.device).cuda_stream)      # every rank's logits slice is here
+        pr.end_token(stream)                     # every rank's logits slice is here
 
     def peer_error(self):
         """1 if a wait on another rank's arrival word gave up since the last call (results were

@@ -140,12 +140,22 @@ class PeerRegion:
         return self.bases[other] + off + elem_offset * torch.empty((), dtype=dtype).element_size()
 
     # arrival words: word r of a rank = sequence number of the last launch of rank r whose results
-    # have all arrived there; word FLAG_WORDS-2 = done counter, FLAG_WORDS-1 = error
+    # have all arrived there; word FLAG_WORDS-3 = sequence base, FLAG_WORDS-2 = done counter, FLAG_WORDS-1 = error
     def arrived_ptr(self, on_rank, word=0):
         return self.bases[on_rank] + self.flag_off + 4 * word
 
+    # A token's launches are numbered 1..n relative to the device word `seq_base`, which
+    # `begin_token` advances by n in stream order: the numbers a launch carries are the same for
+    # every token, so a captured graph can be replayed.
+    def begin_token(self, n_launches, stream):
+        from . import _lib
+        self._rel = 0
+        self._n = n_launches
+        _lib.check(_lib.lib().rwkv_peer_advance(self.arrived_ptr(self.rank, self.FLAG_WORDS - 3), n_launches, stream),
+                   "peer_advance")
+
     def exchange(self, y_names_and_offsets, wait):
-        """The rwkv_mm8_exchange of the next launch.  `y_names_and_offsets`: per problem
+        """The rwkv_mm8_exchange of the token's next launch.  `y_names_and_offsets`: per problem
         (buffer name, element offset of its y inside the buffer); `wait`: whether the launch's
         inputs include results of the previous launch of the other ranks."""
         from . import _lib
@@ -158,16 +168,20 @@ class PeerRegion:
             e.peer_arrived[i] = self.arrived_ptr(r, self.rank)
         e.done_counter = self.arrived_ptr(self.rank, self.FLAG_WORDS - 2)
         e.error = self.arrived_ptr(self.rank, self.FLAG_WORDS - 1)
-        e.wait_seq = self.seq if wait else 0
-        self.seq += 1
-        e.signal_seq = self.seq
+        e.seq_base = self.arrived_ptr(self.rank, self.FLAG_WORDS - 3)
+        # before the first token seq_base is n (advanced once), so numbers start at n + 1 > 0
+        e.wait_seq = self._rel if wait else 0
+        self._rel += 1
+        e.signal_seq = self._rel
         e.world, e.rank = self.world, self.rank
         return e
 
-    def wait_all(self, stream):
+    def end_token(self, stream):
         """Enqueue a wait until the results of every rank's last launch have arrived here."""
         from . import _lib
-        _lib.check(_lib.lib().rwkv_peer_wait(self.arrived_ptr(self.rank), self.world, self.seq,
+        assert self._rel == self._n, (self._rel, self._n)
+        _lib.check(_lib.lib().rwkv_peer_wait(self.arrived_ptr(self.rank), self.world, self._rel,
+                                             self.arrived_ptr(self.rank, self.FLAG_WORDS - 3),
                                              self.arrived_ptr(self.rank, self.FLAG_WORDS - 1), stream), "peer_wait")
 
     def take_error(self):

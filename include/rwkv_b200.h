@@ -200,9 +200,10 @@ int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, int dtype,
  * every other rank's (peer_y), then publishes `signal_seq` in each rank's arrival word for this
  * rank; before touching its inputs it waits (bounded, ~0.1 s) until all `world` arrival words of
  * its own rank have reached `wait_seq` (0: no wait).  Sequence numbers grow by one per launch and
- * must be the same on every rank.  RWKV_ERR_UNSUPPORTED if the launch cannot use the cluster
- * kernel (fp16, aligned rows, integer arithmetic).  Not for stream capture: the numbers change
- * per call.
+ * must be the same on every rank; `seq_base` (optional device word, same protocol on every rank)
+ * is added to both on the device, so that a captured graph whose first node is rwkv_peer_advance
+ * can be replayed.  RWKV_ERR_UNSUPPORTED if the launch cannot use the cluster kernel (fp16,
+ * aligned rows, integer arithmetic).
  * ------------------------------------------------------------------------------------- */
 #define RWKV_PEER_HANDLE_BYTES 64
 typedef struct {
@@ -211,6 +212,7 @@ typedef struct {
     uint32_t* peer_arrived[7]; /* on each other rank: the address of ITS arrival word for this rank */
     uint32_t* done_counter;    /* one zeroed word of this rank's memory (left zero) */
     uint32_t* error;           /* one word of this rank's memory; set to 1 when a wait gives up */
+    const uint32_t* seq_base;  /* NULL, or a word of this rank's memory added to wait_seq and signal_seq */
     uint32_t wait_seq, signal_seq;
     int32_t world, rank;
 } rwkv_mm8_exchange;
@@ -221,7 +223,9 @@ int rwkv_peer_free(void* ptr);
 int rwkv_peer_export(const void* ptr, void* handle_out);    /* RWKV_PEER_HANDLE_BYTES bytes for another process */
 int rwkv_peer_open(const void* handle, void** ptr_out);     /* map another process's region (peer access over NVLink) */
 int rwkv_peer_close(void* ptr);
-int rwkv_peer_wait(const uint32_t* arrived, int world, uint32_t seq, uint32_t* error, void* stream);
+int rwkv_peer_wait(const uint32_t* arrived, int world, uint32_t seq, const uint32_t* seq_base, uint32_t* error,
+                   void* stream);
+int rwkv_peer_advance(uint32_t* seq_base, uint32_t add, void* stream);   /* *seq_base += add, in stream order */
 
 /* Tuning hooks (process-wide, not thread-safe).  split: force the number of K-splits
  * (0 = automatic).  variant: bits 0-1 force the panel width (1 = 512, 2 = 256, 3 = 128
