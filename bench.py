@@ -271,7 +271,7 @@ def main():
 
     if rank == 0:
         n_mm = L * (7 if version == 4 else 8)
-        launches_per_token = 2 if model._use_chain else L * (4 if version == 4 else 9) + 1
+        launches_per_token = 2 if model._use_chain else L * (4 if version == 4 else 6) + 1
         line = {
             "metric": METRIC, "value": (1 if sharded else world) * a.steps / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": dev_ms / a.steps, "higher_is_better": True,
