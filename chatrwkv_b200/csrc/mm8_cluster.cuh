@@ -93,6 +93,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
     __shared__ float xs[ROWS];
     __shared__ float ssum[kWarps][3];
     __shared__ float sh8[kWarps];
+    __shared__ float smax[kWarps];                       // per warp: largest |x'|
     __shared__ float tot3[4];                            // this CTA's scalar sums (read by the cluster)
     __shared__ float all3[4];                            // the cluster's scalar sums
 
@@ -185,7 +186,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
 
     // ---- prologue: one trip to L2 for what earlier kernels wrote, then x' = x * ry ----------
     const bool writer = panel == 0;
-    float sx = 0.f, sxr = 0.f, sxmy = 0.f;
+    float sx = 0.f, sxr = 0.f, sxmy = 0.f, xmax = 0.f;      // xmax: largest |x'| (NaN-propagating max is not needed: see quantize_pairs)
     if (P.prologue == RWKV_PRO_LN_MIX) {
         const __half* x = static_cast<const __half*>(P.x);
         const int nvec = P.N / 8;               // host guarantees N % 8 == 0 and N <= 8192
@@ -249,6 +250,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
                     sx += xv;
                     sxr += xp;
                     sxmy = fmaf(xv, to_f32<F>(s_my[l]), sxmy);
+                    xmax = fmaxf(xmax, fabsf(xp));
                 }
             }
         }
@@ -280,6 +282,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
             sx += xv;
             sxr += xp;
             sxmy = fmaf(xv, to_f32<F>(s_my[l]), sxmy);
+            xmax = fmaxf(xmax, fabsf(xp));
         }
     } else {
         // all loads of a thread first (independent: one trip), then the arithmetic
@@ -302,6 +305,7 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
                 sx += xv;
                 sxr += xp;
                 sxmy = fmaf(xv, to_f32<F>(s_my[l]), sxmy);
+                xmax = fmaxf(xmax, fabsf(xp));
             }
         }
     }
@@ -313,8 +317,8 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
             stage_vec<sizeof(F)>(reinterpret_cast<uint8_t*>(s_aux2), P.aux2, col0 + kc0, kc1 - kc0, tid);
     }
     cp_async_commit();
-    sx = warp_sum(sx); sxr = warp_sum(sxr); sxmy = warp_sum(sxmy);
-    if (lane == 0) { ssum[warp][0] = sx; ssum[warp][1] = sxr; ssum[warp][2] = sxmy; }
+    sx = warp_sum(sx); sxr = warp_sum(sxr); sxmy = warp_sum(sxmy); xmax = warp_max(xmax);
+    if (lane == 0) { ssum[warp][0] = sx; ssum[warp][1] = sxr; ssum[warp][2] = sxmy; smax[warp] = xmax; }
     __syncthreads();
     MM8_STAMP(b.trace_id, blockIdx.x, 3);
 
@@ -322,7 +326,12 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
     float acc[16];
     if (MODE == 2) {
         // integer form: x' as 16-bit fixed point, two rows per step (mm8_core.cuh)
-        const float inv_scale = quantize_pairs<ROWS <= 2048 ? 8 : 10>(xs, nrows, rpp, cpr, sub, ch, active, ngroups * (kGroup / 2), nsteps, sh8);
+        // largest |x'| of the CTA from the warps' maxima; a NaN does not show in a max but does in the sum
+        float xm = 0.f, xt = 0.f;
+#pragma unroll
+        for (int w8 = 0; w8 < kWarps; ++w8) { xm = fmaxf(xm, smax[w8]); xt += ssum[w8][1]; }
+        if (!(xt == xt)) xm = __int_as_float(0x7f800000);
+        const float inv_scale = quantize_pairs<ROWS <= 2048 ? 8 : 10>(xs, rpp, cpr, sub, ch, active, ngroups * (kGroup / 2), nsteps, nrows, xm);
         int iacc[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) iacc[i] = 0;

@@ -172,18 +172,9 @@ __device__ __forceinline__ void dot16_q(int (&acc)[16], const uint4& va, const u
 // scale); the quantisation range is the largest that keeps a thread's 32-bit sums of `nsteps`
 // products q * 255 from overflowing (32767 up to 257 steps).
 template <int NP>   // pairs per thread at most: 8 up to 2048 rows per CTA, 10 up to 2560
-__device__ __forceinline__ float quantize_pairs(float* xs, int nrows, int rpp, int cpr, int sub, int ch, bool active,
-                                                int npairs, int nsteps, float* sh8) {
-    const int tid = threadIdx.x;
-    float m = 0.f;
-    for (int l = tid; l < nrows; l += kThreads) m = fmaxf(m, fabsf(xs[l]));
-    m = warp_max(m);
-    __syncthreads();
-    if ((tid & 31) == 0) sh8[tid >> 5] = m;
-    __syncthreads();
-    m = 0.f;
-#pragma unroll
-    for (int i = 0; i < kWarps; ++i) m = fmaxf(m, sh8[i]);
+__device__ __forceinline__ float quantize_pairs(float* xs, int rpp, int cpr, int sub, int ch, bool active,
+                                                int npairs, int nsteps, int nrows, float m) {
+    // m: the largest |x'| of the CTA's rows, +inf if any of them is not finite (the same in every thread)
     const int qmax = min(32767, 0x7fffffff / (255 * max(nsteps, 1)));
     const bool finite = m < 3.0e38f;            // false for inf and NaN
     const float scale = (finite && m > 0.f) ? float(qmax) / m : 0.f;

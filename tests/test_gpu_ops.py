@@ -400,3 +400,17 @@ def test_wkv56_one(ops, H, N):
                                dl[1].data_ptr(), dl[2].data_ptr(), y.data_ptr(), st), "wkv56_one")
     torch.cuda.synchronize()
     assert torch.equal(dS, dS2)
+
+
+@pytest.mark.parametrize("bad", [float("nan"), float("inf")])
+def test_mm8_one_non_finite_activation_gives_nan(ops, bad):
+    """A NaN or infinity among the activations must not be lost by the fixed-point arithmetic:
+    every output of the rows' K-slice becomes NaN, as it would in fp32 (inf * 0-centred codes)."""
+    from tests.util import packed_case
+    N, M = 4096, 512
+    cpu, dev = packed_case(N, M, seed=3)
+    x = torch.randn(N).half()
+    x[1234] = bad
+    y = torch.zeros(M, dtype=torch.float32, device="cuda")
+    torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y)
+    assert torch.isnan(y).all() or torch.isinf(y).all() or (torch.isnan(y) | torch.isinf(y)).all()
