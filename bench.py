@@ -159,6 +159,9 @@ def main():
     ap.add_argument("--shard", action="store_true",
                     help="second multi-GPU mode: ONE model, every packed matrix split by output columns over the "
                          "ranks with an NCCL all-gather after each matmul (strong scaling; use with --shape v4-14b)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="operator sweep instead of the model bench: mm8_one (T=1) and mm8_seq (T=16,128,1024) on the "
+                         "four (N, M) shapes of the task's operator config; one JSON line with a 'sweep' list")
     ap.add_argument("--layers", type=int, default=0,
                     help="profiling aid: build only this many layers of the shape (the line is then not a bench result)")
     a = ap.parse_args()
@@ -185,6 +188,10 @@ def main():
     from chatrwkv_b200 import synth
     from chatrwkv_b200.model import RWKV
 
+    if a.sweep:
+        if rank == 0:
+            print(json.dumps(operator_sweep(torch.device("cuda", local_rank))), flush=True)
+        return
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -294,6 +301,60 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def operator_sweep(dev, iters=24):
+    """mm8_one / mm8_seq through torch.ops.rwkv on seeded inputs (weights N(0, 0.02) packed on the GPU,
+    activations N(0, 1)), each timed as a CUDA graph of `iters` calls that cycle through enough
+    distinct packed matrices to exceed L2 several times over; CUDA events around 3 replays."""
+    import torch
+    from chatrwkv_b200 import ops
+    torch.cuda.set_device(dev)
+    peak, how = measured_peaks()
+    out = []
+    for (N, M) in [(4096, 4096), (4096, 16384), (16384, 4096), (5120, 20480)]:
+        copies = max(2, int(600e6 // (N * M)) + 1)
+        g = torch.Generator(device=dev).manual_seed(3000)
+        packs = []
+        for _ in range(copies):
+            w = (torch.randn(N, M, generator=g, device=dev) * 0.02).half().float()
+            packs.append(ops.quantize_weight(w, torch.float16))
+            del w
+        for T in (1, 16, 128, 1024):
+            x = torch.randn((T, N) if T > 1 else (N,), generator=g, device=dev).half()
+            y = torch.zeros(M, dtype=torch.float32, device=dev) if T == 1 else \
+                torch.empty((T, M), dtype=torch.float16, device=dev)
+
+            def call(i):
+                q, mx, rx, my, ry = packs[i % copies]
+                if T == 1:
+                    torch.ops.rwkv.mm8_one(N, M, x, q, mx, rx, my, ry, y)
+                else:
+                    torch.ops.rwkv.mm8_seq(T, N, M, x, q, mx, rx, my, ry, y)
+            side = torch.cuda.Stream(dev)           # operator workspaces are per stream: warm up on the capture stream
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                call(0)
+            torch.cuda.synchronize(dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(iters):
+                    call(i)
+            graph.replay()
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            us = e0.elapsed_time(e1) / (3 * iters) * 1e3
+            nbytes = N * M + 2 * T * N + (4 if T == 1 else 2) * T * M + 4 * (N + M)
+            out.append({"N": N, "M": M, "T": T, "us": round(us, 2), "GB/s": round(nbytes / us / 1e3, 1),
+                        "frac_of_hbm_peak": round(nbytes / us / 1e3 / peak, 3), "TFLOP/s": round(2.0 * T * N * M / us / 1e6, 1)})
+        del packs
+        torch.cuda.empty_cache()
+    return {"sweep": out, "hbm_peak_gbs": peak, "peak_source": how, "timing": "CUDA graph of %d calls over distinct matrices" % iters}
 
 
 def gemv_roofline(model, dev, reps=30):
