@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(256) mm8_seq_simt(int B, int N, int M,
 }  // namespace
 
 // tensor-core path (mm8_seq_tc.cu)
-extern "C" size_t rwkv_mm8_seq_tc_workspace_bytes(int64_t B, int64_t N);
+extern "C" size_t rwkv_mm8_seq_tc_workspace_bytes(int64_t B, int64_t N, int64_t M);
 extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
                                const uint8_t* w, int64_t w_stride, const void* mx, const void* rx,
                                const void* my, const void* ry, int dtype, void* y, int64_t y_stride,
@@ -106,9 +106,8 @@ constexpr int kTcMinRows = 8;   // below this the CUDA-core kernel; from here on
                                 // 64 rows, but 4x faster than the CUDA-core kernel already at 16 rows: W is converted once per CTA)
 
 extern "C" size_t rwkv_mm8_seq_workspace_bytes(int64_t B, int64_t N, int64_t M) {
-    (void)M;
-    if (B < 1 || N < 1) return 0;
-    return rwkv_mm8_seq_tc_workspace_bytes(B, N);
+    if (B < 1 || N < 1 || M < 1) return 0;
+    return rwkv_mm8_seq_tc_workspace_bytes(B, N, M);
 }
 
 extern "C" int rwkv_mm8_seq(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,

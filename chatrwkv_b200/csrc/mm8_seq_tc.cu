@@ -152,6 +152,10 @@ struct TcArgs {
     int T, N, M;
     int vec_ok;                                               // y, rx, mx allow 16-byte accesses
     unsigned* error_flag;
+    // K split over blockIdx.z (launches of one row tile that would leave most SMs idle): CTA z takes K
+    // blocks [z * kb_per, (z + 1) * kb_per) and writes its fp32 sums to partial[z][t][m_pad]
+    int ksplit, kb_per, m_pad;
+    float* partial;
 };
 
 template <typename F>
@@ -160,7 +164,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
     extern __shared__ __align__(1024) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
-    const int nkb = (a.N + BK - 1) / BK;
+    const int nkb_all = (a.N + BK - 1) / BK;
+    const int kbase = a.ksplit > 1 ? int(blockIdx.z) * a.kb_per : 0;            // first K block of this CTA
+    const int nkb = a.ksplit > 1 ? max(0, min(nkb_all, kbase + a.kb_per) - kbase) : nkb_all;
 
     uint8_t* bars = smem + STAGES * kStageBytes;
     const uint32_t full0 = s2u(bars), empty0 = full0 + STAGES * 8, accum_bar = empty0 + STAGES * 8;
@@ -195,7 +201,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
         auto load_w = [&](int kb, uint2 (&dst)[8]) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const int k = kb * BK + rg * 8 + i;
+                const int k = (kbase + kb) * BK + rg * 8 + i;
                 dst[i] = (col_ok && k < a.N) ? __ldg(reinterpret_cast<const uint2*>(a.w + (long long)k * a.w_stride + ncol))
                                              : make_uint2(0x80808080u, 0x80808080u);   // code 128 -> value 0
             }
@@ -222,7 +228,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                     // shared memory per store phase, 64 contiguous bytes per row on the global side
                     const int c = tid + i * kProducers;
                     const int row = ((c >> 6) << 3) | (c & 7), kc = (c >> 3) & 7;
-                    const int t = m0 + row, k = kb * BK + kc * 8;
+                    const int t = m0 + row, k = (kbase + kb) * BK + kc * 8;
                     const bool in = t < a.T && k < a.lda;    // hi/lo are zero padded up to lda
                     const long long off = in ? (long long)t * a.lda + k : 0;
                     const uint32_t dst = (row >> 3) * kSBO + kc * kLBO + (row & 7) * 16;
@@ -284,7 +290,15 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                       "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                     : "r"(taddr) : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (t < a.T) {
+                if (a.ksplit > 1) {
+                    if (t < a.T) {               // raw fp32 sums of this K range; rwkv seq_reduce finishes them
+                        float4* prow = reinterpret_cast<float4*>(a.partial + ((long long)blockIdx.z * a.T + t) * a.m_pad + n0 + c * 32);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            prow[q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                                  __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                    }
+                } else if (t < a.T) {
                     const int nb = n0 + c * 32;
                     if (a.vec_ok && nb + 32 <= a.M) {       // 4 x (8 columns: 16-byte loads of rx, mx, 16-byte store)
 #pragma unroll
@@ -350,13 +364,43 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
     if (tid == 0 && *failed) atomicExch(a.error_flag, 1u);
 }
 
+// y[t][n] = affine(sum over the K splits, in split order) for the split-K launches.
+template <typename F>
+__global__ void __launch_bounds__(256) mm8_seq_reduce(int T, int M, int m_pad, int ksplit, const float* __restrict__ partial,
+                                                      const float* __restrict__ sums, const F* __restrict__ mx,
+                                                      const F* __restrict__ rx, F* __restrict__ y, long long y_stride) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int t = blockIdx.y;
+    const float sx = sums[t * 4 + 0], sxr = sums[t * 4 + 1], sxmy = sums[t * 4 + 2];
+    for (int n = blockIdx.x * 256 + threadIdx.x; n < M; n += gridDim.x * 256) {
+        float s = 0.f;
+        for (int z = 0; z < ksplit; ++z) s += partial[((long long)z * T + t) * m_pad + n];
+        const float rxn = to_f32<F>(rx[n]);
+        y[(long long)t * y_stride + n] = from_f32<F>(fmaf(rxn, s, fmaf(rxn * 128.5f, sxr, fmaf(to_f32<F>(mx[n]), sx, sxmy))));
+    }
+}
+
+// K splits of a launch: 1 unless it is a single row tile whose column tiles leave most SMs idle.
+static inline int tc_ksplit(int64_t B, int64_t N, int64_t M) {
+    if (B > BM) return 1;
+    const int tiles = int((M + BN - 1) / BN), nkb = int((N + BK - 1) / BK);
+    int ks = rwkv_sm_count() / tiles;
+    if (ks > 8) ks = 8;
+    if (ks > nkb / 4) ks = nkb / 4;
+    return ks < 2 ? 1 : ks;
+}
+static inline int64_t tc_mpad(int64_t M) { return (M + BN - 1) / BN * BN; }
+
 }  // namespace
 
-// Scratch of the tensor-core path: hi and lo copies of x' ([B, Npad] fp16 each), the row sums
-// and one error word.
-extern "C" size_t rwkv_mm8_seq_tc_workspace_bytes(int64_t B, int64_t N) {
+// Scratch of the tensor-core path: hi and lo copies of x' ([B, Npad] fp16 each), the row sums,
+// one error word and, for split-K launches, the fp32 partial sums [splits][B][M rounded up to 256].
+extern "C" size_t rwkv_mm8_seq_tc_workspace_bytes(int64_t B, int64_t N, int64_t M) {
     const int64_t npad = (N + BK - 1) / BK * BK;
-    return size_t(B) * size_t(npad) * 4 + size_t(B) * 16 + 256;
+    const int ks = tc_ksplit(B, N, M);
+    const size_t part = ks > 1 ? size_t(ks) * size_t(B) * size_t(tc_mpad(M)) * 4 : 0;
+    return (size_t(B) * size_t(npad) * 4 + size_t(B) * 16 + 256 + 255) / 256 * 256 + part;
 }
 
 // Returns RWKV_ERR_UNSUPPORTED when the operands do not meet the layout the tensor-core kernel
@@ -368,7 +412,7 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
     RWKV_CHECK_ARG(B >= 1 && N >= 1 && M >= 1 && x && w && mx && rx && my && ry && y);
     if (dtype != RWKV_F16) return RWKV_ERR_UNSUPPORTED;
     if (reinterpret_cast<uintptr_t>(w) % 8 != 0 || w_stride % 8 != 0 || M % 8 != 0) return RWKV_ERR_UNSUPPORTED;
-    if (workspace == nullptr || workspace_bytes < rwkv_mm8_seq_tc_workspace_bytes(B, N)) return RWKV_ERR_WORKSPACE;
+    if (workspace == nullptr || workspace_bytes < rwkv_mm8_seq_tc_workspace_bytes(B, N, M)) return RWKV_ERR_WORKSPACE;
     RWKV_CHECK_ALIGN(workspace, 256);
     if ((B + BM - 1) / BM > 65535) return RWKV_ERR_UNSUPPORTED;
     const int64_t npad = (N + BK - 1) / BK * BK;
@@ -396,8 +440,19 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
         }
         configured = true;
     }
-    dim3 grid((unsigned)((M + BN - 1) / BN), (unsigned)((B + BM - 1) / BM));
-    return rwkv_launch_pdl(kern, grid, dim3(kThreadsTc), size_t(kSmemTc), st, a);
+    int ks = tc_ksplit(B, N, M);
+    const int nkb_all = int((N + BK - 1) / BK);
+    a.kb_per = (nkb_all + ks - 1) / ks;
+    ks = (nkb_all + a.kb_per - 1) / a.kb_per;          // no empty split
+    a.ksplit = ks;
+    a.m_pad = int(tc_mpad(M));
+    a.partial = reinterpret_cast<float*>(ws + (size_t(B) * size_t(npad) * 4 + size_t(B) * 16 + 256 + 255) / 256 * 256);
+    dim3 grid((unsigned)((M + BN - 1) / BN), (unsigned)((B + BM - 1) / BM), (unsigned)ks);
+    rc = rwkv_launch_pdl(kern, grid, dim3(kThreadsTc), size_t(kSmemTc), st, a);
+    if (rc != RWKV_OK || ks == 1) return rc;
+    return rwkv_launch_pdl(mm8_seq_reduce<__half>, dim3((unsigned)((M + 255) / 256), (unsigned)B), dim3(256), 0, st, int(B),
+                           int(M), a.m_pad, ks, (const float*)a.partial, (const float*)sums, static_cast<const __half*>(mx),
+                           static_cast<const __half*>(rx), static_cast<__half*>(y), (long long)y_stride);
 }
 
 extern "C" int rwkv_mm8_seq_tc_take_error(void* workspace, void* stream, int* error_out) {
