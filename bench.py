@@ -354,7 +354,40 @@ def operator_sweep(dev, iters=24):
                         "frac_of_hbm_peak": round(nbytes / us / 1e3 / peak, 3), "TFLOP/s": round(2.0 * T * N * M / us / 1e6, 1)})
         del packs
         torch.cuda.empty_cache()
-    return {"sweep": out, "hbm_peak_gbs": peak, "peak_source": how, "timing": "CUDA graph of %d calls over distinct matrices" % iters}
+    # WKV recurrences at the 7B width (C = 4096, 64 heads of 64): fp32 operands as on the model path
+    wkv = []
+    C, H = 4096, 64
+    Nh = C // H
+    g = torch.Generator(device=dev).manual_seed(3001)
+    for T in (16, 256, 2048):
+        k, v, r = (torch.randn(T, C, generator=g, device=dev) for _ in range(3))
+        w6 = torch.exp(-torch.exp(torch.rand(T, C, generator=g, device=dev) * 6 - 5))
+        w4, u = -torch.exp(torch.rand(C, generator=g, device=dev) * 6 - 5), torch.rand(C, generator=g, device=dev) * 2 - 1
+        y = torch.empty(T, C, device=dev)
+        aa, bb, pp = torch.zeros(C, device=dev), torch.zeros(C, device=dev), torch.full((C,), -1e30, device=dev)
+        S = torch.zeros(H, Nh, Nh, device=dev)
+        cases = {
+            "wkv_forward (v4)": (lambda: torch.ops.rwkv.wkv_forward(1, T, C, w4, u, k, v, y, aa, bb, pp), 12 * T * C + 32 * C),
+            "rwkv5 forward_fp32": (lambda: torch.ops.rwkv5.forward_fp32(1, T, C, H, S, r, k, v, w6[0].contiguous(), u, y),
+                                   16 * T * C + 8 * H * Nh * Nh + 8 * C),
+            "rwkv6 forward_fp32": (lambda: torch.ops.rwkv6.forward_fp32(1, T, C, H, S, r, k, v, w6, u, y),
+                                   20 * T * C + 8 * H * Nh * Nh + 4 * C),
+        }
+        for name, (fn, nbytes) in cases.items():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            us = e0.elapsed_time(e1) / 10 * 1e3
+            wkv.append({"op": name, "T": T, "C": C, "us": round(us, 1), "GB/s": round(nbytes / us / 1e3, 1),
+                        "us_per_token": round(us / T, 3)})
+    return {"sweep": out, "wkv": wkv, "hbm_peak_gbs": peak, "peak_source": how,
+            "timing": "mm8: CUDA graph of %d calls over distinct matrices; wkv: 10 direct calls" % iters}
 
 
 def gemv_roofline(model, dev, reps=30):
