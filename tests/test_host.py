@@ -75,3 +75,31 @@ def test_synth_checkpoint_schema():
     w2 = synth.make_checkpoint(6, 2, 64, 224, 100, seed=1, head_size=16, maa_rank=8, decay_rank=16)
     assert all(torch.equal(w[k], w2[k]) for k in w)
     assert synth.make_tokens(5, 100, 3) == synth.make_tokens(5, 100, 3)
+
+
+def test_peer_region_launch_numbering_without_gpu():
+    """The exchange descriptors of a token: launch j publishes j and waits for j - 1 (0 = no wait), every
+    rank addresses the others' arrival word for itself, and the numbering restarts with each token (the
+    device-side base is advanced instead)."""
+    from chatrwkv_b200 import shard
+    import torch
+    pr = shard.PeerRegion.__new__(shard.PeerRegion)
+    pr.world, pr.rank = 4, 2
+    pr.others = [0, 1, 3]
+    pr.bases = [0x10000000 * (r + 1) for r in range(4)]
+    pr.base = pr.bases[2]
+    pr.offsets = {"x": (0, torch.float16, 64), "fk": (256, torch.float16, 256)}
+    pr.flag_off = 1024
+    pr._rel, pr._n = 0, 3
+    e1 = pr.exchange([("x", 16)], wait=False)
+    e2 = pr.exchange([("fk", 128), ("x", 16)], wait=True)
+    e3 = pr.exchange([("x", 16)], wait=True)
+    assert (e1.wait_seq, e1.signal_seq) == (0, 1) and (e2.wait_seq, e2.signal_seq) == (1, 2) and (e3.wait_seq, e3.signal_seq) == (2, 3)
+    assert e2.world == 4 and e2.rank == 2
+    # problem 0 of launch 2 is fk at element 128 on ranks 0, 1, 3; problem 1 is x at element 16
+    assert [e2.peer_y[0][i] for i in range(3)] == [pr.bases[r] + 256 + 2 * 128 for r in (0, 1, 3)]
+    assert [e2.peer_y[1][i] for i in range(3)] == [pr.bases[r] + 0 + 2 * 16 for r in (0, 1, 3)]
+    # this rank's words, and on every other rank the word that belongs to this rank (index 2)
+    assert e2.arrived == pr.bases[2] + 1024
+    assert [e2.peer_arrived[i] for i in range(3)] == [pr.bases[r] + 1024 + 4 * 2 for r in (0, 1, 3)]
+    assert e2.seq_base == pr.bases[2] + 1024 + 4 * (shard.PeerRegion.FLAG_WORDS - 3)
