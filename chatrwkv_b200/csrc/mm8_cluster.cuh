@@ -577,8 +577,14 @@ static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, 
         cudaGetLastError();
         return RWKV_ERR_UNSUPPORTED;
     }
-    const int slots = exch ? cluster_slots(kern_x, S, smem) : cluster_slots(kern, S, smem);
+    int slots = exch ? cluster_slots(kern_x, S, smem) : cluster_slots(kern, S, smem);
     if (slots <= 0) return RWKV_ERR_UNSUPPORTED;
+    // Plan for four fifths of the resident clusters (26 of 33): the slots left free let the next
+    // launch's first clusters become resident, and fill their rings, while this one still streams
+    // (7B shape: 487 -> 507 tok/s; 14B shape: -1 %).  A negative panel_width of
+    // rwkv_mm8_one_set_cluster plans for that many clusters instead.
+    if (g_cluster_pw < 0) { if (-g_cluster_pw < slots) slots = -g_cluster_pw; }
+    else if (g_cluster_pw == 0 && slots >= 10) slots = slots * 4 / 5;
 
     // Panel width: the narrowest multiple of 16 columns with which one wave of clusters covers
     // every matrix of the launch.

@@ -236,7 +236,9 @@ void rwkv_mm8_one_set_variant(int variant);
  * are one thread-block cluster of up to 8 CTAs that adds its partial sums through distributed
  * shared memory; matrices that kernel cannot take (unaligned rows, more than 16384 in-features)
  * use global scratch and an atomic ticket.  cluster_size -1 forces the ticket kernel, 1/2/4/8
- * force a cluster size; panel_width forces the panel width in columns (0 = automatic).  Forcing
+ * force a cluster size; panel_width forces the panel width in columns (0 = automatic: the narrowest
+ * width with which four fifths of the resident clusters cover the launch; a negative value plans for
+ * that many clusters).  Forcing
  * a split or a width with the two hooks above also selects the ticket kernel.  No counterpart in
  * the reference. */
 void rwkv_mm8_one_set_cluster(int cluster_size, int panel_width);
