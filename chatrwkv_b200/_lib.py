@@ -73,6 +73,7 @@ SIGNATURES = {
     "rwkv_mm8_one_set_split": (None, [_i32]),
     "rwkv_mm8_one_set_variant": (None, [_i32]),
     "rwkv_mm8_one_set_cluster": (None, [_i32, _i32]),
+    "rwkv_mm8_one_set_plan": (None, [_i64, _i32]),
     "rwkv_mm8_chain_ctas": (_i32, []),
     "rwkv_mm8_chain_table_bytes": (_sz, [_i32, _i32]),
     "rwkv_mm8_chain_plan": (_i32, [C.POINTER(Mm8Problem), C.POINTER(C.c_int32), _i32, _i32, _i32, _vp, _sz, _vp, _sz]),

@@ -506,6 +506,10 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_cluster_kernel(const __grid_c
 
 int g_cluster_size = 0;       // 0 = automatic, -1 = off, else forced (1, 2, 4 or 8)
 int g_cluster_pw = 0;         // 0 = automatic, else forced panel width (multiple of 16)
+// tuning table: launches whose matrices have `cols` output columns in all are planned for `clusters`
+struct PlanEntry { long long cols; int clusters; };
+PlanEntry g_plan[16];
+int g_plan_n = 0;
 
 // Clusters of `S` CTAs (256 threads, `smem` bytes each) that can be resident at once on the
 // current device; 0 if the query fails.  Asked once per (device, S).
@@ -583,8 +587,13 @@ static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, 
     // launch's first clusters become resident, and fill their rings, while this one still streams
     // (7B shape: 487 -> 507 tok/s; 14B shape: -1 %).  A negative panel_width of
     // rwkv_mm8_one_set_cluster plans for that many clusters instead.
-    if (g_cluster_pw < 0) { if (-g_cluster_pw < slots) slots = -g_cluster_pw; }
-    else if (g_cluster_pw == 0 && slots >= 10) slots = slots * 4 / 5;
+    {
+        int planned = 0;
+        for (int i = 0; i < g_plan_n; ++i) if (g_plan[i].cols == total_cols) planned = g_plan[i].clusters;
+        if (planned > 0) { if (planned < slots) slots = planned; }
+        else if (g_cluster_pw < 0) { if (-g_cluster_pw < slots) slots = -g_cluster_pw; }
+        else if (g_cluster_pw == 0 && slots >= 10) slots = slots * 4 / 5;
+    }
 
     // Panel width: the narrowest multiple of 16 columns with which one wave of clusters covers
     // every matrix of the launch.
@@ -644,6 +653,12 @@ static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, 
 }
 
 }  // namespace
+
+extern "C" void rwkv_mm8_one_set_plan(int64_t total_columns, int clusters) {
+    for (int i = 0; i < g_plan_n; ++i)
+        if (g_plan[i].cols == total_columns) { g_plan[i].clusters = clusters; return; }
+    if (g_plan_n < 16) { g_plan[g_plan_n].cols = total_columns; g_plan[g_plan_n].clusters = clusters; ++g_plan_n; }
+}
 
 extern "C" void rwkv_mm8_one_set_cluster(int cluster_size, int panel_width) {
     g_cluster_size = cluster_size;

@@ -242,6 +242,9 @@ void rwkv_mm8_one_set_variant(int variant);
  * a split or a width with the two hooks above also selects the ticket kernel.  No counterpart in
  * the reference. */
 void rwkv_mm8_one_set_cluster(int cluster_size, int panel_width);
+/* Tuning: launches whose matrices have `total_columns` output columns in all are planned for `clusters`
+ * clusters (0 = back to automatic).  Up to 16 entries, process-wide. */
+void rwkv_mm8_one_set_plan(int64_t total_columns, int clusters);
 
 
 /* ---------------------------------------------------------------------------------------
