@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(kT) wkv56_one_kernel(int N, const __half* __re
 constexpr int kPT = 512;
 
 struct AttPre {
-    int D, Lm, Ld, rows;
+    int D, Lm, Ld, rows, ncta;   // ncta: CTAs of the one cluster (8, or 16 where the device allows it)
     const __half *x, *ln_w, *ln_b, *state, *maa_x, *w1, *w2, *dw1, *dw2;
     const __half* maa[5];
     const float* decay;
@@ -535,8 +535,7 @@ __global__ void __launch_bounds__(kPT) v6_att_pre_kernel(const AttPre a) {
     cluster.sync();
     for (int c = tid; c < R1; c += kPT) {
         float s = 0.f;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) s += cluster.map_shared_rank(part1, q)[c];
+        for (int q = 0; q < a.ncta; ++q) s += cluster.map_shared_rank(part1, q)[c];
         h[c] = r16(tanhf(r16(s)));
     }
     __syncthreads();
@@ -552,8 +551,7 @@ __global__ void __launch_bounds__(kPT) v6_att_pre_kernel(const AttPre a) {
     cluster.sync();
     for (int c = tid; c < R3; c += kPT) {
         float s = 0.f;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) s += cluster.map_shared_rank(part3, q)[c];
+        for (int q = 0; q < a.ncta; ++q) s += cluster.map_shared_rank(part3, q)[c];
         h[c] = r16(tanhf(r16(s)));
     }
     __syncthreads();
@@ -655,7 +653,14 @@ extern "C" int rwkv_v6_att_pre(int64_t D, int64_t Lm, int64_t Ld, const void* x,
     for (const void* p : al) RWKV_CHECK_ALIGN(p, 16);
     AttPre a = {};
     a.D = int(D); a.Lm = int(Lm); a.Ld = int(Ld);
-    a.rows = int(((D + 7) / 8 + 7) / 8 * 8);
+    // 16 CTAs (a non-portable cluster size) halve every CTA's share of the weights; 8 where the
+    // device or the shape (fewer than 16 x 8 channels) does not allow it.
+    static int big = -1;
+    if (big < 0)
+        big = cudaFuncSetAttribute(v6_att_pre_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess ? 1 : 0;
+    cudaGetLastError();
+    a.ncta = (big == 1 && D >= 16 * 64) ? 16 : 8;
+    a.rows = int(((D + a.ncta - 1) / a.ncta + 7) / 8 * 8);
     a.x = static_cast<const __half*>(x); a.ln_w = static_cast<const __half*>(ln_w); a.ln_b = static_cast<const __half*>(ln_b);
     a.state = static_cast<const __half*>(state); a.maa_x = static_cast<const __half*>(maa_x);
     a.w1 = static_cast<const __half*>(tm_w1); a.w2 = static_cast<const __half*>(tm_w2);
@@ -677,13 +682,13 @@ extern "C" int rwkv_v6_att_pre(int64_t D, int64_t Lm, int64_t Ld, const void* x,
         use_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(8);
+    cfg.gridDim = dim3(unsigned(a.ncta));
     cfg.blockDim = dim3(kPT);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 8;
+    attr[0].val.clusterDim.x = unsigned(a.ncta);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -691,6 +696,15 @@ extern "C" int rwkv_v6_att_pre(int64_t D, int64_t Lm, int64_t Ld, const void* x,
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, v6_att_pre_kernel, a);
+    if (e != cudaSuccess && a.ncta == 16) {      // no room for a 16-CTA cluster: 8 from now on
+        cudaGetLastError();
+        big = 0;
+        a.ncta = 8;
+        a.rows = int(((D + 7) / 8 + 7) / 8 * 8);
+        cfg.gridDim = dim3(8);
+        attr[0].val.clusterDim.x = 8;
+        e = cudaLaunchKernelEx(&cfg, v6_att_pre_kernel, a);
+    }
     if (e != cudaSuccess) { cudaGetLastError(); return RWKV_ERR_LAUNCH; }
     return RWKV_OK;
 }
