@@ -121,6 +121,11 @@ def cpu_arm(steps, warmup, budget_s=100.0):
     weight bytes -- and scales to the 7,185,256,448 weight bytes of one 7B-shape token."""
     import torch
     from oracle import rwkv_oracle as orc
+    # all host threads, also under torchrun (which exports OMP_NUM_THREADS=1 to its workers)
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        torch.set_num_threads(os.cpu_count() or 1)
     L, per_layer, head = matrices_of_token(WORKLOAD)
     token_bytes = L * sum(n * m for n, m in per_layer) + head[0] * head[1]
     N = M = per_layer[0][0]
