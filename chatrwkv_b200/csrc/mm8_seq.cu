@@ -100,8 +100,14 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
                                const void* my, const void* ry, int dtype, void* y, int64_t y_stride,
                                void* workspace, size_t workspace_bytes, void* stream);
 
+extern "C" void rwkv_mm8_seq_tc_set_single(int single);
 static int g_seq_path = 0;      // 0 = automatic, 1 = CUDA cores only, 2 = tensor cores whenever the layout allows
-extern "C" void rwkv_mm8_seq_set_path(int path) { g_seq_path = path; }
+// bit 2 (value 4) of `path`: the tensor-core kernel multiplies fp16(x*ry) in one pass instead of the exact
+// hi + lo pair
+extern "C" void rwkv_mm8_seq_set_path(int path) {
+    g_seq_path = path & 3;
+    rwkv_mm8_seq_tc_set_single((path & 4) != 0);
+}
 constexpr int kTcMinRows = 8;   // below this the CUDA-core kernel; from here on the 128-row tensor-core tile (mostly padding up to
                                 // 64 rows, but 4x faster than the CUDA-core kernel already at 16 rows: W is converted once per CTA)
 

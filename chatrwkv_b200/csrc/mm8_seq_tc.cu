@@ -151,6 +151,7 @@ struct TcArgs {
     void* y; long long y_stride;
     int T, N, M;
     int vec_ok;                                               // y, rx, mx allow 16-byte accesses
+    int single;                                               // 1: multiply fp16(x*ry) only (no low-order pass)
     unsigned* error_flag;
     // K split over blockIdx.z (launches of one row tile that would leave most SMs idle): CTA z takes K
     // blocks [z * kb_per, (z + 1) * kb_per) and writes its fp32 sums to partial[z][t][m_pad]
@@ -233,7 +234,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                     const long long off = in ? (long long)t * a.lda + k : 0;
                     const uint32_t dst = (row >> 3) * kSBO + kc * kLBO + (row & 7) * 16;
                     cp_async16_zfill(a_hi + dst, a.hi + off, in ? 16 : 0);
-                    cp_async16_zfill(a_lo + dst, a.lo + off, in ? 16 : 0);
+                    if (!a.single) cp_async16_zfill(a_lo + dst, a.lo + off, in ? 16 : 0);
                 }
                 cp_async_arrive(full0 + s * 8);
                 // B tile: transpose this thread's 8x8 byte block, convert, store one core matrix
@@ -347,7 +348,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
             for (int j = 0; j < BK / 16; ++j) {          // one UMMA consumes K = 16: two core matrices
                 const uint64_t bd = umma_desc(b_t + j * 2 * kLBO, kSBO_B);
                 umma_f16(tmem_base, umma_desc(a_hi + j * 2 * kLBO, kSBO), bd, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-                umma_f16(tmem_base, umma_desc(a_lo + j * 2 * kLBO, kSBO), bd, idesc, 1u);
+                if (!a.single) umma_f16(tmem_base, umma_desc(a_lo + j * 2 * kLBO, kSBO), bd, idesc, 1u);
             }
             umma_commit(empty0 + s * 8);                 // frees the stage when these MMAs retire
         }
@@ -380,6 +381,8 @@ __global__ void __launch_bounds__(256) mm8_seq_reduce(int T, int M, int m_pad, i
         y[(long long)t * y_stride + n] = from_f32<F>(fmaf(rxn, s, fmaf(rxn * 128.5f, sxr, fmaf(to_f32<F>(mx[n]), sx, sxmy))));
     }
 }
+
+int g_tc_single = 0;
 
 // K splits of a launch: 1 unless it is a single row tile whose column tiles leave most SMs idle.
 static inline int tc_ksplit(int64_t B, int64_t N, int64_t M) {
@@ -429,6 +432,7 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
     TcArgs a;
     a.hi = hi; a.lo = lo; a.lda = npad; a.sums = sums; a.w = w; a.w_stride = w_stride; a.mx = mx; a.rx = rx;
     a.y = y; a.y_stride = y_stride; a.T = int(B); a.N = int(N); a.M = int(M); a.error_flag = err;
+    a.single = g_tc_single;
     a.vec_ok = (reinterpret_cast<uintptr_t>(y) % 16 == 0 && y_stride % 8 == 0 && reinterpret_cast<uintptr_t>(rx) % 16 == 0 &&
                 reinterpret_cast<uintptr_t>(mx) % 16 == 0) ? 1 : 0;
     auto kern = mm8_seq_tc_kernel<__half>;
@@ -454,6 +458,10 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
                            int(M), a.m_pad, ks, (const float*)a.partial, (const float*)sums, static_cast<const __half*>(mx),
                            static_cast<const __half*>(rx), static_cast<__half*>(y), (long long)y_stride);
 }
+
+// 1: one tensor-core pass with fp16(x*ry) instead of the exact hi + lo pair (about 1e-4 of the output RMS less
+// accurate, half the tensor work); 0 (default): exact.  Set through rwkv_mm8_seq_set_path.
+extern "C" void rwkv_mm8_seq_tc_set_single(int single) { g_tc_single = single ? 1 : 0; }
 
 extern "C" int rwkv_mm8_seq_tc_take_error(void* workspace, void* stream, int* error_out) {
     RWKV_CHECK_ARG(workspace != nullptr && error_out != nullptr);

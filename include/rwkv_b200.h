@@ -289,12 +289,14 @@ int rwkv_mm8_chain_take_error(void* workspace, void* stream, int* error_out);
  *
  * x [B, N] row stride x_stride, y [B, M] row stride y_stride, both in `dtype`, fp32
  * accumulation, one rounding to `dtype` at the store (operators.cu:138).
- * Two kernels: from 64 rows up, fp16 operands whose w is 8-byte aligned (pointer, stride, M)
+ * Two kernels: from 8 rows up, fp16 operands whose w is 8-byte aligned (pointer, stride, M)
  * run on the tensor cores (tcgen05 UMMA, fp32 accumulation in tensor memory; x*ry enters as
  * an exact hi + lo pair of fp16 values) and need `workspace` =
  * rwkv_mm8_seq_workspace_bytes(B, N, M) bytes, 256-byte aligned, zero when first handed over;
  * everything else (or workspace == NULL) runs on a CUDA-core kernel that accepts any layout.
- * rwkv_mm8_seq_set_path: 0 automatic, 1 CUDA cores only, 2 tensor cores whenever possible.
+ * rwkv_mm8_seq_set_path: 0 automatic, 1 CUDA cores only, 2 tensor cores whenever possible; adding 4
+ * makes the tensor-core kernel multiply fp16(x*ry) in ONE pass instead of the exact hi + lo pair
+ * (about 1e-4 of the output's RMS less accurate, 10-35 % faster at T = 1024; off by default).
  * rwkv_mm8_seq_tc_take_error synchronises `stream` and returns/clears the workspace's error
  * word (1 if a bounded wait inside the tensor-core kernel gave up; outputs then undefined).
  * ------------------------------------------------------------------------------------- */

@@ -414,3 +414,23 @@ def test_mm8_one_non_finite_activation_gives_nan(ops, bad):
     y = torch.zeros(M, dtype=torch.float32, device="cuda")
     torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y)
     assert torch.isnan(y).all() or torch.isinf(y).all() or (torch.isnan(y) | torch.isinf(y)).all()
+
+
+def test_mm8_seq_single_pass_option(ops):
+    """rwkv_mm8_seq_set_path(4): one tensor-core pass with fp16(x*ry); within two fp16 ulps of the oracle."""
+    from chatrwkv_b200._lib import lib
+    from tests.util import packed_case
+    T, N, M = 256, 1024, 768
+    cpu, dev = packed_case(N, M, seed=11)
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(T, N, generator=g).half()
+    ref = orc.mm8_kernel(x, *cpu).half().float()
+    y = torch.empty(T, M, dtype=torch.float16, device="cuda")
+    lib().rwkv_mm8_seq_set_path(4)
+    try:
+        torch.ops.rwkv.mm8_seq(T, N, M, x.cuda(), *dev, y)
+        torch.cuda.synchronize()
+    finally:
+        lib().rwkv_mm8_seq_set_path(0)
+    err = (y.float().cpu() - ref).abs()
+    assert (err <= 2 * 2.0 ** -10 * ref.abs().clamp(min=1.0)).all(), err.max().item()
