@@ -68,7 +68,7 @@ class RWKV:
             self.RESCALE_LAYER = 6      # 'fp16' in strategy (model.py:634)
         self._use_graph = os.environ.get("RWKV_B200_GRAPH", "1") != "0"
         # RWKV_B200_EXACT=1: decode matmuls in fp32 arithmetic instead of 16-bit fixed-point activations
-        # (process-wide; about 10 % slower; see rwkv_mm8_one_set_variant in include/rwkv_b200.h)
+        # (process-wide; about 20 % slower; see rwkv_mm8_one_set_variant in include/rwkv_b200.h)
         if os.environ.get("RWKV_B200_EXACT", "0") == "1":
             lib().rwkv_mm8_one_set_variant(8)
 
