@@ -12,8 +12,9 @@
 //     carries ~22 bits of x' and matches the fp32 CUDA-core kernel to rounding.
 //
 // CTA = 128 (rows of x) x 256 (columns of W) output tile, K in blocks of 64, 3 stages.
-//   warps 0-7  producers (cp.async of the A tiles; W rows are fetched four K blocks ahead into
-//              registers and converted into the B tile), then epilogue: tcgen05.ld of their
+//   warps 0-7  producers: one thread starts the bulk copies of the A tiles (the preparation kernel stores them
+//              as ready-made 16 KB operand images); all of them fetch W rows four K blocks ahead into
+//              registers and convert them into the B tile.  Then epilogue: tcgen05.ld of their
 //              32 TMEM lanes (warp % 4) x 128 columns (warp / 4), affine epilogue, fp16 stores
 //   warp 8     TMEM allocation; lane 0 issues tcgen05.mma and tcgen05.commit
 // Synchronisation is by mbarriers only.  Every wait is bounded: on give-up the CTA raises an
@@ -38,6 +39,17 @@ constexpr uint32_t kLBO = 128;                           // bytes between core m
 constexpr uint32_t kSBO = (BK / 8) * 128;                // A: bytes between 8-row groups
 constexpr unsigned kWaitLimit = 1u << 22;
 
+// Optional timeline of one CTA for tuning (compiled in only with -DRWKV_SEQ_TRACE): per K block the clock
+// after the producers' wait, after their A copies were issued, after the B tile was stored, and on the MMA
+// thread after its wait and after the issue.
+#ifdef RWKV_SEQ_TRACE
+constexpr int kTraceBlocks = 512;
+__device__ long long g_seq_trace[2][kTraceBlocks][5];
+#define SEQ_STAMP(kb, slot) do { if (traced && (kb) < kTraceBlocks) g_seq_trace[trace_row][kb][slot] = clock64(); } while (0)
+#else
+#define SEQ_STAMP(kb, slot) do { } while (0)
+#endif
+
 __device__ __forceinline__ uint32_t s2u(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -55,13 +67,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
     return false;
 }
-// zero-filling 16-byte async copy (src_bytes = 0 writes zeros)
-__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+// one arrival on `bar` that also announces `bytes` of bulk-copy traffic to it
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// arrive on `bar` when all cp.async of this thread issued so far have landed
-__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+// contiguous global -> shared bulk copy (both addresses 16-byte aligned, bytes % 16 == 0) that reports to `bar`
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"((uint64_t)__cvta_generic_to_global(src)), "r"(bytes), "r"(bar) : "memory");
 }
 
 // Shared-memory matrix descriptor: K-major, no swizzle, core matrices of 8 rows x 16 bytes.
@@ -93,37 +106,74 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 }
 
 // ---- preparation: x' hi/lo split and the three row sums ---------------------------------------
+// hi and lo are written in the order the GEMM consumes them: for every (128-row tile, K block of 64) one
+// contiguous 16 KB image of the shared-memory operand tile (core matrices of 8 rows x 16 bytes, 128 bytes
+// between K chunks, 1 KB between 8-row groups), so that the GEMM fetches a tile with one bulk copy.  Rows
+// from T up to the end of the last tile and columns from N up to the end of the last K block are zeros.
+// One block = 8 rows (one group of core matrices); thread = (row, 16-byte chunk of 8 k).
 template <typename F>
-__global__ void __launch_bounds__(256) mm8_seq_prep(int T, int N, int Npad, const F* __restrict__ x, long long x_stride,
-                                                    const F* __restrict__ ry, const F* __restrict__ my,
-                                                    __half* __restrict__ hi, __half* __restrict__ lo,
+__device__ __forceinline__ void load8(const F* __restrict__ p, long long base, int k0, int N, bool vec, float (&out)[8]) {
+    if (vec && k0 + 8 <= N) {
+        if constexpr (sizeof(F) == 2) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(p + base + k0));
+            const F* h = reinterpret_cast<const F*>(&v);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) out[e] = to_f32<F>(h[e]);
+            return;
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = (k0 + e < N) ? to_f32<F>(p[base + k0 + e]) : 0.f;
+}
+
+template <typename F>
+__global__ void __launch_bounds__(256) mm8_seq_prep(int T, int N, int nkb, const F* __restrict__ x, long long x_stride,
+                                                    const F* __restrict__ ry, const F* __restrict__ my, int vec_x, int vec_v,
+                                                    uint8_t* __restrict__ hi, uint8_t* __restrict__ lo,
                                                     float* __restrict__ sums) {
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int t = blockIdx.x;
-    __shared__ float sh[3][8];
+    const int row = threadIdx.x & 7, cl = threadIdx.x >> 3;          // cl: 0..31
+    const int t = blockIdx.x * 8 + row;
+    const int rt = blockIdx.x >> 4, group = blockIdx.x & 15;         // 128-row tile, 8-row group within it
+    __shared__ float sh[3][8][8];
     float sx = 0.f, sxr = 0.f, sxmy = 0.f;
-    for (int k = threadIdx.x; k < Npad; k += 256) {
-        float xp = 0.f;
-        if (k < N) {
-            const float xv = to_f32<F>(x[(long long)t * x_stride + k]);
-            xp = xv * to_f32<F>(ry[k]);
-            sx += xv;
-            sxr += xp;
-            sxmy = fmaf(xv, to_f32<F>(my[k]), sxmy);
+    for (int c = cl; c < nkb * 8; c += 32) {
+        const int k0 = c * 8;
+        uint4 h4 = make_uint4(0, 0, 0, 0), l4 = make_uint4(0, 0, 0, 0);
+        if (t < T && k0 < N) {
+            float xv[8], rv[8], mv[8];
+            load8<F>(x, (long long)t * x_stride, k0, N, vec_x != 0, xv);
+            load8<F>(ry, 0, k0, N, vec_v != 0, rv);
+            load8<F>(my, 0, k0, N, vec_v != 0, mv);
+            __half* hh = reinterpret_cast<__half*>(&h4);
+            __half* lh = reinterpret_cast<__half*>(&l4);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float xp = xv[e] * rv[e];
+                sx += xv[e];
+                sxr += xp;
+                sxmy = fmaf(xv[e], mv[e], sxmy);
+                hh[e] = __float2half_rn(xp);
+                lh[e] = __float2half_rn(xp - __half2float(hh[e]));
+            }
         }
-        const __half h = __float2half_rn(xp);
-        hi[(long long)t * Npad + k] = h;
-        lo[(long long)t * Npad + k] = __float2half_rn(xp - __half2float(h));
+        const size_t off = (size_t(rt) * nkb + (c >> 3)) * kTileBytes + group * kSBO + (c & 7) * kLBO + row * 16;
+        *reinterpret_cast<uint4*>(hi + off) = h4;
+        *reinterpret_cast<uint4*>(lo + off) = l4;
     }
-    sx = warp_sum(sx); sxr = warp_sum(sxr); sxmy = warp_sum(sxmy);
+    // row sums: lanes 8 and 16 apart hold the same row, then the 8 warps in order
+    sx += __shfl_xor_sync(0xffffffffu, sx, 8);   sx += __shfl_xor_sync(0xffffffffu, sx, 16);
+    sxr += __shfl_xor_sync(0xffffffffu, sxr, 8); sxr += __shfl_xor_sync(0xffffffffu, sxr, 16);
+    sxmy += __shfl_xor_sync(0xffffffffu, sxmy, 8); sxmy += __shfl_xor_sync(0xffffffffu, sxmy, 16);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) { sh[0][warp] = sx; sh[1][warp] = sxr; sh[2][warp] = sxmy; }
+    if (lane < 8) { sh[0][warp][lane] = sx; sh[1][warp][lane] = sxr; sh[2][warp][lane] = sxmy; }
     __syncthreads();
-    if (threadIdx.x < 3) {
+    if (threadIdx.x < 24) {
+        const int which = threadIdx.x >> 3, r = threadIdx.x & 7;
         float s = 0.f;
-        for (int i = 0; i < 8; ++i) s += sh[threadIdx.x][i];
-        sums[t * 4 + threadIdx.x] = s;
+        for (int i = 0; i < 8; ++i) s += sh[which][i][r];
+        if (blockIdx.x * 8 + r < T) sums[(blockIdx.x * 8 + r) * 4 + which] = s;
     }
 }
 
@@ -144,7 +194,7 @@ __device__ __forceinline__ uint4 bytes_to_half8(uint32_t lo4, uint32_t hi4) {
 }
 
 struct TcArgs {
-    const __half* hi; const __half* lo; long long lda;      // [T, Npad] fp16 (K contiguous)
+    const uint8_t* hi; const uint8_t* lo;                     // fp16 operand tile images [row tile][K block][16 KB]
     const float* sums;                                        // [T, 4]: SX, SXR, SXMY
     const uint8_t* w; long long w_stride;
     const void* mx; const void* rx;                           // [M] in the output dtype
@@ -168,6 +218,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
     const int nkb_all = (a.N + BK - 1) / BK;
     const int kbase = a.ksplit > 1 ? int(blockIdx.z) * a.kb_per : 0;            // first K block of this CTA
     const int nkb = a.ksplit > 1 ? max(0, min(nkb_all, kbase + a.kb_per) - kbase) : nkb_all;
+#ifdef RWKV_SEQ_TRACE
+    const bool last_cta = blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1;
+    const bool traced = (tid == 0 || tid == kProducers) && blockIdx.z == 0 && ((blockIdx.x == 0 && blockIdx.y == 0) || last_cta);
+    const int trace_row = last_cta ? 1 : 0;
+#endif
 
     uint8_t* bars = smem + STAGES * kStageBytes;
     const uint32_t full0 = s2u(bars), empty0 = full0 + STAGES * 8, accum_bar = empty0 + STAGES * 8;
@@ -176,7 +231,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full0 + s * 8, 2 * kProducers);    // per producer: its cp.async arrival + its own arrive
+            mbar_init(full0 + s * 8, kProducers + 1);    // every producer's B part + the thread that starts the A copies
             mbar_init(empty0 + s * 8, 1);                // tcgen05.commit
         }
         mbar_init(accum_bar, 1);
@@ -220,23 +275,17 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                 const uint32_t ph = (kb / STAGES) & 1;
                 ok = mbar_wait(empty0 + s * 8, ph ^ 1);
                 if (!ok) continue;
+                SEQ_STAMP(kb, 0);
                 uint8_t* stage = smem + s * kStageBytes;
-                // A tiles: 128 rows x 8 chunks of 16 bytes, twice (hi, lo); 4 chunks per thread each
-                const uint32_t a_hi = s2u(stage), a_lo = a_hi + kTileBytes;
-#pragma unroll
-                for (int i = 0; i < (128 * 8) / kProducers; ++i) {
-                    // 8 consecutive lanes = the 8 rows of one core matrix: 128 contiguous bytes of
-                    // shared memory per store phase, 64 contiguous bytes per row on the global side
-                    const int c = tid + i * kProducers;
-                    const int row = ((c >> 6) << 3) | (c & 7), kc = (c >> 3) & 7;
-                    const int t = m0 + row, k = (kbase + kb) * BK + kc * 8;
-                    const bool in = t < a.T && k < a.lda;    // hi/lo are zero padded up to lda
-                    const long long off = in ? (long long)t * a.lda + k : 0;
-                    const uint32_t dst = (row >> 3) * kSBO + kc * kLBO + (row & 7) * 16;
-                    cp_async16_zfill(a_hi + dst, a.hi + off, in ? 16 : 0);
-                    if (!a.single) cp_async16_zfill(a_lo + dst, a.lo + off, in ? 16 : 0);
+                // A tiles: one bulk copy each (hi, lo) of the 16 KB image the preparation kernel laid out
+                if (tid == 0) {
+                    const uint32_t a_hi = s2u(stage), a_lo = a_hi + kTileBytes;
+                    const size_t src = (size_t(blockIdx.y) * nkb_all + kbase + kb) * kTileBytes;
+                    mbar_arrive_expect_tx(full0 + s * 8, a.single ? kTileBytes : 2 * kTileBytes);
+                    bulk_g2s(a_hi, a.hi + src, kTileBytes, full0 + s * 8);
+                    if (!a.single) bulk_g2s(a_lo, a.lo + src, kTileBytes, full0 + s * 8);
                 }
-                cp_async_arrive(full0 + s * 8);
+                SEQ_STAMP(kb, 1);
                 // B tile: transpose this thread's 8x8 byte block, convert, store one core matrix
                 uint32_t lo4[8], hi4[8];                 // column j: bytes of k = 0..3 and k = 4..7
                 {
@@ -264,6 +313,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                 for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(bt + j * 16) = bytes_to_half8(lo4[j], hi4[j]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(full0 + s * 8);
+                SEQ_STAMP(kb, 2);
             }
         }
         // ================= epilogue =================
@@ -341,6 +391,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
             const uint32_t ph = (kb / STAGES) & 1;
             ok = mbar_wait(full0 + s * 8, ph);
             if (!ok) break;
+            SEQ_STAMP(kb, 3);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             const uint32_t a_hi = s2u(smem + s * kStageBytes), a_lo = a_hi + kTileBytes, b_t = a_hi + 2 * kTileBytes;
@@ -351,6 +402,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                 if (!a.single) umma_f16(tmem_base, umma_desc(a_lo + j * 2 * kLBO, kSBO), bd, idesc, 1u);
             }
             umma_commit(empty0 + s * 8);                 // frees the stage when these MMAs retire
+            SEQ_STAMP(kb, 4);
         }
         if (ok) umma_commit(accum_bar);                  // accumulator complete
         else atomicExch(failed, 1);
@@ -358,6 +410,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (*failed) {                                       // a wait gave up: give bulk copies still in flight time to land
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
     if (warp == kProdWarps) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
@@ -397,13 +453,17 @@ static inline int64_t tc_mpad(int64_t M) { return (M + BN - 1) / BN * BN; }
 
 }  // namespace
 
-// Scratch of the tensor-core path: hi and lo copies of x' ([B, Npad] fp16 each), the row sums,
-// one error word and, for split-K launches, the fp32 partial sums [splits][B][M rounded up to 256].
+// Scratch of the tensor-core path: one error word, the row sums, the hi and lo operand tile images of x'
+// (whole 128-row tiles x whole K blocks, fp16 each) and, for split-K launches, the fp32 partial sums
+// [splits][B][M rounded up to 256].
+static inline size_t tc_sums_end(int64_t B) { return (256 + size_t(B) * 16 + 255) / 256 * 256; }
+static inline size_t tc_image_bytes(int64_t B, int64_t N) {          // one of hi, lo
+    return size_t((B + BM - 1) / BM) * size_t((N + BK - 1) / BK) * kTileBytes;
+}
 extern "C" size_t rwkv_mm8_seq_tc_workspace_bytes(int64_t B, int64_t N, int64_t M) {
-    const int64_t npad = (N + BK - 1) / BK * BK;
     const int ks = tc_ksplit(B, N, M);
     const size_t part = ks > 1 ? size_t(ks) * size_t(B) * size_t(tc_mpad(M)) * 4 : 0;
-    return (size_t(B) * size_t(npad) * 4 + size_t(B) * 16 + 256 + 255) / 256 * 256 + part;
+    return tc_sums_end(B) + 2 * tc_image_bytes(B, N) + part;
 }
 
 // Returns RWKV_ERR_UNSUPPORTED when the operands do not meet the layout the tensor-core kernel
@@ -418,19 +478,22 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
     if (workspace == nullptr || workspace_bytes < rwkv_mm8_seq_tc_workspace_bytes(B, N, M)) return RWKV_ERR_WORKSPACE;
     RWKV_CHECK_ALIGN(workspace, 256);
     if ((B + BM - 1) / BM > 65535) return RWKV_ERR_UNSUPPORTED;
-    const int64_t npad = (N + BK - 1) / BK * BK;
+    const int nkb_all = int((N + BK - 1) / BK);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     unsigned* err = reinterpret_cast<unsigned*>(ws);
     float* sums = reinterpret_cast<float*>(ws + 256);
-    __half* hi = reinterpret_cast<__half*>(ws + 256 + size_t(B) * 16);
-    __half* lo = hi + size_t(B) * size_t(npad);
+    uint8_t* hi = ws + tc_sums_end(B);
+    uint8_t* lo = hi + tc_image_bytes(B, N);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int rc = rwkv_launch_pdl(mm8_seq_prep<__half>, dim3((unsigned)B), dim3(256), 0, st, int(B), int(N), int(npad),
+    const int vec_x = (reinterpret_cast<uintptr_t>(x) % 16 == 0 && x_stride % 8 == 0) ? 1 : 0;
+    const int vec_v = (reinterpret_cast<uintptr_t>(ry) % 16 == 0 && reinterpret_cast<uintptr_t>(my) % 16 == 0) ? 1 : 0;
+    const unsigned groups = (unsigned)((B + BM - 1) / BM) * (BM / 8);          // 8-row groups of whole row tiles
+    int rc = rwkv_launch_pdl(mm8_seq_prep<__half>, dim3(groups), dim3(256), 0, st, int(B), int(N), nkb_all,
                              static_cast<const __half*>(x), (long long)x_stride, static_cast<const __half*>(ry),
-                             static_cast<const __half*>(my), hi, lo, sums);
+                             static_cast<const __half*>(my), vec_x, vec_v, hi, lo, sums);
     if (rc != RWKV_OK) return rc;
     TcArgs a;
-    a.hi = hi; a.lo = lo; a.lda = npad; a.sums = sums; a.w = w; a.w_stride = w_stride; a.mx = mx; a.rx = rx;
+    a.hi = hi; a.lo = lo; a.sums = sums; a.w = w; a.w_stride = w_stride; a.mx = mx; a.rx = rx;
     a.y = y; a.y_stride = y_stride; a.T = int(B); a.N = int(N); a.M = int(M); a.error_flag = err;
     a.single = g_tc_single;
     a.vec_ok = (reinterpret_cast<uintptr_t>(y) % 16 == 0 && y_stride % 8 == 0 && reinterpret_cast<uintptr_t>(rx) % 16 == 0 &&
@@ -445,12 +508,11 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
         configured = true;
     }
     int ks = tc_ksplit(B, N, M);
-    const int nkb_all = int((N + BK - 1) / BK);
     a.kb_per = (nkb_all + ks - 1) / ks;
     ks = (nkb_all + a.kb_per - 1) / a.kb_per;          // no empty split
     a.ksplit = ks;
     a.m_pad = int(tc_mpad(M));
-    a.partial = reinterpret_cast<float*>(ws + (size_t(B) * size_t(npad) * 4 + size_t(B) * 16 + 256 + 255) / 256 * 256);
+    a.partial = reinterpret_cast<float*>(ws + tc_sums_end(B) + 2 * tc_image_bytes(B, N));
     dim3 grid((unsigned)((M + BN - 1) / BN), (unsigned)((B + BM - 1) / BM), (unsigned)ks);
     rc = rwkv_launch_pdl(kern, grid, dim3(kThreadsTc), size_t(kSmemTc), st, a);
     if (rc != RWKV_OK || ks == 1) return rc;
