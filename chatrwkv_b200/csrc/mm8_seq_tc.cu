@@ -12,11 +12,12 @@
 //     carries ~22 bits of x' and matches the fp32 CUDA-core kernel to rounding.
 //
 // CTA = 128 (rows of x) x 256 (columns of W) output tile, K in blocks of 64, 3 stages.
-//   warps 0-7  producers: one thread starts the bulk copies of the A tiles (the preparation kernel stores them
-//              as ready-made 16 KB operand images); all of them fetch W rows four K blocks ahead into
-//              registers and convert them into the B tile.  Then epilogue: tcgen05.ld of their
-//              32 TMEM lanes (warp % 4) x 128 columns (warp / 4), affine epilogue, fp16 stores
-//   warp 8     TMEM allocation; lane 0 issues tcgen05.mma and tcgen05.commit
+//   warps 0-15 producers: fetch W rows four K blocks ahead into registers (8 k x 4 columns per thread and
+//              K block) and convert them into the B tile.  Then epilogue: tcgen05.ld of their
+//              32 TMEM lanes (warp % 4) x 64 columns (warp / 4), affine epilogue, fp16 stores
+//   warp 16    TMEM allocation; lane 0 issues tcgen05.mma and tcgen05.commit
+//   warp 17    lane 0 starts the bulk copies of the A tiles (the preparation kernel stores them as
+//              ready-made 16 KB operand images)
 // Synchronisation is by mbarriers only.  Every wait is bounded: on give-up the CTA raises an
 // error word, skips the rest of its work, frees its tensor memory and returns.
 #include "common.cuh"
@@ -24,9 +25,9 @@
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 3;
-constexpr int kProducers = 256;
+constexpr int kProducers = 512;
 constexpr int kProdWarps = kProducers / 32;
-constexpr int kThreadsTc = kProducers + 32;
+constexpr int kThreadsTc = kProducers + 64;              // + the MMA warp and the warp that starts the A copies
 constexpr int kWAhead = 4;                               // K blocks of W held in registers
 constexpr int kTileBytes = 128 * BK * 2;                 // 16 KB: one 128 x 64 fp16 operand tile
 constexpr uint32_t kSBO_B = (BK / 8) * 128 + 16;         // B: 8-row groups 16 bytes further apart, so that the
@@ -220,7 +221,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
     const int nkb = a.ksplit > 1 ? max(0, min(nkb_all, kbase + a.kb_per) - kbase) : nkb_all;
 #ifdef RWKV_SEQ_TRACE
     const bool last_cta = blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1;
-    const bool traced = (tid == 0 || tid == kProducers) && blockIdx.z == 0 && ((blockIdx.x == 0 && blockIdx.y == 0) || last_cta);
+    const bool traced = (tid == 0 || tid == kProducers || tid == kProducers + 32) && blockIdx.z == 0 && ((blockIdx.x == 0 && blockIdx.y == 0) || last_cta);
     const int trace_row = last_cta ? 1 : 0;
 #endif
 
@@ -250,70 +251,64 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
 
     if (warp < kProdWarps) {
         // ================= producers =================
-        const int cg = tid & 31, rg = tid >> 5;          // B: 8 columns x 8 k-rows per thread
-        const int ncol = n0 + cg * 8;
+        const int cg = tid & 63, rg = tid >> 6;          // B: 4 columns x 8 k-rows per thread
+        const int ncol = n0 + cg * 4;
         const bool col_ok = ncol < a.M;                  // M % 8 == 0 is a launch condition
-        uint2 wreg[kWAhead][8];                          // W rows of the next kWAhead K blocks
-        auto load_w = [&](int kb, uint2 (&dst)[8]) {
+        uint32_t wreg[kWAhead][8];                       // W rows of the next kWAhead K blocks
+        auto load_w = [&](int kb, uint32_t (&dst)[8]) {
+            const int k0 = (kbase + kb) * BK + rg * 8;
+            const uint8_t* p = a.w + (long long)k0 * a.w_stride + ncol;
+            if (col_ok && k0 + 8 <= a.N) {                   // all but the ragged edges: one add per row
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int k = (kbase + kb) * BK + rg * 8 + i;
-                dst[i] = (col_ok && k < a.N) ? __ldg(reinterpret_cast<const uint2*>(a.w + (long long)k * a.w_stride + ncol))
-                                             : make_uint2(0x80808080u, 0x80808080u);   // code 128 -> value 0
+                for (int i = 0; i < 8; ++i) {
+                    dst[i] = __ldg(reinterpret_cast<const uint32_t*>(p));
+                    p += a.w_stride;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    dst[i] = (col_ok && k0 + i < a.N) ? __ldg(reinterpret_cast<const uint32_t*>(p + (long long)i * a.w_stride))
+                                                      : 0x80808080u;      // code 128 -> value 0
             }
         };
 #pragma unroll
         for (int u = 0; u < kWAhead; ++u)
             if (u < nkb) load_w(u, wreg[u]);
         bool ok = true;
+        int s = 0;                                           // stage of K block kb and the parity of its use
+        uint32_t ph = 0;
         for (int kb0 = 0; kb0 < nkb && ok; kb0 += kWAhead) {
 #pragma unroll
             for (int u = 0; u < kWAhead; ++u) {
                 const int kb = kb0 + u;
                 if (kb >= nkb || !ok) continue;
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
                 ok = mbar_wait(empty0 + s * 8, ph ^ 1);
                 if (!ok) continue;
                 SEQ_STAMP(kb, 0);
                 uint8_t* stage = smem + s * kStageBytes;
-                // A tiles: one bulk copy each (hi, lo) of the 16 KB image the preparation kernel laid out
-                if (tid == 0) {
-                    const uint32_t a_hi = s2u(stage), a_lo = a_hi + kTileBytes;
-                    const size_t src = (size_t(blockIdx.y) * nkb_all + kbase + kb) * kTileBytes;
-                    mbar_arrive_expect_tx(full0 + s * 8, a.single ? kTileBytes : 2 * kTileBytes);
-                    bulk_g2s(a_hi, a.hi + src, kTileBytes, full0 + s * 8);
-                    if (!a.single) bulk_g2s(a_lo, a.lo + src, kTileBytes, full0 + s * 8);
-                }
-                SEQ_STAMP(kb, 1);
-                // B tile: transpose this thread's 8x8 byte block, convert, store one core matrix
-                uint32_t lo4[8], hi4[8];                 // column j: bytes of k = 0..3 and k = 4..7
-                {
-                    uint32_t x0[2], x1[2];
+                // B tile: transpose this thread's 8 (k) x 4 (columns) byte block, convert, store four
+                // rows of one core matrix: column j holds k = 0..3 in lo4[j] and k = 4..7 in hi4[j]
+                uint32_t lo4[4], hi4[4];
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {   // rows 0-3, rows 4-7
-                        const uint2* r = &wreg[u][half * 4];
-#pragma unroll
-                        for (int q = 0; q < 2; ++q) {        // columns 0-3 (.x), 4-7 (.y)
-                            const uint32_t a0 = q ? r[0].y : r[0].x, a1 = q ? r[1].y : r[1].x;
-                            const uint32_t a2 = q ? r[2].y : r[2].x, a3 = q ? r[3].y : r[3].x;
-                            x0[0] = __byte_perm(a0, a1, 0x5140); x0[1] = __byte_perm(a2, a3, 0x5140);
-                            x1[0] = __byte_perm(a0, a1, 0x7362); x1[1] = __byte_perm(a2, a3, 0x7362);
-                            uint32_t* dstw = half ? hi4 : lo4;
-                            dstw[q * 4 + 0] = __byte_perm(x0[0], x0[1], 0x5410);
-                            dstw[q * 4 + 1] = __byte_perm(x0[0], x0[1], 0x7632);
-                            dstw[q * 4 + 2] = __byte_perm(x1[0], x1[1], 0x5410);
-                            dstw[q * 4 + 3] = __byte_perm(x1[0], x1[1], 0x7632);
-                        }
-                    }
+                for (int half = 0; half < 2; ++half) {       // k rows 0-3, 4-7
+                    const uint32_t a0 = wreg[u][half * 4 + 0], a1 = wreg[u][half * 4 + 1];
+                    const uint32_t a2 = wreg[u][half * 4 + 2], a3 = wreg[u][half * 4 + 3];
+                    const uint32_t x00 = __byte_perm(a0, a1, 0x5140), x01 = __byte_perm(a2, a3, 0x5140);
+                    const uint32_t x10 = __byte_perm(a0, a1, 0x7362), x11 = __byte_perm(a2, a3, 0x7362);
+                    uint32_t* dstw = half ? hi4 : lo4;
+                    dstw[0] = __byte_perm(x00, x01, 0x5410);
+                    dstw[1] = __byte_perm(x00, x01, 0x7632);
+                    dstw[2] = __byte_perm(x10, x11, 0x5410);
+                    dstw[3] = __byte_perm(x10, x11, 0x7632);
                 }
                 if (kb + kWAhead < nkb) load_w(kb + kWAhead, wreg[u]);   // refill this register slot
-                uint8_t* bt = stage + 2 * kTileBytes + cg * kSBO_B + rg * kLBO;
+                uint8_t* bt = stage + 2 * kTileBytes + (cg >> 1) * kSBO_B + rg * kLBO + (cg & 1) * 64;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(bt + j * 16) = bytes_to_half8(lo4[j], hi4[j]);
+                for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(bt + j * 16) = bytes_to_half8(lo4[j], hi4[j]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(full0 + s * 8);
                 SEQ_STAMP(kb, 2);
+                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
         }
         // ================= epilogue =================
@@ -321,7 +316,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
         if (!ok) atomicExch(failed, 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
-            const int quarter = warp & 3, chalf = warp >> 2;     // TMEM lanes 32*quarter.., columns 128*chalf..
+            const int quarter = warp & 3, cq = warp >> 2;        // TMEM lanes 32*quarter.., columns 64*cq..
             const int t = m0 + quarter * 32 + lane;
             float sx = 0.f, sxr = 0.f, sxmy = 0.f;
             if (t < a.T) { sx = a.sums[t * 4 + 0]; sxr = a.sums[t * 4 + 1]; sxmy = a.sums[t * 4 + 2]; }
@@ -329,7 +324,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
             const F* rx = static_cast<const F*>(a.rx);
             F* yrow = static_cast<F*>(a.y) + (long long)t * a.y_stride;
 #pragma unroll 1
-            for (int c = chalf * 4; c < chalf * 4 + 4; ++c) {
+            for (int c = cq * 2; c < cq * 2 + 2; ++c) {
                 uint32_t v[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 32;
                 asm volatile(
@@ -381,6 +376,24 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                     }
                 }
             }
+        }
+    } else if (warp == kProdWarps + 1) {
+        // ================= A tiles: one bulk copy each (hi, lo) of the 16 KB image the preparation kernel laid out
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                ok = mbar_wait(empty0 + s * 8, ph ^ 1);
+                if (!ok) break;
+                const uint32_t a_hi = s2u(smem + s * kStageBytes), a_lo = a_hi + kTileBytes;
+                const size_t src = (size_t(blockIdx.y) * nkb_all + kbase + kb) * kTileBytes;
+                mbar_arrive_expect_tx(full0 + s * 8, a.single ? kTileBytes : 2 * kTileBytes);
+                bulk_g2s(a_hi, a.hi + src, kTileBytes, full0 + s * 8);
+                if (!a.single) bulk_g2s(a_lo, a.lo + src, kTileBytes, full0 + s * 8);
+                SEQ_STAMP(kb, 1);
+            }
+            if (!ok) atomicExch(failed, 1);
         }
     } else if (lane == 0) {
         // ================= MMA issuer =================
