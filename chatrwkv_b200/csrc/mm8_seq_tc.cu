@@ -21,6 +21,7 @@
 // Synchronisation is by mbarriers only.  Every wait is bounded: on give-up the CTA raises an
 // error word, skips the rest of its work, frees its tensor memory and returns.
 #include "common.cuh"
+#include <algorithm>
 
 namespace {
 
@@ -109,9 +110,12 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 // ---- preparation: x' hi/lo split and the three row sums ---------------------------------------
 // hi and lo are written in the order the GEMM consumes them: for every (128-row tile, K block of 64) one
 // contiguous 16 KB image of the shared-memory operand tile (core matrices of 8 rows x 16 bytes, 128 bytes
-// between K chunks, 1 KB between 8-row groups), so that the GEMM fetches a tile with one bulk copy.  Rows
-// from T up to the end of the last tile and columns from N up to the end of the last K block are zeros.
-// One block = 8 rows (one group of core matrices); thread = (row, 16-byte chunk of 8 k).
+// between K chunks, 1 KB between 8-row groups), so that the GEMM fetches a tile with one bulk copy.
+// Columns from N up to the end of the last K block are zeros; rows from T up to the end of the last tile
+// are left as they are (an output row depends on its own row of x' only, and those rows are not stored).
+// One block = 8 rows (one group of core matrices) x one share of the K range (blockIdx.y, so that short
+// sequences still fill the GPU); thread = (row, 16-byte chunk of 8 k).  Each share writes its own partial
+// row sums, which the consumers add in share order.
 template <typename F>
 __device__ __forceinline__ void load8(const F* __restrict__ p, long long base, int k0, int N, bool vec, float (&out)[8]) {
     if (vec && k0 + 8 <= N) {
@@ -130,7 +134,7 @@ __device__ __forceinline__ void load8(const F* __restrict__ p, long long base, i
 template <typename F>
 __global__ void __launch_bounds__(256) mm8_seq_prep(int T, int N, int nkb, const F* __restrict__ x, long long x_stride,
                                                     const F* __restrict__ ry, const F* __restrict__ my, int vec_x, int vec_v,
-                                                    uint8_t* __restrict__ hi, uint8_t* __restrict__ lo,
+                                                    int chunks_per, uint8_t* __restrict__ hi, uint8_t* __restrict__ lo,
                                                     float* __restrict__ sums) {
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -139,10 +143,12 @@ __global__ void __launch_bounds__(256) mm8_seq_prep(int T, int N, int nkb, const
     const int rt = blockIdx.x >> 4, group = blockIdx.x & 15;         // 128-row tile, 8-row group within it
     __shared__ float sh[3][8][8];
     float sx = 0.f, sxr = 0.f, sxmy = 0.f;
-    for (int c = cl; c < nkb * 8; c += 32) {
+    const int c_begin = blockIdx.y * chunks_per, c_end = min(nkb * 8, c_begin + chunks_per);
+    for (int c = c_begin + cl; c < c_end; c += 32) {
+        if (t >= T) break;
         const int k0 = c * 8;
         uint4 h4 = make_uint4(0, 0, 0, 0), l4 = make_uint4(0, 0, 0, 0);
-        if (t < T && k0 < N) {
+        if (k0 < N) {
             float xv[8], rv[8], mv[8];
             load8<F>(x, (long long)t * x_stride, k0, N, vec_x != 0, xv);
             load8<F>(ry, 0, k0, N, vec_v != 0, rv);
@@ -174,7 +180,7 @@ __global__ void __launch_bounds__(256) mm8_seq_prep(int T, int N, int nkb, const
         const int which = threadIdx.x >> 3, r = threadIdx.x & 7;
         float s = 0.f;
         for (int i = 0; i < 8; ++i) s += sh[which][i][r];
-        if (blockIdx.x * 8 + r < T) sums[(blockIdx.x * 8 + r) * 4 + which] = s;
+        if (blockIdx.x * 8 + r < T) sums[((size_t)blockIdx.y * T + blockIdx.x * 8 + r) * 4 + which] = s;
     }
 }
 
@@ -196,7 +202,7 @@ __device__ __forceinline__ uint4 bytes_to_half8(uint32_t lo4, uint32_t hi4) {
 
 struct TcArgs {
     const uint8_t* hi; const uint8_t* lo;                     // fp16 operand tile images [row tile][K block][16 KB]
-    const float* sums;                                        // [T, 4]: SX, SXR, SXMY
+    const float* sums; int nsum;                              // [nsum][T][4]: partial SX, SXR, SXMY, added in order
     const uint8_t* w; long long w_stride;
     const void* mx; const void* rx;                           // [M] in the output dtype
     void* y; long long y_stride;
@@ -319,7 +325,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
             const int quarter = warp & 3, cq = warp >> 2;        // TMEM lanes 32*quarter.., columns 64*cq..
             const int t = m0 + quarter * 32 + lane;
             float sx = 0.f, sxr = 0.f, sxmy = 0.f;
-            if (t < a.T) { sx = a.sums[t * 4 + 0]; sxr = a.sums[t * 4 + 1]; sxmy = a.sums[t * 4 + 2]; }
+            if (t < a.T)
+                for (int z = 0; z < a.nsum; ++z) {
+                    const float* sp = a.sums + ((size_t)z * a.T + t) * 4;
+                    sx += sp[0]; sxr += sp[1]; sxmy += sp[2];
+                }
             const F* mx = static_cast<const F*>(a.mx);
             const F* rx = static_cast<const F*>(a.rx);
             F* yrow = static_cast<F*>(a.y) + (long long)t * a.y_stride;
@@ -437,12 +447,16 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
 // y[t][n] = affine(sum over the K splits, in split order) for the split-K launches.
 template <typename F>
 __global__ void __launch_bounds__(256) mm8_seq_reduce(int T, int M, int m_pad, int ksplit, const float* __restrict__ partial,
-                                                      const float* __restrict__ sums, const F* __restrict__ mx,
+                                                      const float* __restrict__ sums, int nsum, const F* __restrict__ mx,
                                                       const F* __restrict__ rx, F* __restrict__ y, long long y_stride) {
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int t = blockIdx.y;
-    const float sx = sums[t * 4 + 0], sxr = sums[t * 4 + 1], sxmy = sums[t * 4 + 2];
+    float sx = 0.f, sxr = 0.f, sxmy = 0.f;
+    for (int z = 0; z < nsum; ++z) {
+        const float* sp = sums + ((size_t)z * T + t) * 4;
+        sx += sp[0]; sxr += sp[1]; sxmy += sp[2];
+    }
     for (int n = blockIdx.x * 256 + threadIdx.x; n < M; n += gridDim.x * 256) {
         float s = 0.f;
         for (int z = 0; z < ksplit; ++z) s += partial[((long long)z * T + t) * m_pad + n];
@@ -469,7 +483,8 @@ static inline int64_t tc_mpad(int64_t M) { return (M + BN - 1) / BN * BN; }
 // Scratch of the tensor-core path: one error word, the row sums, the hi and lo operand tile images of x'
 // (whole 128-row tiles x whole K blocks, fp16 each) and, for split-K launches, the fp32 partial sums
 // [splits][B][M rounded up to 256].
-static inline size_t tc_sums_end(int64_t B) { return (256 + size_t(B) * 16 + 255) / 256 * 256; }
+constexpr int kMaxSumShares = 8;
+static inline size_t tc_sums_end(int64_t B) { return (256 + size_t(kMaxSumShares) * size_t(B) * 16 + 255) / 256 * 256; }
 static inline size_t tc_image_bytes(int64_t B, int64_t N) {          // one of hi, lo
     return size_t((B + BM - 1) / BM) * size_t((N + BK - 1) / BK) * kTileBytes;
 }
@@ -500,13 +515,17 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int vec_x = (reinterpret_cast<uintptr_t>(x) % 16 == 0 && x_stride % 8 == 0) ? 1 : 0;
     const int vec_v = (reinterpret_cast<uintptr_t>(ry) % 16 == 0 && reinterpret_cast<uintptr_t>(my) % 16 == 0) ? 1 : 0;
-    const unsigned groups = (unsigned)((B + BM - 1) / BM) * (BM / 8);          // 8-row groups of whole row tiles
-    int rc = rwkv_launch_pdl(mm8_seq_prep<__half>, dim3(groups), dim3(256), 0, st, int(B), int(N), nkb_all,
-                             static_cast<const __half*>(x), (long long)x_stride, static_cast<const __half*>(ry),
-                             static_cast<const __half*>(my), vec_x, vec_v, hi, lo, sums);
+    const int groups = int((B + 7) / 8);                                       // 8-row groups
+    int shares = std::min(kMaxSumShares, std::max(1, 2 * rwkv_sm_count() / groups));
+    shares = std::max(1, std::min(shares, nkb_all * 8 / 32));                  // at least one chunk per thread
+    const int chunks_per = (nkb_all * 8 + shares - 1) / shares;
+    shares = (nkb_all * 8 + chunks_per - 1) / chunks_per;                      // no empty share
+    int rc = rwkv_launch_pdl(mm8_seq_prep<__half>, dim3((unsigned)groups, (unsigned)shares), dim3(256), 0, st, int(B), int(N),
+                             nkb_all, static_cast<const __half*>(x), (long long)x_stride, static_cast<const __half*>(ry),
+                             static_cast<const __half*>(my), vec_x, vec_v, chunks_per, hi, lo, sums);
     if (rc != RWKV_OK) return rc;
     TcArgs a;
-    a.hi = hi; a.lo = lo; a.sums = sums; a.w = w; a.w_stride = w_stride; a.mx = mx; a.rx = rx;
+    a.hi = hi; a.lo = lo; a.sums = sums; a.nsum = shares; a.w = w; a.w_stride = w_stride; a.mx = mx; a.rx = rx;
     a.y = y; a.y_stride = y_stride; a.T = int(B); a.N = int(N); a.M = int(M); a.error_flag = err;
     a.single = g_tc_single;
     a.vec_ok = (reinterpret_cast<uintptr_t>(y) % 16 == 0 && y_stride % 8 == 0 && reinterpret_cast<uintptr_t>(rx) % 16 == 0 &&
@@ -530,7 +549,7 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
     rc = rwkv_launch_pdl(kern, grid, dim3(kThreadsTc), size_t(kSmemTc), st, a);
     if (rc != RWKV_OK || ks == 1) return rc;
     return rwkv_launch_pdl(mm8_seq_reduce<__half>, dim3((unsigned)((M + 255) / 256), (unsigned)B), dim3(256), 0, st, int(B),
-                           int(M), a.m_pad, ks, (const float*)a.partial, (const float*)sums, static_cast<const __half*>(mx),
+                           int(M), a.m_pad, ks, (const float*)a.partial, (const float*)sums, shares, static_cast<const __half*>(mx),
                            static_cast<const __half*>(rx), static_cast<__half*>(y), (long long)y_stride);
 }
 
