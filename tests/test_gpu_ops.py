@@ -255,10 +255,11 @@ def test_op_schemas(ops):
             assert hasattr(ns, f)
 
 
-@pytest.mark.parametrize("T,N,M", [(128, 256, 128), (64, 64, 128), (200, 768, 3072), (1024, 4096, 512), (257, 1000, 264)])
+@pytest.mark.parametrize("T,N,M", [(128, 256, 128), (64, 64, 128), (200, 768, 3072), (1024, 4096, 512), (257, 1000, 264),
+                                   (130, 100, 304), (13, 4104, 512)])
 def test_mm8_seq_tensor_core_path(ops, T, N, M):
-    """Rows >= 64 with an 8-byte-aligned matrix run on tcgen05; same oracle, same tolerance.
-    Includes ragged T (not a multiple of 128), N (not a multiple of 64) and M (not of 128)."""
+    """Rows >= 8 with an 8-byte-aligned matrix run on tcgen05; same oracle, same tolerance.
+    Includes ragged T (not a multiple of 128 or 8), N (not a multiple of 64 or 8) and M (not of 128)."""
     import ctypes
     from chatrwkv_b200 import _lib
     from tests.util import packed_case
@@ -284,6 +285,28 @@ def test_mm8_seq_tensor_core_path(ops, T, N, M):
     finally:
         _lib.lib().rwkv_mm8_seq_set_path(0)
     assert ((y.float() - y2.float()).abs() <= y2.float().abs() * 2 ** -9 + 2e-4).all()
+
+
+def test_mm8_seq_ignores_stale_scratch_rows(ops):
+    """The operand images keep whatever the scratch held in the rows past T of the last 128-row tile
+    (here: NaN patterns); no stored output may depend on them."""
+    from tests.util import packed_case
+    T, N, M = 130, 512, 256
+    cpu, dev = packed_case(N, M, seed=5)
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(T, N, generator=g).half()
+    ref = orc.mm8_kernel(x, *cpu)
+    y = torch.empty((T, M), dtype=torch.float16, device="cuda")
+    torch.ops.rwkv.mm8_seq(T, N, M, x.cuda(), *dev, y)              # sizes the scratch
+    torch.cuda.synchronize()
+    ws = ops.workspace(torch.device("cuda", torch.cuda.current_device()), 1024, "mm8_seq")
+    ws[256:8 << 20].fill_(0xFF)                                       # fp16 / fp32 NaN everywhere but the error word
+    y.zero_()
+    torch.ops.rwkv.mm8_seq(T, N, M, x.cuda(), *dev, y)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y).all()
+    assert ((y.float().cpu() - ref).abs() <= ref.abs() * 2 ** -10 + 1e-4).all()
+    ws[256:8 << 20].zero_()
 
 
 # ------------------------------------------------------------------- RWKV-5/6 one-token pieces
