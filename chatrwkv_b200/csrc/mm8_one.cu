@@ -370,7 +370,8 @@ extern "C" int rwkv_mm8_one(int64_t N, int64_t M, const void* x, const uint8_t* 
 //
 // `g_static_scratch` names a DEVICE symbol.  In host code that name is only a stand-in: the
 // address a kernel may use comes from cudaGetSymbolAddress, looked up once per device (with
-// that device current) on the first call and remembered in g_static_ptr[].
+// that device current) on the first call and remembered in g_static_ptr[] (filled without a
+// lock: like the tuning hooks, not thread-safe -- make the first call per device from one thread).
 // ---------------------------------------------------------------------------------------------
 namespace {
 constexpr int kStaticMaxM = 32768;

@@ -188,10 +188,7 @@ class RWKV:
                     gc.collect()
 
             if convert_and_save_and_exit:                             # model.py:894-903
-                out = {k: (v.contiguous().cpu() if torch.is_tensor(v) else v) for k, v in w.items()}
-                out["_strategy"] = args.strategy_string
-                out["_rescale_layer"] = self.RESCALE_LAYER
-                out["_version"] = "0.7"
+                out = self.export_converted()
                 if not convert_and_save_and_exit.endswith(".pth"):
                     convert_and_save_and_exit += ".pth"
                 prxxx(f"Saving to {convert_and_save_and_exit}...")
@@ -222,6 +219,18 @@ class RWKV:
         torch.cuda.empty_cache()
 
     # -----------------------------------------------------------------------------------
+    def export_converted(self, strategy_string=None):
+        """The loaded weights as the dict the reference's loader saves for
+        `convert_and_save_and_exit` (model.py:894-903: every tensor already transposed / packed,
+        plus `_strategy`, `_rescale_layer`, `_version`), on the CPU, row padding dropped."""
+        if self._world > 1:
+            raise NotImplementedError("export_converted: column-sharded models hold only their slices")
+        out = {k: (v.contiguous().cpu() if torch.is_tensor(v) else v) for k, v in self.w.items()}
+        out["_strategy"] = strategy_string or self.args.strategy_string
+        out["_rescale_layer"] = self.RESCALE_LAYER
+        out["_version"] = "0.7"
+        return out
+
     @staticmethod
     def _repad(q):
         """Give a contiguous packed matrix the 16-byte row stride the fast kernels want."""

@@ -98,7 +98,11 @@ int rwkv_mm8_one(int64_t N, int64_t M, const void* x, const uint8_t* w, int64_t 
  *   - The array (about 9 MiB) is held on every GPU that loads the library until the process
  *     exits, whether or not this entry point is ever called.
  *   - The first call on each device looks the array's device address up (with the caller's
- *     current device) before launching.  Make that first call outside of any stream capture.
+ *     current device) before launching.  Make that first call outside of any stream capture,
+ *     and from one thread: the per-device lookup is cached without a lock (not thread-safe).
+ *   - Only the split-K kernel reads the array (matrices whose rows are not 16-byte aligned, or any
+ *     matrix after rwkv_mm8_one_set_cluster(-1, 0)); the default cluster kernel for aligned matrices
+ *     reduces in shared memory and leaves the array untouched.
  *   - All calls on a device share the one array, which keeps whatever the previous call left
  *     in it; the call clears the part that has to start at zero on `stream` before the kernel.
  *     Two calls that can overlap on the GPU (different streams, no dependency) race on it:

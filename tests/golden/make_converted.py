@@ -20,7 +20,7 @@ from chatrwkv_b200 import synth  # noqa: E402
 from tests.golden.make_golden import TOY  # noqa: E402
 
 if __name__ == "__main__":
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ["RWKV_REFERENCE_ROOT"]
     sys.path.insert(0, os.path.join(ref_root, "rwkv_pip_package", "src"))
     import rwkv.model as ref
     tmp = tempfile.mkdtemp()
