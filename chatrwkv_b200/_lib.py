@@ -79,6 +79,13 @@ SIGNATURES = {
     "rwkv_mm8_chain_plan": (_i32, [C.POINTER(Mm8Problem), C.POINTER(C.c_int32), _i32, _i32, _i32, _vp, _sz, _vp, _sz]),
     "rwkv_mm8_chain_run": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp]),
     "rwkv_mm8_chain_take_error": (_i32, [_vp, _vp, C.POINTER(C.c_int)]),
+    "rwkv_mm8_stream_ctas": (_i32, []),
+    "rwkv_mm8_stream_weight_bytes": (_sz, [C.POINTER(Mm8Problem), _i32, _i32]),
+    "rwkv_mm8_stream_pack": (_i32, [C.POINTER(Mm8Problem), _i32, _i32, _vp, _sz, _vp]),
+    "rwkv_mm8_stream_table_bytes": (_sz, [_i32]),
+    "rwkv_mm8_stream_plan": (_i32, [C.POINTER(Mm8Problem), C.POINTER(C.c_int32), _i32, _i32, _i32, _vp, _sz]),
+    "rwkv_mm8_stream_run": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "rwkv_mm8_stream_take_error": (_i32, [_vp, _vp, C.POINTER(C.c_int)]),
     "rwkv_mm8_seq_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "rwkv_mm8_seq_set_path": (None, [_i32]),
     "rwkv_mm8_seq_tc_take_error": (_i32, [_vp, _vp, C.POINTER(C.c_int)]),

@@ -282,6 +282,13 @@ class RWKV:
         # (csrc/mm8_chain.cu) instead of four launches per layer.  Both reach the same speed on a
         # B200; the launch-per-matmul path is the default because it contains no wait loop.
         self._use_chain = os.environ.get("RWKV_B200_CHAIN", "0") == "1"
+        # RWKV-4 decode default: the whole token as ONE persistent kernel over a re-tiled copy of the
+        # packed matrices (csrc/mm8_stream.cu); RWKV_B200_STREAM=0 or RWKV_B200_EXACT=1 keep the launch per
+        # matmul.  Costs a second copy of the codes in HBM (the row-major one still serves prefill).
+        self._use_stream = (self.version == 4 and self._world == 1 and not self._use_chain and
+                            os.environ.get("RWKV_B200_STREAM", "1") != "0" and
+                            os.environ.get("RWKV_B200_EXACT", "0") != "1")
+        self._stream = None
         self._mm = {}
 
     def _scales(self, name):
@@ -543,10 +550,61 @@ class RWKV:
         then undefined); synchronises the device."""
         return self._peer.take_error() if self._peer is not None else 0
 
+    def _build_stream(self):
+        """Re-tile the packed matrices for the persistent decode kernel and lay out its phase tables (one per
+        state direction).  Returns False when a matrix does not meet that kernel's limits."""
+        import ctypes as C
+        L = lib()
+        G = L.rwkv_mm8_stream_ctas()
+        tables = []
+        wstream = None
+        for cur in (0, 1):
+            launches = self._launches_v4(cur)
+            flat = [p for probs in launches for p in probs]
+            arr = (_lib.Mm8Problem * len(flat))(*flat)
+            counts = (C.c_int32 * len(launches))(*[len(p) for p in launches])
+            if wstream is None:
+                nbytes = L.rwkv_mm8_stream_weight_bytes(arr, len(flat), G)
+                wstream = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+                rc = L.rwkv_mm8_stream_pack(arr, len(flat), G, wstream.data_ptr(), nbytes,
+                                            torch.cuda.current_stream(self.device).cuda_stream)
+                if rc == _lib.ERR_UNSUPPORTED:
+                    return False
+                check(rc, "mm8_stream_pack")
+            tbytes = L.rwkv_mm8_stream_table_bytes(len(launches))
+            host = torch.zeros(tbytes, dtype=torch.uint8)
+            rc = L.rwkv_mm8_stream_plan(arr, counts, len(launches), _lib.F16, G, host.data_ptr(), tbytes)
+            if rc == _lib.ERR_UNSUPPORTED:
+                return False
+            check(rc, "mm8_stream_plan")
+            tables.append((host, host.to(self.device)))
+        sync = torch.zeros(16, dtype=torch.int32, device=self.device)
+        self._stream = types.SimpleNamespace(wstream=wstream, tables=tables, sync=sync, trace=None, n_phases=len(launches))
+        return True
+
+    def stream_error(self):
+        """1 if a wait inside the persistent decode kernel gave up since the last call (the step's results were
+        then undefined); synchronises the current stream."""
+        import ctypes as C
+        if self._stream is None:
+            return 0
+        e = C.c_int(0)
+        check(lib().rwkv_mm8_stream_take_error(self._stream.sync.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream,
+                                               C.byref(e)), "mm8_stream_take_error")
+        return e.value
+
     def _step_one_v4(self, cur):
         b, w = self._b, self.w
+        if self._use_stream and self._stream is None and not self._build_stream():
+            self._use_stream = False
         torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
-        if self._use_chain:
+        if self._use_stream:
+            st = self._stream
+            host, dev = st.tables[cur]
+            check(lib().rwkv_mm8_stream_run(dev.data_ptr(), host.data_ptr(), st.wstream.data_ptr(), st.sync.data_ptr(),
+                                            st.trace.data_ptr() if st.trace is not None else None,
+                                            torch.cuda.current_stream(self.device).cuda_stream), "mm8_stream_run")
+        elif self._use_chain:
             if self._chain[cur] is None:
                 self._build_chain(cur)
             table, n, n_ctas = self._chain[cur]

@@ -286,6 +286,50 @@ int rwkv_mm8_chain_run(const void* table_device, int n_launches, int n_ctas, voi
 int rwkv_mm8_chain_take_error(void* workspace, void* stream, int* error_out);
 
 /* ---------------------------------------------------------------------------------------
+ * mm8 stream — one decode step (the same list of dependent mm8_one problems with fused prologues
+ * and epilogues that rwkv_mm8_one_batch takes launch by launch) as ONE persistent cooperative
+ * kernel, one CTA per SM, over a re-tiled copy of the codes.  Replaces the per-token loop of
+ * RWKV.forward over att_one / ffn_one (pkg/model.py:1477-1677) for T = 1; no counterpart in the
+ * reference.  fp16 only; every N a multiple of 8; x, ry, my and the prologue vectors 16-byte
+ * aligned; LayerNorm prologues up to 8192 features.
+ *
+ * Layout ("weight stream"): the output columns of every matrix are dealt to the CTAs in units of
+ * four, so a CTA owns whole dot products (no split-K, no reduction between CTAs).  The bytes a CTA
+ * needs for the whole step are one contiguous region of the stream, in the order its threads
+ * consume them: 8-byte cells of 2 rows x 4 columns, row-interleaved for dp2a.  A producer warp
+ * moves the region through a ring of 16 KB shared-memory slots with bulk asynchronous copies and
+ * runs ahead of the arithmetic across matrix and phase boundaries.  Between phases the CTAs meet
+ * at a grid barrier (every wait is bounded: after 2 s it sets the error word and carries on).
+ * Arithmetic: x * ry as 30-bit fixed point, exact 64-bit integer sums (see csrc/mm8_stream.cu).
+ *
+ *   rwkv_mm8_stream_ctas()          CTAs of the grid on the current device (its SM count).
+ *   rwkv_mm8_stream_weight_bytes()  size of the weight stream for `problems` (all phases' problems
+ *                                   back to back; only w, w_stride, N, M are read).
+ *   rwkv_mm8_stream_pack()          re-tiles the codes into `wstream` (device, 16-byte aligned).
+ *   rwkv_mm8_stream_table_bytes()   size of the phase table.
+ *   rwkv_mm8_stream_plan()          HOST-side: writes the table for the same problems, counts[p] =
+ *                                   problems of phase p (1..4), into `table_host`.  Copy it to the
+ *                                   device; keep the host copy for rwkv_mm8_stream_run.
+ *                                   RWKV_ERR_UNSUPPORTED when a problem does not meet the limits.
+ *   rwkv_mm8_stream_run()           enqueues one step.  sync_words: two device words (barrier
+ *                                   counter, error); the call clears the counter in stream order.
+ *                                   trace: NULL, or n_phases x 2 x 4 uint64 (device) receiving
+ *                                   %globaltimer stamps of CTAs 0 and 1 per phase: barrier
+ *                                   arrival, barrier passed, prologue done, matrices done.
+ *   rwkv_mm8_stream_take_error()    synchronises `stream`, returns and clears the error word.
+ * ------------------------------------------------------------------------------------- */
+int rwkv_mm8_stream_ctas(void);
+size_t rwkv_mm8_stream_weight_bytes(const rwkv_mm8_problem* problems, int n_problems, int n_ctas);
+int rwkv_mm8_stream_pack(const rwkv_mm8_problem* problems, int n_problems, int n_ctas, void* wstream,
+                         size_t wstream_bytes, void* stream);
+size_t rwkv_mm8_stream_table_bytes(int n_phases);
+int rwkv_mm8_stream_plan(const rwkv_mm8_problem* problems, const int32_t* counts, int n_phases, int dtype,
+                         int n_ctas, void* table_host, size_t table_bytes);
+int rwkv_mm8_stream_run(const void* table_device, const void* table_host, const void* wstream,
+                        uint32_t* sync_words, uint64_t* trace, void* stream);
+int rwkv_mm8_stream_take_error(uint32_t* sync_words, void* stream, int* error_out);
+
+/* ---------------------------------------------------------------------------------------
  * mm8_seq — replaces cuda_mm8_seq<F> (pkg/cuda/operators.cu:102-154) behind
  * torch.ops.rwkv.mm8_seq (pkg/cuda/wrapper.cpp:50-83).
  *

@@ -77,7 +77,9 @@ def test_mm8_seq_at_sweep_shapes(packed, T, N, M):
     q, mx, rx, my, ry = cpu
     ref = orc.mm8_kernel(x, q[:, cols], mx[cols], rx[cols], my, ry)
     got = y[:, cols.cuda()].float().cpu()
-    assert ((got - ref).abs() <= ref.abs() * 2 ** -10 + 1e-4).all(), (got - ref).abs().max().item()
+    # one fp16 rounding of an fp32-accumulated sum over up to 20480 terms: one fp16 ulp
+    assert ((got - ref).abs() <= ref.abs() * 2 ** -9 + 2e-4).all(), (got - ref).abs().max().item()
+    assert (got.half() != ref.half()).float().mean().item() < 0.08
     assert torch.isfinite(y).all()
 
 

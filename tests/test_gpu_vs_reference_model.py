@@ -35,9 +35,9 @@ TOL = 2e-2
 # name: (version, shape name, checkpoint seed, prompt tokens, greedy steps, measure noise floor)
 CONFIGS = {
     "config0_v4_169m": (4, "v4-169m", 1000, 64, 128, True),
-    "config2_v4_7b": (4, "v4-7b", 1002, 1024, 256, False),
-    "config3_v6_7b": (6, "v6-7b", 1003, 2048, 512, False),
-    "config4_v4_14b": (4, "v4-14b", 1004, 256, 512, False),
+    "config2_v4_7b": (4, "v4-7b", 1002, 1024, 256, True),
+    "config3_v6_7b": (6, "v6-7b", 1003, 2048, 512, True),
+    "config4_v4_14b": (4, "v4-14b", 1004, 256, 512, True),
 }
 
 
@@ -127,10 +127,16 @@ def test_logits_and_greedy_tokens_match_reference_cuda_path(name, tmp_path):
               "reference": {"decode_tok_s": float(ref["decode_tok_s"]), "prefill_ms": float(ref["prefill_ms"]),
                             "noise_max": float(ref["noise_max"]) if "noise_max" in ref else None},
               "product": {"prefill_ms": prefill_ms}}
+    # every decode path of the runtime: the persistent weight-stream kernel (RWKV-4 default), a launch per
+    # matmul with 16-bit fixed-point activations, and the same with fp32 arithmetic
+    paths = [("launch", False, 0), ("launch_fp32", False, 8)]
+    if version == 4:
+        paths.insert(0, ("stream", True, 0))
     try:
-        for label, variant in (("default", 0), ("fp32", 8)):
+        for label, use_stream, variant in paths:
             _lib.lib().rwkv_mm8_one_set_variant(variant)
-            model._graphs = [None, None]            # captured graphs hold the kernels of the other arithmetic
+            model._use_stream = use_stream and version == 4
+            model._graphs = [None, None]            # captured graphs hold the kernels of the other path
             st = copy.deepcopy(snapshot)
             worst, mismatch, forgiven, min_margin, rate = _decode(model, st, tokens, ref["logits_steps"])
             report["product"][label] = {"max_abs": worst, "argmax_mismatch_steps": mismatch, "forgiven_steps": forgiven,
@@ -144,7 +150,7 @@ def test_logits_and_greedy_tokens_match_reference_cuda_path(name, tmp_path):
             json.dump(report, f, indent=1)
     print(json.dumps(report))
     assert err_p <= TOL and first_ok, report
-    for label in ("default", "fp32"):
+    for label, _, _ in paths:
         r = report["product"][label]
         assert r["max_abs"] <= TOL, report
         assert r["argmax_mismatch_steps"] == r["forgiven_steps"], report
