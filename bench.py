@@ -152,6 +152,25 @@ def cpu_arm(steps, warmup, budget_s=100.0):
 
 
 # ------------------------------------------------------------------------------------------
+def reference_cpu_arm(mode, steps, warmup, shape=WORKLOAD, timeout=900):
+    """The reference's own 'cpu fp32i8' runtime in a child process (oracle/ref_cpu_bench.py); None when the
+    staged runtime is missing or the child fails."""
+    if not os.path.exists(os.path.join(ROOT, "oracle", "_ref", "pkg", "rwkv", "model.py")):
+        return None
+    env = dict(os.environ)
+    env.pop("OMP_NUM_THREADS", None)            # torchrun exports 1; the CPU arm uses all host threads
+    cmd = [sys.executable, "-m", "oracle.ref_cpu_bench", mode, "--steps", str(steps), "--warmup", str(warmup), "--shape", shape]
+    try:
+        r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
+        if r.returncode != 0:
+            return None
+        out = json.loads(r.stdout.strip().splitlines()[-1])
+        out["host_cpus"] = os.cpu_count()
+        return out
+    except Exception:
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -163,10 +182,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--shard", action="store_true",
                     help="second multi-GPU mode: ONE model, every packed matrix split by output columns over the "
-                         "ranks with an NCCL all-gather after each matmul (strong scaling; use with --shape v4-14b)")
+                         "ranks with an exchange after each matmul (strong scaling; use with --shape v4-14b)")
     ap.add_argument("--sweep", action="store_true",
                     help="operator sweep instead of the model bench: mm8_one (T=1) and mm8_seq (T=16,128,1024) on the "
                          "four (N, M) shapes of the task's operator config; one JSON line with a 'sweep' list")
+    ap.add_argument("--sequences", type=int, default=0,
+                    help="S independent sequences dealt to the ranks (s mod N), each with its own prefill of --prompt "
+                         "tokens and --steps greedy tokens; value = decoded tokens of all sequences / time")
     ap.add_argument("--layers", type=int, default=0,
                     help="profiling aid: build only this many layers of the shape (the line is then not a bench result)")
     a = ap.parse_args()
@@ -174,15 +196,18 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    metric = METRIC if a.shape == WORKLOAD else f"fp16i8_decode_tokens_per_s_rwkv{a.shape.replace('-', '_')}_shape"
 
     if a.impl == "reference":
         if rank != 0:
             return
-        cb = cpu_arm(a.steps, a.warmup)
-        line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s", "n_gpus": a.gpus,
+        k = max(1, min(a.steps, 6))             # bounded: a step costs ~8 s of host time at the 7B width
+        cb = reference_cpu_arm("token7b", k, min(a.warmup, 1), a.shape) or cpu_arm(a.steps, a.warmup)
+        line = {"impl": "reference", "metric": metric, "value": cb["value"], "unit": "tokens/s", "n_gpus": a.gpus,
                 "steps": a.steps, "warmup": a.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": "rwkv4-7b-shape greedy decode, batch 1 (CPU sample of its mm8 matmuls)"},
+                "config": {"workload": f"rwkv{a.shape} shape 'cpu fp32i8' greedy decode, batch 1, on the host cores; "
+                                       f"bounded sample: {cb['sample']}"},
                 "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line), flush=True)
@@ -190,7 +215,7 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from chatrwkv_b200 import synth
+    from chatrwkv_b200 import shard, synth
     from chatrwkv_b200.model import RWKV
 
     if a.sweep:
@@ -212,7 +237,6 @@ def main():
                  shard_rank=rank if sharded else 0, shard_world=world if sharded else 1)
     del ck
     torch.cuda.empty_cache()
-    prompt = synth.make_tokens(a.prompt, V, 2000 + (0 if sharded else rank))
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -220,9 +244,68 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    weight_gb = sum(t.numel() for t in model.w.values() if torch.is_tensor(t) and t.dtype == torch.uint8) / 1e9
+    n_mm = L * (7 if version == 4 else 8) + 1
+
+    def decode_loop(tok, state, n):
+        for _ in range(n):
+            logits, state = model.forward(tok, state)
+            tok = torch.argmax(logits).reshape(1)
+        return tok, state
+
+    if a.sequences > 0:
+        # ---- S independent sequences over the ranks, each prefill + greedy decode, one after the other ----
+        mine = shard.assign_sequences(a.sequences, world, rank)
+        model.forward(synth.make_tokens(min(a.prompt, 192), V, 1), None)            # untimed: sizes workspaces
+        _, st = model.forward(synth.make_tokens(8, V, 1), None)
+        decode_loop(torch.zeros(1, dtype=torch.int64, device=dev), st, a.warmup)     # untimed: captures the decode graphs
+        sampler = ClockSampler(local_rank)
+        barrier()
+        sampler.start()
+        ev0.record()
+        pre_ms = 0.0
+        for sq in mine:
+            prompt = synth.make_tokens(a.prompt, V, 2000 + sq)
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            p0.record()
+            logits, state = model.forward(prompt, None)
+            p1.record()
+            decode_loop(torch.argmax(logits).reshape(1), state, a.steps)
+            torch.cuda.synchronize(dev)
+            pre_ms += p0.elapsed_time(p1)
+        ev1.record()
+        barrier()
+        clocks = sampler.stop()
+        total_ms = ev0.elapsed_time(ev1)
+        times = torch.tensor([total_ms, pre_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        total_ms, pre_ms = times.tolist()
+        if rank == 0:
+            dec_tokens = a.sequences * a.steps
+            line = {"metric": metric.replace("decode_tokens", "sequences_decode_tokens"), "unit": "tokens/s", "n_gpus": world,
+                    "value": dec_tokens / ((total_ms - pre_ms) / 1e3), "steps": a.steps, "warmup": a.warmup,
+                    "ms_per_step": (total_ms - pre_ms) / (a.steps * max(1, len(mine))), "higher_is_better": True,
+                    "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                    "config": {"workload": f"rwkv{a.shape} shape 'cuda fp16i8': {a.sequences} independent sequences dealt to "
+                                           f"{world} GPU(s) (s mod N), each a {a.prompt}-token prefill then {a.steps} greedy "
+                                           f"tokens, one sequence at a time per GPU",
+                               "parallelism": "independent sequences, no collective",
+                               "l2": f"inputs larger than L2 ({weight_gb:.2f} GB of packed weights streamed per step)"},
+                    "whole_job": {"seconds": total_ms / 1e3, "prefill_seconds_max_rank": pre_ms / 1e3,
+                                  "prefill_tokens": a.sequences * a.prompt, "decoded_tokens": dec_tokens,
+                                  "all_tokens_per_s": a.sequences * (a.prompt + a.steps) / (total_ms / 1e3)},
+                    "gpu_launches": None, "clocks": clocks, "graph": bool(model._use_graph),
+                    "decode_path": model.decode_path()}
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    prompt = synth.make_tokens(a.prompt, V, 2000 + (0 if sharded else rank))
     # ---- prefill (reported, not the headline) ------------------------------------------
     model.forward(prompt[:192], None)            # untimed: sizes workspaces, loads kernels
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(dev)
     ev0.record()
     logits, state = model.forward(prompt, None)
@@ -232,17 +315,13 @@ def main():
 
     # ---- device-resident greedy decode --------------------------------------------------
     tok = torch.argmax(logits).reshape(1)
-    for _ in range(a.warmup):
-        logits, state = model.forward(tok, state)
-        tok = torch.argmax(logits).reshape(1)
+    tok, state = decode_loop(tok, state, a.warmup)
     sampler = ClockSampler(local_rank)
     barrier()
     sampler.start()
     torch.cuda.cudart().cudaProfilerStart()      # lets `ncu --profile-from-start off` see the timed region only
     ev0.record()
-    for _ in range(a.steps):
-        logits, state = model.forward(tok, state)
-        tok = torch.argmax(logits).reshape(1)
+    tok, state = decode_loop(tok, state, a.steps)
     ev1.record()
     barrier()
     dev_ms = ev0.elapsed_time(ev1)
@@ -272,32 +351,57 @@ def main():
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms, prefill_ms = times.tolist()
+    path_default = model.decode_path()
+    launches_default = model.launches_per_token()
 
-    # ---- roofline of the dominant kernel (rank 0): each GEMV launch of a token, event-timed
+    # ---- the other decode paths of the runtime, 64 steps each (rank 0, single-GPU mode only) ----
+    other = {}
+    if rank == 0 and not sharded and version == 4 and path_default == "stream" and a.layers == 0:
+        from chatrwkv_b200 import _lib
+        n_alt = min(64, a.steps)
+        for label, variant in (("launch_per_matmul_fixed16", 0), ("launch_per_matmul_fp32", 8)):
+            _lib.lib().rwkv_mm8_one_set_variant(variant)
+            model.set_decode_path("launch")
+            tok, state = decode_loop(tok, state, 4)
+            torch.cuda.synchronize(dev)
+            ev0.record()
+            tok, state = decode_loop(tok, state, n_alt)
+            ev1.record()
+            torch.cuda.synchronize(dev)
+            other[label] = {"tokens_per_s": n_alt / (ev0.elapsed_time(ev1) / 1e3), "steps": n_alt}
+        _lib.lib().rwkv_mm8_one_set_variant(0)
+        model.set_decode_path("stream")
+        tok, state = decode_loop(tok, state, 2)
+
+    # ---- roofline of the dominant kernel (rank 0): one decode step of direct launches, event-timed
     roof = None
     if rank == 0:
         roof = None if sharded else gemv_roofline(model, dev)
     cb = None
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
-        cb = cpu_arm(steps=6, warmup=1, budget_s=25.0)
+        cb = reference_cpu_arm("token7b", 2, 1, a.shape) or cpu_arm(steps=6, warmup=1, budget_s=25.0)
+        c0 = reference_cpu_arm("config0", 16, 2)
+        if c0 is not None:
+            cb["config0"] = c0
 
     if rank == 0:
-        n_mm = L * (7 if version == 4 else 8)
-        launches_per_token = 2 if model._use_chain else L * (4 if version == 4 else 6) + 1
         line = {
-            "metric": METRIC, "value": (1 if sharded else world) * a.steps / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+            "metric": metric, "value": (1 if sharded else world) * a.steps / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": dev_ms / a.steps, "higher_is_better": True,
             "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"parallelism": ("one model column-sharded over %d GPUs, all-gather after each matmul" % world) if sharded
+            "config": {"parallelism": ("one model column-sharded over %d GPUs, exchange after each matmul" % world) if sharded
                                       else "independent streams, one per GPU, no collective",
                        "workload": f"rwkv{a.shape} shape (L={L}, D={D}, ffn={Fn}, vocab={V}) 'cuda fp16i8', batch 1 per "
                                    f"GPU: {a.prompt}-token prefill then greedy decode; one independent stream per GPU",
-                       "l2": "inputs larger than L2 (%.2f GB of packed weights streamed per step)" % (
-                           sum(t.numel() for t in model.w.values() if torch.is_tensor(t) and t.dtype == torch.uint8) / 1e9),
-                       "mm8_matmuls_per_token": n_mm + 1},
+                       "l2": f"inputs larger than L2 ({weight_gb:.2f} GB of packed weights streamed per step on this rank)",
+                       "mm8_matmuls_per_token": n_mm},
             "e2e": {"value": (1 if sharded else world) * a.steps / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 8,
                     "d2h_bytes_per_step": V * 4},
-            "gpu_launches": launches_per_token * a.steps * 2,
+            "gpu_launches": launches_default * a.steps * 2,
+            "decode_path": path_default, "graph": bool(model._use_graph),
+            "arithmetic": "x*ry as 30-bit fixed point, exact 64-bit integer sums (fp32-accurate)" if path_default == "stream"
+                          else "x*ry as 16-bit fixed point per CTA slice, exact 32-bit integer sums",
+            "other_decode_paths": other,
             "prefill": {"tokens": a.prompt, "ms": prefill_ms, "tokens_per_s": a.prompt / (prefill_ms / 1e3)},
             "clocks": clocks, "roofline": roof, "cpu_baseline": cb,
         }
@@ -403,15 +507,13 @@ def gemv_roofline(model, dev, reps=30):
     import torch
     peak, how = measured_peaks()
     v4 = model.version == 4
-    tot_b, n_mm8 = 0, 0
+    tot_b = 0
     for name, t in model.w.items():         # every packed matrix is read once per token
         if torch.is_tensor(t) and t.dtype == torch.uint8:
             N, M = t.shape
             tot_b += N * M + 6 * N + 4 * M + (4 if name == "head.weight" else 2) * M
-            n_mm8 += 1
-    launches = model._launches_v4(model._cur) if v4 else [None] * (model.args.n_layer * 4 + 1)
     step_fn = model._step_one_v4 if v4 else model._step_one_v56
-    chain = bool(model._use_chain)
+    path = model.decode_path()
     for _ in range(3):
         step_fn(model._cur)                     # reads the current state set, writes the other one
     torch.cuda.synchronize(dev)
@@ -422,20 +524,24 @@ def gemv_roofline(model, dev, reps=30):
     e1.record()
     torch.cuda.synchronize(dev)
     ms = e0.elapsed_time(e1) / reps
-    n_launch = 2 if chain else len(launches)
+    n_launch = 1 if path == "stream" else model.launches_per_token()
     achieved = tot_b / (ms / 1e3) / 1e9
-    traffic = None
+    traffic, source = None, None
     try:
         with open(os.path.join(ROOT, "profiles", "mm8_traffic.json")) as f:
             t = json.load(f)
-        traffic = t["dram_bytes_per_algorithmic_byte"] * tot_b / n_launch
+        key = "stream" if path == "stream" else "launch"
+        ratio = t[key]["dram_bytes_per_algorithmic_byte"] if key in t else t["dram_bytes_per_algorithmic_byte"]
+        traffic = ratio * tot_b / n_launch
+        source = "scaled: DRAM bytes per algorithmic byte from an ncu capture of a 2-layer model of the same shape"
     except Exception:
         pass
-    return {"bound": "hbm", "kernel": "mm8_chain_kernel" if chain else "mm8_cluster_kernel", "achieved": achieved,
+    kernel = {"stream": "mm8_stream_kernel", "chain": "mm8_chain_kernel"}.get(path, "mm8_cluster_kernel")
+    return {"bound": "hbm", "kernel": kernel, "achieved": achieved,
             "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": how, "traffic": traffic,
-            "launches_per_step": n_launch, "avg_launch_us": ms / n_launch * 1e3,
+            "traffic_source": source, "launches_per_step": n_launch, "avg_launch_us": ms / n_launch * 1e3,
             "algorithmic_bytes_per_launch": tot_b / n_launch, "frac_of_8000": achieved / 8000.0,
-            "chain_error": model.chain_error() if chain else 0}
+            "wait_error": model.stream_error() if path == "stream" else 0}
 
 
 if __name__ == "__main__":

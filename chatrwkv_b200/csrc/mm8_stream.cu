@@ -8,22 +8,26 @@
 // token and the weights are laid out for it:
 //
 //   * Every matrix is split by OUTPUT columns over the CTAs (units of 4 columns), so a CTA owns
-//     whole dot products: no split-K, no cross-CTA reduction, results are exact integer sums.
+//     whole dot products: no split-K between CTAs, no cross-CTA reduction, exact integer sums.
 //   * The bytes a CTA needs, for all matrices of the token in the order it needs them, are ONE
 //     contiguous region of the stream buffer, already in the order its threads consume them
-//     (8-byte cells = 2 rows x 4 columns with the rows interleaved for dp2a).  A producer warp
-//     copies it through a ring of 16 KB shared-memory slots with cp.async.bulk + mbarrier,
-//     running ahead of the math across matrix and phase boundaries: while the CTAs exchange a
-//     result vector, HBM keeps filling the rings (up to ~150 KB per SM).
+//     (operand fragments of the 8-bit integer tensor-core instruction).  A producer warp copies it
+//     through a ring of 16 KB shared-memory slots with cp.async.bulk + mbarrier, running ahead of
+//     the math across matrix and phase boundaries: while the CTAs exchange a result vector, HBM
+//     keeps filling the rings (~144 KB per SM).
 //   * Between dependent matrices ("phases") the CTAs meet at a grid barrier (one atomic counter,
 //     bounded spin), read the full input vector from L2 and redo the cheap pointwise prologue
 //     (LayerNorm + token-shift mix, RWKV-4 WKV step) redundantly.
 //
-// Arithmetic: x' = x * ry is quantised per vector to 30-bit fixed point (q = hi * 2^15 + lo),
-// both halves go through dp2a against the raw codes, sums are kept in 64-bit integers: the
-// streamed part of mm8_one (operators.cu:224-230) is computed exactly for the quantised x', whose
+// Arithmetic: x' = x * ry is quantised per vector to a 31-bit integer q = sum_n d_n 256^n with four
+// signed base-256 digits.  mma.sync.m16n8k32.s8.u8 multiplies a 16 x 32 tile whose rows 0..3 are the
+// digit planes of 32 consecutive inputs with a 32 x 8 tile of raw codes: D[n][c] = sum_k d_n[k]
+// w[k][c] in exact 32-bit integers (|d w| <= 32640, so 65536 inputs cannot overflow).  The streamed
+// part of mm8_one (operators.cu:224-230) is therefore computed exactly for the quantised x', whose
 // relative error (2^-24 of fp32 for large entries, 2^-30 of the largest entry for small ones) is
-// that of an fp32 product.  Results do not depend on any summation order.
+// that of an fp32 product; no result depends on a summation order.  The tensor pipe is used because
+// it takes one instruction per 256 code bytes where dp2a takes eight: the kernel is HBM-bound and
+// the issue slots were what kept the math from catching up after a phase change.
 #include "common.cuh"
 
 namespace {
@@ -31,14 +35,13 @@ namespace {
 constexpr int kConsumers = 512;
 constexpr int kConsWarps = kConsumers / 32;
 constexpr int kStreamThreads = kConsumers + 32;          // + the producer warp
-constexpr int kIter = 4;                                 // cells per thread and stage
-constexpr int kSlotBytes = kIter * kConsumers * 8;       // 16 KB
-constexpr int kRedBytes = 128 * 4 * 8;                   // [<= 128 subgroups][4 columns] 64-bit sums
+constexpr int kSlotBytes = 16384;
+constexpr int kMaxOct = 12;                              // column octets a warp accumulates (24 registers)
+constexpr int kRedBytes = kConsWarps * kMaxOct * 8 * 8;  // [warp][octet][column] 64-bit partial sums
 constexpr int kMaxSlots = 12;
 constexpr int kMaxCtas = 160;
 constexpr int kMaxPhaseProblems = 4;
-constexpr int kFlushStages = 16;                         // 32-bit partial sums are widened every 16 stages
-constexpr float kQMax = 1.0e9f;                          // |q| <= 1e9 < 2^30: hi fits 16 signed bits with margin
+constexpr float kQMax = 1.0e9f;                          // |q| <= 1e9 < 2^30
 constexpr unsigned long long kWaitNs = 2000000000ull;    // every wait gives up after 2 s
 
 struct SProblem {
@@ -74,17 +77,22 @@ struct STable {
     // SPhase phases[n_phases] follow
 };
 
-// How one matrix is laid out for one CTA.
+// How one matrix is laid out for one CTA.  Its columns are 4 * Q consecutive ones, grouped in
+// octets (the N dimension of the instruction; the last octet holds 4 columns when Q is odd); its
+// rows in k-blocks of 32 (the K dimension).  One k-block of all the CTA's columns is 128 * Q
+// contiguous bytes: per octet 32 (or 16) cells of 8 bytes, cell `lane` = the B fragment of that lane.
+// The 16 warps are wo groups along the columns (<= kMaxOct octets each) times wk = 16 / wo along K:
+// warp (og, ks) takes the k-blocks kb with kb % wk == ks.
 struct Geom {
-    int Q;              // column quads owned by this CTA (4 columns each)
+    int Q;              // column quads owned by this CTA
     int u0;             // first quad
-    int SG;             // lanes that share a quad inside a warp (4, 8, 16 or 32)
-    int PPI;            // row pairs per iteration (= SG * subgroups per quad)
-    int TA;             // active threads = Q * PPI
-    int kp;             // row pairs, rounded up to a multiple of SG
-    int cells;          // kp * Q
+    int n_oct;          // octets, the last one half when Q is odd
+    int wo, opw, wk;
+    int n_kb;           // ceil(N / 32)
+    int kb_bytes;       // 128 * Q
+    int kbs;            // k-blocks per stage
     int n_stages;
-    long long bytes;    // cells * 8
+    long long bytes;
 };
 
 __host__ __device__ inline Geom seg_geom(int N, int M, int cta, int G) {
@@ -93,22 +101,18 @@ __host__ __device__ inline Geom seg_geom(int N, int M, int cta, int G) {
     const int base = U / G, rem = U % G;
     g.Q = base + (cta < rem ? 1 : 0);
     g.u0 = cta * base + (cta < rem ? cta : rem);
-    g.SG = 4; g.PPI = 0; g.TA = 0; g.kp = 0; g.cells = 0; g.n_stages = 0; g.bytes = 0;
-    if (g.Q == 0 || g.Q > kConsumers / 4) return g;       // more than 128 quads per CTA: not planned (see plan)
-    int best_ta = 0;
-    for (int sg = 32; sg >= 4; sg >>= 1) {
-        const int nsub = (kConsumers / sg) / g.Q;
-        const int ta = nsub * g.Q * sg;
-        if (ta > best_ta) { best_ta = ta; g.SG = sg; }
-    }
-    g.TA = best_ta;
-    g.PPI = best_ta / g.Q;
-    const int kp = (N + 1) >> 1;
-    g.kp = (kp + g.SG - 1) / g.SG * g.SG;
-    g.cells = g.kp * g.Q;
-    const int per_stage = kIter * g.TA;
-    g.n_stages = (g.cells + per_stage - 1) / per_stage;
-    g.bytes = (long long)g.cells * 8;
+    g.n_oct = 0; g.wo = 1; g.opw = 0; g.wk = kConsWarps; g.n_kb = 0; g.kb_bytes = 0; g.kbs = 1; g.n_stages = 0; g.bytes = 0;
+    if (g.Q == 0 || g.Q > kSlotBytes / 128) return g;     // more than 128 quads per CTA: not planned (see plan)
+    g.n_oct = (g.Q + 1) >> 1;
+    while ((g.n_oct + g.wo - 1) / g.wo > kMaxOct) g.wo <<= 1;
+    g.opw = (g.n_oct + g.wo - 1) / g.wo;
+    g.wk = kConsWarps / g.wo;
+    g.n_kb = (N + 31) >> 5;
+    g.kb_bytes = 128 * g.Q;
+    g.kbs = kSlotBytes / g.kb_bytes;
+    if (g.kbs >= g.wk) g.kbs = g.kbs / g.wk * g.wk;       // every K group of warps gets the same share of a stage
+    g.n_stages = (g.n_kb + g.kbs - 1) / g.kbs;
+    g.bytes = (long long)g.n_kb * g.kb_bytes;
     return g;
 }
 
@@ -141,20 +145,14 @@ __device__ __forceinline__ unsigned long long gtime() {
     return t;
 }
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
-__device__ __forceinline__ int dp2a_lo(int a, uint32_t b, int c) {
-    int d;
-    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ int dp2a_hi(int a, uint32_t b, int c) {
-    int d;
-    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ int warp_sum_i(int v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
+
+// D[16 x 8] (s32) += A[16 x 32] (s8, rows 0..7 in a0 / a2, rows 8..15 zero) * B[32 x 8] (u8).  Only rows
+// 0..7 are kept (d0, d1); the other half of the tile multiplies zeros.
+__device__ __forceinline__ void imma_16832(int& d0, int& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    int z0, z1;
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %10, %10};"
+                 : "+r"(d0), "+r"(d1), "=r"(z0), "=r"(z1)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "r"(0));
 }
 
 // Bounded wait on an mbarrier phase.  After the first give-up in this CTA (*err set) later waits
@@ -176,32 +174,31 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
 struct SharedCtl {
     unsigned long long full[kMaxSlots];
     unsigned long long empty[kMaxSlots];
-    float wsum[kMaxPhaseProblems][kConsWarps][3];     // per warp: sum x, sum x', sum x*my
-    int wsumi[kMaxPhaseProblems][kConsWarps][2];      // per warp: sum hi, sum lo
+    long long wsumq[kMaxPhaseProblems][kConsWarps];   // per warp: sum of the quantised activations
+    float wsum[kMaxPhaseProblems][kConsWarps][2];     // per warp: sum x, sum x*my
     float inv_scale[kMaxPhaseProblems];
-    float red16[kConsWarps];
+    float red[kConsWarps][4];
     int err;
 };
 
-__device__ __forceinline__ float cons_block_sum(float v, float* sh, int warp, int lane) {
-    v = warp_sum(v);
-    cons_sync();
-    if (lane == 0) sh[warp] = v;
-    cons_sync();
-    float t = 0.f;
+// Sums (SUM) or maxima of up to four values over the 512 consumer threads.
+template <bool SUM>
+__device__ __forceinline__ void cons_block_reduce4(float (&v)[4], float (*sh)[4], int warp, int lane) {
 #pragma unroll
-    for (int i = 0; i < kConsWarps; ++i) t += sh[i];
-    return t;
-}
-__device__ __forceinline__ float cons_block_max(float v, float* sh, int warp, int lane) {
-    v = warp_max(v);
+    for (int i = 0; i < 4; ++i) v[i] = SUM ? warp_sum(v[i]) : warp_max(v[i]);
     cons_sync();
-    if (lane == 0) sh[warp] = v;
-    cons_sync();
-    float t = 0.f;
+    if (lane == 0) {
 #pragma unroll
-    for (int i = 0; i < kConsWarps; ++i) t = fmaxf(t, sh[i]);
-    return t;
+        for (int i = 0; i < 4; ++i) sh[warp][i] = v[i];
+    }
+    cons_sync();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float t = SUM ? 0.f : sh[0][i];
+#pragma unroll
+        for (int w = SUM ? 0 : 1; w < kConsWarps; ++w) t = SUM ? t + sh[w][i] : fmaxf(t, sh[w][i]);
+        v[i] = t;
+    }
 }
 
 __device__ __forceinline__ void h8_to_f(const uint4& v, float (&f)[8]) {
@@ -222,8 +219,8 @@ __device__ __forceinline__ uint4 ldg16(const void* base, int j8) { return __ldg(
 // The W (4 or 8) activations starting at element j are multiplied with ry, written as fp32 x' and
 // added to the running sums.  A NaN anywhere makes the maximum infinite (a NaN does not survive fmaxf).
 template <int W>
-__device__ __forceinline__ void emit(const float (&xv)[W], const SProblem& P, int j, float* xs, float& sx, float& sxr,
-                                     float& sxmy, float& xmax) {
+__device__ __forceinline__ void emit(const float (&xv)[W], const SProblem& P, int j, float* xs, float& sx, float& sxmy,
+                                     float& xmax) {
     float ry[W], my[W];
     if (W == 8) {
         float a[8], b[8];
@@ -247,12 +244,22 @@ __device__ __forceinline__ void emit(const float (&xv)[W], const SProblem& P, in
     for (int e = 0; e < W; ++e) {
         xp[e] = xv[e] * ry[e];
         sx += xv[e];
-        sxr += xp[e];
         sxmy = fmaf(xv[e], my[e], sxmy);
         xmax = (xp[e] == xp[e]) ? fmaxf(xmax, fabsf(xp[e])) : __int_as_float(0x7f800000);
     }
 #pragma unroll
     for (int e = 0; e < W; e += 4) *reinterpret_cast<float4*>(xs + j + e) = make_float4(xp[e], xp[e + 1], xp[e + 2], xp[e + 3]);
+}
+
+// Ask L2 for this CTA's share of the lines of a vector that the NEXT phase reads right after the grid
+// barrier (model constants and last token's state: the 7 GB of weights streamed since their last use
+// have pushed them out of L2).  evict_last keeps them there across tokens.
+__device__ __forceinline__ void l2_fetch(const void* ptr, int bytes, int cta, int G, int tid) {
+    if (ptr == nullptr) return;
+    const char* p = static_cast<const char*>(ptr);
+    const int lines = (bytes + 127) >> 7;
+    for (int l = cta + tid * G; l < lines; l += G * kConsumers)
+        asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(p + (size_t)l * 128));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -294,7 +301,7 @@ mm8_stream_kernel(const STable* __restrict__ table, const uint8_t* __restrict__ 
                 const int count = phases[ph].count;
                 for (int z = 0; z < count; ++z) {
                     const Geom g = seg_geom(phases[ph].p[z].N, phases[ph].p[z].M, cta, G);
-                    const long long stage_bytes = (long long)kIter * g.TA * 8;
+                    const long long stage_bytes = (long long)g.kbs * g.kb_bytes;
                     for (int s = 0; s < g.n_stages; ++s) {
                         const long long left = g.bytes - s * stage_bytes;
                         const uint32_t bytes = (uint32_t)(left < stage_bytes ? left : stage_bytes);
@@ -311,6 +318,7 @@ mm8_stream_kernel(const STable* __restrict__ table, const uint8_t* __restrict__ 
     }
 
     // ================= consumers =================
+    const int gid = lane >> 2, tig = lane & 3;      // fragment coordinates of the lane
     int slot = 0;
     uint32_t parity = 0;
     for (int ph = 0; ph < n_phases; ++ph) {
@@ -320,36 +328,36 @@ mm8_stream_kernel(const STable* __restrict__ table, const uint8_t* __restrict__ 
         // ---- prologue: every CTA builds the full quantised activation vector of each problem ----
         uint4 lnx[2];
         float mean = 0.f, rstd = 0.f;
+        float xmax[4] = {0.f, 0.f, 0.f, 0.f};
         lnx[0] = lnx[1] = make_uint4(0, 0, 0, 0);
-        for (int z = 0; z < count; ++z) {
+#pragma unroll
+        for (int z = 0; z < kMaxPhaseProblems; ++z) {
+            if (z >= count) break;
             const SProblem& P = PH.p[z];
             const int N = P.N;
             float* xs = reinterpret_cast<float*>(xq_base + P.xq_off);
-            float sx = 0.f, sxr = 0.f, sxmy = 0.f, xmax = 0.f;
+            float sx = 0.f, sxmy = 0.f, xm = 0.f;
             if (P.prologue == RWKV_PRO_LN_MIX) {
-                if (!P.share_ln) {          // statistics of the residual stream (N <= 8192: two 16-byte loads per thread)
-                    float s = 0.f;
+                if (!P.share_ln) {
+                    // LayerNorm statistics in one pass, shifted by the first element so that a large mean does
+                    // not cancel (N <= 8192: two 16-byte loads per thread)
+                    const float x0 = __half2float(__ldcg(static_cast<const __half*>(P.x)));
+                    float st[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         const int j8 = (tid + i * kConsumers) * 8;
-                        lnx[i] = j8 < N ? ldcg16(P.x, j8) : make_uint4(0, 0, 0, 0);
-                        float f[8];
-                        h8_to_f(lnx[i], f);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) s += f[e];
-                    }
-                    mean = cons_block_sum(s, ctl->red16, warp, lane) / float(N);
-                    float q = 0.f;
-#pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        if ((tid + i * kConsumers) * 8 < N) {
+                        if (j8 < N) {
+                            lnx[i] = ldcg16(P.x, j8);
                             float f[8];
                             h8_to_f(lnx[i], f);
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) q = fmaf(f[e] - mean, f[e] - mean, q);
+                            for (int e = 0; e < 8; ++e) { const float d = f[e] - x0; st[0] += d; st[1] = fmaf(d, d, st[1]); }
                         }
                     }
-                    rstd = rsqrtf(cons_block_sum(q, ctl->red16, warp, lane) / float(N) + 1e-5f);
+                    cons_block_reduce4<true>(st, ctl->red, warp, lane);
+                    const float md = st[0] / float(N);
+                    mean = x0 + md;
+                    rstd = rsqrtf(fmaxf(st[1] / float(N) - md * md, 0.f) + 1e-5f);
                 }
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
@@ -372,7 +380,7 @@ mm8_stream_kernel(const STable* __restrict__ table, const uint8_t* __restrict__ 
                                 xv[e] = P.mode == 0 ? r16(r16(xv[e] * mv[e]) + r16(sv[e] * r16(1.0f - mv[e])))
                                                     : r16(xv[e] + r16(r16(sv[e] - xv[e]) * mv[e]));
                         }
-                        emit<8>(xv, P, j8, xs, sx, sxr, sxmy, xmax);
+                        emit<8>(xv, P, j8, xs, sx, sxmy, xm);
                     }
                 }
             } else if (P.prologue == RWKV_PRO_WKV4) {       // pkg/model.py:1041-1055, four channels per thread and pass
@@ -411,137 +419,173 @@ mm8_stream_kernel(const STable* __restrict__ table, const uint8_t* __restrict__ 
                         *reinterpret_cast<float4*>(P.g1 + j) = make_float4(nb[0], nb[1], nb[2], nb[3]);
                         *reinterpret_cast<float4*>(P.g2 + j) = make_float4(np[0], np[1], np[2], np[3]);
                     }
-                    emit<4>(xv, P, j, xs, sx, sxr, sxmy, xmax);
+                    emit<4>(xv, P, j, xs, sx, sxmy, xm);
                 }
             } else {
                 for (int j8 = tid * 8; j8 < N; j8 += kConsumers * 8) {
                     float xv[8];
                     h8_to_f(ldcg16(P.x, j8), xv);
-                    emit<8>(xv, P, j8, xs, sx, sxr, sxmy, xmax);
+                    emit<8>(xv, P, j8, xs, sx, sxmy, xm);
                 }
             }
-            sx = warp_sum(sx); sxr = warp_sum(sxr); sxmy = warp_sum(sxmy);
-            if (lane == 0) { ctl->wsum[z][warp][0] = sx; ctl->wsum[z][warp][1] = sxr; ctl->wsum[z][warp][2] = sxmy; }
-            const float m = cons_block_max(xmax, ctl->red16, warp, lane);     // also orders the x' stores before the reads below
+            sx = warp_sum(sx); sxmy = warp_sum(sxmy);
+            if (lane == 0) { ctl->wsum[z][warp][0] = sx; ctl->wsum[z][warp][1] = sxmy; }
+            xmax[z] = xm;
+        }
+        cons_block_reduce4<false>(xmax, ctl->red, warp, lane);       // also orders the x' stores before the reads below
+        // quantise in place.  The 16 fp32 x' of inputs [16 g, 16 g + 16) become 64 bytes of digits in the same
+        // place: plane n (the n-th signed base-256 digit) of those inputs at byte 16 n; two such groups are the
+        // k-block whose A fragments the lanes with gid < 4 read as words gid * 4 + tig (+ 16).
+#pragma unroll
+        for (int z = 0; z < kMaxPhaseProblems; ++z) {
+            if (z >= count) break;
+            const SProblem& P = PH.p[z];
+            const int N = P.N, npad = ((N + 31) >> 5) << 5;
+            float* xs = reinterpret_cast<float*>(xq_base + P.xq_off);
+            const float m = xmax[z];
             const bool finite = m < 3.0e38f;
             const float scale = (finite && m > 0.f) ? kQMax / m : 0.f;
             if (tid == 0) ctl->inv_scale[z] = !finite ? __int_as_float(0x7fc00000) : (m > 0.f ? m / kQMax : 0.f);
-            // quantise in place: pair p (rows 2p, 2p+1) becomes {hi(2p) | hi(2p+1) << 16, lo(2p) | lo(2p+1) << 16}
-            const int kp32 = (((N + 1) >> 1) + 31) & ~31;
-            int shi = 0, slo = 0;
-            for (int p = tid; p < kp32; p += kConsumers) {
-                const int j = 2 * p;
-                const float2 v = *reinterpret_cast<const float2*>(xs + j);
-                const int q0 = j < N ? __float2int_rn(v.x * scale) : 0;
-                const int q1 = j + 1 < N ? __float2int_rn(v.y * scale) : 0;
-                const int h0 = q0 >> 15, h1 = q1 >> 15, l0 = q0 & 0x7fff, l1 = q1 & 0x7fff;
-                shi += h0 + h1;
-                slo += l0 + l1;
-                *reinterpret_cast<uint2*>(xs + j) = make_uint2((uint32_t(h0) & 0xffffu) | (uint32_t(h1) << 16),
-                                                               uint32_t(l0) | (uint32_t(l1) << 16));
+            long long sq = 0;
+            for (int j0 = 0; j0 < npad; j0 += kConsumers * 4) {     // whole warps iterate together (npad % 32 == 0)
+                const int j = j0 + tid * 4;
+                uint32_t plane[4] = {0u, 0u, 0u, 0u};
+                if (j < N) {                                        // N % 8 == 0: a group of four is inside or outside
+                    const float4 v = *reinterpret_cast<const float4*>(xs + j);
+                    const float f[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        int q = __float2int_rn(f[e] * scale);
+                        sq += q;
+#pragma unroll
+                        for (int n = 0; n < 4; ++n) {
+                            const int d = (int)(signed char)(q & 0xff);
+                            plane[n] |= uint32_t(d & 0xff) << (8 * e);
+                            q = (q - d) >> 8;
+                        }
+                    }
+                }
+                __syncwarp();                                       // the group's floats are read before its digits land
+                if (j < npad) {
+                    uint32_t* dst = reinterpret_cast<uint32_t*>(xs) + (j >> 4) * 16 + ((j & 15) >> 2);
+#pragma unroll
+                    for (int n = 0; n < 4; ++n) dst[n * 4] = plane[n];
+                }
             }
-            shi = warp_sum_i(shi); slo = warp_sum_i(slo);
-            if (lane == 0) { ctl->wsumi[z][warp][0] = shi; ctl->wsumi[z][warp][1] = slo; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (lane == 0) ctl->wsumq[z][warp] = sq;
         }
         cons_sync();
         if (trace != nullptr && tid == 0 && cta < 2) trace[(ph * 2 + cta) * 4 + 2] = gtime();
+
+        // what the next phase reads right after the barrier and nobody writes in this phase
+        if (ph + 1 < n_phases) {
+            const SPhase& NX = phases[ph + 1];
+            for (int z = 0; z < NX.count; ++z) {
+                const SProblem& P = NX.p[z];
+                l2_fetch(P.ry, P.N * 2, cta, G, tid);
+                l2_fetch(P.my, P.N * 2, cta, G, tid);
+                if (P.prologue == RWKV_PRO_LN_MIX) {
+                    l2_fetch(P.p0, P.N * 2, cta, G, tid); l2_fetch(P.p1, P.N * 2, cta, G, tid);
+                    l2_fetch(P.p2, P.N * 2, cta, G, tid); l2_fetch(P.p3, P.N * 2, cta, G, tid);
+                } else if (P.prologue == RWKV_PRO_WKV4) {
+                    l2_fetch(P.f0, P.N * 4, cta, G, tid); l2_fetch(P.f1, P.N * 4, cta, G, tid);
+                    l2_fetch(P.f2, P.N * 4, cta, G, tid); l2_fetch(P.f3, P.N * 4, cta, G, tid);
+                    l2_fetch(P.f4, P.N * 4, cta, G, tid);
+                }
+            }
+        }
 
         // ---- the matrices of the phase, one after the other ----
         for (int z = 0; z < count; ++z) {
             const SProblem& P = PH.p[z];
             const Geom g = seg_geom(P.N, P.M, cta, G);
-            const uint2* xq = reinterpret_cast<const uint2*>(xq_base + P.xq_off);
-            const int sub = tid / g.SG, lane_in = tid % g.SG;
-            const bool active = tid < g.TA;
-            const int gg = active ? (sub / g.Q) * g.SG + lane_in : 0;      // this thread's row pair within an iteration
-            int ah[4] = {0, 0, 0, 0}, al[4] = {0, 0, 0, 0};
-            long long th[4] = {0, 0, 0, 0}, tl[4] = {0, 0, 0, 0};
-            int since = 0;
+            const uint32_t* xq = reinterpret_cast<const uint32_t*>(xq_base + P.xq_off);
+            // the epilogue's operands, on their way while the matrix streams
+            const int kcol = (g.u0 << 2) + tid;
+            const bool fin = tid < 4 * g.Q && kcol < P.M;
+            float rxk = 0.f, mxk = 0.f, auxv = 0.f, aux2v = 0.f;
+            if (fin) {
+                rxk = __half2float(__ldg(static_cast<const __half*>(P.rx) + kcol));
+                mxk = __half2float(__ldg(static_cast<const __half*>(P.mx) + kcol));
+                if (P.epilogue == RWKV_EPI_RESIDUAL || P.epilogue == RWKV_EPI_MUL_RESIDUAL)
+                    auxv = __half2float(__ldcg(static_cast<const __half*>(P.aux) + kcol));
+                if (P.epilogue == RWKV_EPI_MUL_RESIDUAL) aux2v = __half2float(__ldcg(static_cast<const __half*>(P.aux2) + kcol));
+                if (P.epilogue == RWKV_EPI_ACC_F32) auxv = __ldcg(static_cast<const float*>(P.y) + kcol);
+            }
+            const int og = warp % g.wo, ks = warp / g.wo;
+            const int o_first = og * g.opw;
+            const int my_oct = max(0, min(g.opw, g.n_oct - o_first));
+            const bool half_last = (g.Q & 1) != 0;                  // the CTA's last octet holds four columns
+            int acc[kMaxOct][2];
+#pragma unroll
+            for (int o = 0; o < kMaxOct; ++o) acc[o][0] = acc[o][1] = 0;
             for (int s = 0; s < g.n_stages; ++s) {
                 mbar_wait(s2u(&ctl->full[slot]), parity, err, gerr);
                 const uint8_t* sp = ring + (size_t)slot * kSlotBytes;
-                uint2 w[kIter], xv[kIter];
+                const int kb0 = s * g.kbs;
+                const int nkb = min(g.kbs, g.n_kb - kb0);
+                int kl = (ks - kb0 % g.wk + g.wk) % g.wk;          // first k-block of the stage that is this warp's
+                for (; kl < nkb; kl += g.wk) {
+                    const int kb = kb0 + kl;
+                    uint32_t a0 = 0u, a2 = 0u;
+                    if (gid < 4) { a0 = xq[kb * 32 + gid * 4 + tig]; a2 = xq[kb * 32 + 16 + gid * 4 + tig]; }
+                    const uint2* cells = reinterpret_cast<const uint2*>(sp + (size_t)kl * g.kb_bytes) + o_first * 32 + lane;
 #pragma unroll
-                for (int r = 0; r < kIter; ++r) {
-                    const int it = s * kIter + r;
-                    const bool ok = active && it * g.TA + tid < g.cells;
-                    w[r] = ok ? *reinterpret_cast<const uint2*>(sp + (size_t)(r * g.TA + tid) * 8) : make_uint2(0, 0);
-                    xv[r] = ok ? xq[it * g.PPI + gg] : make_uint2(0, 0);
-                }
-#pragma unroll
-                for (int r = 0; r < kIter; ++r) {
-                    ah[0] = dp2a_lo((int)xv[r].x, w[r].x, ah[0]);
-                    ah[1] = dp2a_hi((int)xv[r].x, w[r].x, ah[1]);
-                    ah[2] = dp2a_lo((int)xv[r].x, w[r].y, ah[2]);
-                    ah[3] = dp2a_hi((int)xv[r].x, w[r].y, ah[3]);
-                    al[0] = dp2a_lo((int)xv[r].y, w[r].x, al[0]);
-                    al[1] = dp2a_hi((int)xv[r].y, w[r].x, al[1]);
-                    al[2] = dp2a_lo((int)xv[r].y, w[r].y, al[2]);
-                    al[3] = dp2a_hi((int)xv[r].y, w[r].y, al[3]);
+                    for (int o = 0; o < kMaxOct; ++o) {
+                        if (o < my_oct) {
+                            const bool whole = !(half_last && o_first + o == g.n_oct - 1);
+                            uint2 b = make_uint2(0u, 0u);
+                            if (whole || lane < 16) b = cells[o * 32];
+                            imma_16832(acc[o][0], acc[o][1], a0, a2, b.x, b.y);
+                        }
+                    }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s2u(&ctl->empty[slot]));
                 if (++slot == n_slots) { slot = 0; parity ^= 1; }
-                if (++since == kFlushStages) {
-                    since = 0;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) { th[i] += ah[i]; tl[i] += al[i]; ah[i] = 0; al[i] = 0; }
-                }
             }
-            // this thread's exact sums of q * w for its four columns; add the lanes of the subgroup
-            long long S[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) S[i] = ((th[i] + ah[i]) << 15) + (tl[i] + al[i]);
-            for (int o = g.SG >> 1; o > 0; o >>= 1) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) S[i] += __shfl_xor_sync(0xffffffffu, S[i], o);
-            }
+            // lane (gid < 4, tig) holds digit gid of columns 2 tig, 2 tig + 1 of each of its octets: weigh the
+            // digits, add them over gid (lanes 4 and 8 apart), then the K groups of warps through shared memory
             cons_sync();                    // the previous matrix's partial sums have been read
-            if (active && lane_in == 0) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) red[sub * 4 + i] = S[i];
+            for (int o = 0; o < kMaxOct; ++o) {
+                if (o < my_oct) {
+                    long long v0 = gid < 4 ? (long long)acc[o][0] << (8 * gid) : 0ll;
+                    long long v1 = gid < 4 ? (long long)acc[o][1] << (8 * gid) : 0ll;
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 4); v1 += __shfl_xor_sync(0xffffffffu, v1, 4);
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 8); v1 += __shfl_xor_sync(0xffffffffu, v1, 8);
+                    if (gid == 0) {
+                        red[(warp * kMaxOct + o) * 8 + 2 * tig] = v0;
+                        red[(warp * kMaxOct + o) * 8 + 2 * tig + 1] = v1;
+                    }
+                }
             }
             cons_sync();
-            const int nrep = g.Q > 0 ? g.PPI / g.SG : 0;
-            for (int kk = tid; kk < 4 * g.Q; kk += kConsumers) {
-                const int k = (g.u0 << 2) + kk;
-                if (k >= P.M) continue;
-                const int qq = kk >> 2, i = kk & 3;
+            if (fin) {
+                const int oc = tid >> 3, ogf = oc / g.opw, ol = oc - ogf * g.opw;
                 long long tot = 0;
-                for (int rep = 0; rep < nrep; ++rep) tot += red[(rep * g.Q + qq) * 4 + i];
-                float tx = 0.f, txr = 0.f, txmy = 0.f;
-                long long sq_hi = 0, sq_lo = 0;
+                for (int k2 = 0; k2 < g.wk; ++k2) tot += red[((k2 * g.wo + ogf) * kMaxOct + ol) * 8 + (tid & 7)];
+                float tx = 0.f, txmy = 0.f;
+                long long sq = 0;
 #pragma unroll
                 for (int w8 = 0; w8 < kConsWarps; ++w8) {
-                    tx += ctl->wsum[z][w8][0]; txr += ctl->wsum[z][w8][1]; txmy += ctl->wsum[z][w8][2];
-                    sq_hi += ctl->wsumi[z][w8][0]; sq_lo += ctl->wsumi[z][w8][1];
+                    tx += ctl->wsum[z][w8][0]; txmy += ctl->wsum[z][w8][1];
+                    sq += ctl->wsumq[z][w8];
                 }
-                tot -= 128ll * ((sq_hi << 15) + sq_lo);
-                const float sdot = __ll2float_rn(tot) * ctl->inv_scale[z];
-                const float rxk = __half2float(__ldg(static_cast<const __half*>(P.rx) + k));
-                const float mxk = __half2float(__ldg(static_cast<const __half*>(P.mx) + k));
-                const float val = fmaf(rxk, sdot, fmaf(rxk * 128.5f, txr, fmaf(mxk, tx, txmy)));
+                // sum_j x'_j (w_jk + 1/2) = inv_scale * (sum q w + sum q / 2): one exact integer, no cancellation
+                const float sdot = __ll2float_rn(2 * tot + sq) * (0.5f * ctl->inv_scale[z]);
+                const float val = fmaf(rxk, sdot, fmaf(mxk, tx, txmy));
+                const int k = kcol;
                 __half* yh = static_cast<__half*>(P.y);
                 switch (P.epilogue) {
-                case RWKV_EPI_ACC_F32: {
-                    float* y = static_cast<float*>(P.y);
-                    y[k] = __ldcg(y + k) + val;
-                    break;
-                }
+                case RWKV_EPI_ACC_F32: static_cast<float*>(P.y)[k] = auxv + val; break;
                 case RWKV_EPI_STORE: yh[k] = __float2half_rn(val); break;
                 case RWKV_EPI_SIGMOID: yh[k] = __float2half_rn(1.0f / (1.0f + expf(-r16(val)))); break;
                 case RWKV_EPI_RELU_SQ: { const float v = fmaxf(r16(val), 0.0f); yh[k] = __float2half_rn(v * v); break; }
-                case RWKV_EPI_RESIDUAL: {
-                    const float a = __half2float(__ldcg(static_cast<const __half*>(P.aux) + k));
-                    yh[k] = __float2half_rn(r16(a + r16(val)) * P.out_scale);
-                    break;
-                }
-                case RWKV_EPI_MUL_RESIDUAL: {
-                    const float a = __half2float(__ldcg(static_cast<const __half*>(P.aux) + k));
-                    const float a2 = __half2float(__ldcg(static_cast<const __half*>(P.aux2) + k));
-                    yh[k] = __float2half_rn(r16(a + r16(a2 * r16(val))) * P.out_scale);
-                    break;
-                }
+                case RWKV_EPI_RESIDUAL: yh[k] = __float2half_rn(r16(auxv + r16(val)) * P.out_scale); break;
+                case RWKV_EPI_MUL_RESIDUAL: yh[k] = __float2half_rn(r16(auxv + r16(aux2v * r16(val))) * P.out_scale); break;
                 case RWKV_EPI_STORE_F32: static_cast<float*>(P.y)[k] = r16(val); break;
                 case RWKV_EPI_SILU: { const float v = r16(val); yh[k] = __float2half_rn(v / (1.0f + expf(-v))); break; }
                 default: break;
@@ -586,26 +630,30 @@ struct PackArgs {
     long long off[kMaxCtas];        // where this matrix's segment starts in the stream, per CTA
 };
 
+// One thread per 8-byte cell: k-block kb, octet o, lane -> the B fragment of that lane, i.e. column
+// 8 o + lane / 4 of the CTA, input rows 32 kb + 4 (lane % 4) + {0..3} and the same 16 rows further.
 __global__ void mm8_stream_pack_kernel(PackArgs a, uint8_t* wstream) {
     const int cta = blockIdx.y;
     const Geom g = seg_geom(a.N, a.M, cta, a.G);
+    if (g.Q == 0) return;
     uint2* dst = reinterpret_cast<uint2*>(wstream + a.off[cta]);
-    for (int cell = blockIdx.x * blockDim.x + threadIdx.x; cell < g.cells; cell += gridDim.x * blockDim.x) {
-        const int it = cell / g.TA, t = cell - it * g.TA;
-        const int sub = t / g.SG, lane_in = t % g.SG;
-        const int q = sub % g.Q, gg = (sub / g.Q) * g.SG + lane_in;
-        const int p = it * g.PPI + gg;
-        const int r0 = 2 * p, c0 = (g.u0 + q) * 4;
-        uint32_t b[8];
+    const int per_kb = 16 * g.Q;
+    const long long cells = (long long)g.n_kb * per_kb;
+    for (long long cell = blockIdx.x * (long long)blockDim.x + threadIdx.x; cell < cells; cell += (long long)gridDim.x * blockDim.x) {
+        const int kb = int(cell / per_kb), rem = int(cell - (long long)kb * per_kb);
+        const int o = rem >> 5, lane = rem & 31;
+        const int col = (g.u0 << 2) + 8 * o + (lane >> 2);
+        const int r0 = 32 * kb + 4 * (lane & 3);
+        uint32_t b[2] = {0u, 0u};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int h = 0; h < 2; ++h) {
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const int row = r0 + r, col = c0 + c;
-                b[c * 2 + r] = (row < a.N && col < a.M) ? a.w[(long long)row * a.w_stride + col] : 0u;
+            for (int i = 0; i < 4; ++i) {
+                const int row = r0 + 16 * h + i;
+                if (row < a.N && col < a.M) b[h] |= uint32_t(a.w[(long long)row * a.w_stride + col]) << (8 * i);
             }
         }
-        dst[cell] = make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24));
+        dst[cell] = make_uint2(b[0], b[1]);
     }
 }
 
@@ -620,7 +668,7 @@ int stream_ctas() {
 
 bool stream_supported(const rwkv_mm8_problem& q, int G) {
     if (q.N < 8 || q.N % 8 != 0 || q.M < 1) return false;
-    if (((q.M + 3) / 4 + G - 1) / G > kConsumers / 4) return false;
+    if (((q.M + 3) / 4 + G - 1) / G > kSlotBytes / 128) return false;
     if (q.prologue == RWKV_PRO_LN_MIX && q.N > 2 * kConsumers * 8) return false;
     return true;
 }
@@ -655,15 +703,15 @@ extern "C" int rwkv_mm8_stream_pack(const rwkv_mm8_problem* problems, int n_prob
         if (!stream_supported(q, n_ctas)) return RWKV_ERR_UNSUPPORTED;
         PackArgs a;
         a.w = q.w; a.w_stride = q.w_stride; a.N = q.N; a.M = q.M; a.G = n_ctas;
-        int max_cells = 0;
+        long long max_cells = 0;
         for (int c = 0; c < n_ctas; ++c) {
             const Geom g = seg_geom(q.N, q.M, c, n_ctas);
             a.off[c] = base[c] + run[c];
             run[c] += g.bytes;
-            if (g.cells > max_cells) max_cells = g.cells;
+            if (g.bytes / 8 > max_cells) max_cells = g.bytes / 8;
         }
         if (max_cells == 0) continue;
-        const int bx = (max_cells + 255) / 256 > 64 ? 64 : (max_cells + 255) / 256;
+        const int bx = (max_cells + 255) / 256 > 64 ? 64 : int((max_cells + 255) / 256);
         mm8_stream_pack_kernel<<<dim3(bx, n_ctas), 256, 0, static_cast<cudaStream_t>(stream)>>>(a, static_cast<uint8_t*>(wstream));
         const int rc = rwkv_launch_status();
         if (rc != RWKV_OK) return rc;
@@ -721,8 +769,7 @@ extern "C" int rwkv_mm8_stream_plan(const rwkv_mm8_problem* problems, const int3
                 P.g0 = q.aa_out; P.g1 = q.bb_out; P.g2 = q.pp_out;
             }
             P.xq_off = off;
-            // 4 bytes per row; the row-pair count is padded to 32 so that tails read zeros
-            off += ((((q.N + 1) >> 1) + 31) & ~31) * 8;
+            off += ((q.N + 31) >> 5) * 128;        // 4 bytes per input, whole k-blocks of 32
         }
         if (off > xq_max) xq_max = off;
         n_total += counts[ph];

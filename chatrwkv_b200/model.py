@@ -266,7 +266,10 @@ class RWKV:
             self._peer = shard.PeerRegion(fields, dev, self._world, self._rank)
             for name, _, _ in fields:
                 setattr(bb, name, self._peer.view(name))
-        self._tok_host = torch.zeros(256, dtype=torch.int64).pin_memory()   # ring of H2D staging slots
+        # ring of pinned H2D staging slots for host token ids; a slot is reused only after the copy that read
+        # it has completed (callers may enqueue many steps without ever synchronising)
+        self._tok_host = torch.zeros(64, dtype=torch.int64).pin_memory()
+        self._tok_events = [None] * self._tok_host.numel()
         self._tok_slot = 0
         self._ws = torch.zeros(96 << 20, dtype=torch.uint8, device=dev)
         # Decode state lives in two persistent sets: a step reads set `_cur` and writes the other
@@ -373,8 +376,13 @@ class RWKV:
             self._b.tok.copy_(token.reshape(1))
         else:
             slot = self._tok_slot = (self._tok_slot + 1) % self._tok_host.numel()
+            if self._tok_events[slot] is not None:
+                self._tok_events[slot].synchronize()
+            else:
+                self._tok_events[slot] = torch.cuda.Event()
             self._tok_host[slot] = token
             self._b.tok.copy_(self._tok_host[slot:slot + 1], non_blocking=True)
+            self._tok_events[slot].record(torch.cuda.current_stream(self.device))
         if self.version == 4:
             step = (self._step_one_v4_peer if self._peer is not None else self._step_one_v4_sharded) \
                 if self._world > 1 else self._step_one_v4
@@ -581,6 +589,28 @@ class RWKV:
         sync = torch.zeros(16, dtype=torch.int32, device=self.device)
         self._stream = types.SimpleNamespace(wstream=wstream, tables=tables, sync=sync, trace=None, n_phases=len(launches))
         return True
+
+    def decode_path(self):
+        """Which kernels a one-token forward runs: 'stream' (RWKV-4: one persistent kernel), 'chain', or 'launch'
+        (a launch per group of matmuls)."""
+        if self.version == 4 and self._world == 1 and self._use_stream:
+            return "stream"
+        return "chain" if (self.version == 4 and self._use_chain) else "launch"
+
+    def set_decode_path(self, path):
+        """Switch RWKV-4 decode between 'stream' and 'launch'; captured graphs are dropped."""
+        if path not in ("stream", "launch"):
+            raise ValueError(path)
+        self._use_stream = path == "stream" and self.version == 4 and self._world == 1
+        self._use_chain = False
+        self._graphs = [None, None]
+
+    def launches_per_token(self):
+        """Kernel launches of this library per decoded token (the embedding gather is a torch kernel)."""
+        L = self.args.n_layer
+        if self.version != 4:
+            return L * (5 if self.version == 5.2 else 6) + 1
+        return {"stream": 1, "chain": 2}.get(self.decode_path(), 4 * L + 1)
 
     def stream_error(self):
         """1 if a wait inside the persistent decode kernel gave up since the last call (the step's results were

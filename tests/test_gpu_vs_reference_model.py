@@ -9,8 +9,16 @@ reference's after the prompt and at EVERY decode step (the product is teacher-fo
 reference's greedy tokens), and the product's arg-max equal to the reference's next token at
 every step; a step whose arg-max differs is forgiven only when the reference's own top-2
 margin is below twice the logit difference observed at that step, and the number of forgiven
-steps is recorded.  Both decode arithmetics are run (default and the fp32 form).  The
-reference's decode rate and prefill time on the same GPU are recorded next to the product's.
+steps is recorded.  Every decode path of the runtime is run.  The reference's decode rate and
+prefill time on the same GPU are recorded next to the product's.
+
+The reference is not bit-stable: its mm8_one adds partial sums with atomics in arbitrary order
+(operators.cu:230), a different fp32 sum flips fp16 roundings, and the flips random-walk through
+the layers.  The runner therefore repeats the whole protocol and reports the reference's own
+run-to-run difference (`noise_max`).  Measured on a B200: 0.003 at the 169M shape, 0.022 at the
+7B shape, 0.025 at 14B, 0.042 for RWKV-6 7B -- above 2e-2 from 7B on.  The bound asserted is
+therefore max(2e-2, 1.5 x noise_max): 2e-2 wherever the reference itself can meet it, and
+"indistinguishable from a second run of the reference" where it cannot.
 
 Reports go to $RWKV_B200_REPORT_DIR/reference_model_<config>.json when that variable is set.
 """
@@ -143,14 +151,16 @@ def test_logits_and_greedy_tokens_match_reference_cuda_path(name, tmp_path):
                                         "min_reference_top2_margin": min_margin, "decode_tok_s_host_loop": rate}
     finally:
         _lib.lib().rwkv_mm8_one_set_variant(0)
+    tol = max(TOL, 1.5 * float(ref["noise_max"])) if "noise_max" in ref else TOL
+    report["tolerance"] = tol
     rdir = os.environ.get("RWKV_B200_REPORT_DIR")
     if rdir:
         os.makedirs(rdir, exist_ok=True)
         with open(os.path.join(rdir, f"reference_model_{name}.json"), "w") as f:
             json.dump(report, f, indent=1)
     print(json.dumps(report))
-    assert err_p <= TOL and first_ok, report
+    assert err_p <= tol and first_ok, report
     for label, _, _ in paths:
         r = report["product"][label]
-        assert r["max_abs"] <= TOL, report
+        assert r["max_abs"] <= tol, report
         assert r["argmax_mismatch_steps"] == r["forgiven_steps"], report
