@@ -536,7 +536,7 @@ def gemv_roofline(model, dev, reps=30):
         source = "scaled: DRAM bytes per algorithmic byte from an ncu capture of a 2-layer model of the same shape"
     except Exception:
         pass
-    kernel = {"stream": "mm8_stream_kernel", "chain": "mm8_chain_kernel"}.get(path, "mm8_cluster_kernel")
+    kernel = "mm8_stream_kernel" if path == "stream" else "mm8_cluster_kernel"
     return {"bound": "hbm", "kernel": kernel, "achieved": achieved,
             "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": how, "traffic": traffic,
             "traffic_source": source, "launches_per_step": n_launch, "avg_launch_us": ms / n_launch * 1e3,

@@ -15,6 +15,7 @@ OK = 0
 F32, F16, BF16 = 0, 1, 2
 PRO_PLAIN, PRO_LN_MIX, PRO_WKV4 = 0, 1, 2
 ERR_UNSUPPORTED = -5
+MM8_WIDE_BUILD = 1
 EPI_ACC_F32, EPI_STORE, EPI_SIGMOID, EPI_RELU_SQ, EPI_RESIDUAL, EPI_MUL_RESIDUAL, EPI_STORE_F32, EPI_SILU = range(8)
 
 
@@ -63,6 +64,7 @@ SIGNATURES = {
     "rwkv_mm8_one_batch_workspace_bytes": (_sz, [C.POINTER(Mm8Problem), _i32]),
     "rwkv_mm8_one_batch": (_i32, [C.POINTER(Mm8Problem), _i32, _i32, _vp, _sz, _vp]),
     "rwkv_mm8_one_batch_exchange": (_i32, [C.POINTER(Mm8Problem), _i32, C.POINTER(Mm8Exchange), _i32, _vp, _sz, _vp]),
+    "rwkv_mm8_one_batch_flags": (_i32, [C.POINTER(Mm8Problem), _i32, C.POINTER(Mm8Exchange), _i32, _i32, _vp, _sz, _vp]),
     "rwkv_peer_alloc": (_i32, [_sz, C.POINTER(_vp)]),
     "rwkv_peer_free": (_i32, [_vp]),
     "rwkv_peer_export": (_i32, [_vp, _vp]),
@@ -74,12 +76,8 @@ SIGNATURES = {
     "rwkv_mm8_one_set_variant": (None, [_i32]),
     "rwkv_mm8_one_set_cluster": (None, [_i32, _i32]),
     "rwkv_mm8_one_set_plan": (None, [_i64, _i32]),
-    "rwkv_mm8_chain_ctas": (_i32, []),
-    "rwkv_mm8_chain_table_bytes": (_sz, [_i32, _i32]),
-    "rwkv_mm8_chain_plan": (_i32, [C.POINTER(Mm8Problem), C.POINTER(C.c_int32), _i32, _i32, _i32, _vp, _sz, _vp, _sz]),
-    "rwkv_mm8_chain_run": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp]),
-    "rwkv_mm8_chain_take_error": (_i32, [_vp, _vp, C.POINTER(C.c_int)]),
     "rwkv_mm8_stream_ctas": (_i32, []),
+    "rwkv_mm8_stream_set_planes": (None, [_i32]),
     "rwkv_mm8_stream_weight_bytes": (_sz, [C.POINTER(Mm8Problem), _i32, _i32]),
     "rwkv_mm8_stream_pack": (_i32, [C.POINTER(Mm8Problem), _i32, _i32, _vp, _sz, _vp]),
     "rwkv_mm8_stream_table_bytes": (_sz, [_i32]),

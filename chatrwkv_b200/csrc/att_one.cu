@@ -655,9 +655,14 @@ extern "C" int rwkv_v6_att_pre(int64_t D, int64_t Lm, int64_t Ld, const void* x,
     a.D = int(D); a.Lm = int(Lm); a.Ld = int(Ld);
     // 16 CTAs (a non-portable cluster size) halve every CTA's share of the weights; 8 where the
     // device or the shape (fewer than 16 x 8 channels) does not allow it.
-    static int big = -1;
-    if (big < 0)
-        big = cudaFuncSetAttribute(v6_att_pre_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess ? 1 : 0;
+    static int big_by_device[64];            // 0 = not asked yet, 1 = allowed, 2 = refused (function attributes are per device)
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); dev = -1; }
+    int big = dev >= 0 ? big_by_device[dev] : 0;
+    if (big == 0) {
+        big = cudaFuncSetAttribute(v6_att_pre_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess ? 1 : 2;
+        if (dev >= 0) big_by_device[dev] = big;
+    }
     cudaGetLastError();
     a.ncta = (big == 1 && D >= 16 * 64) ? 16 : 8;
     a.rows = int(((D + a.ncta - 1) / a.ncta + 7) / 8 * 8);

@@ -43,14 +43,16 @@ static inline int rwkv_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
     return RWKV_OK;
 }
 
-static inline int rwkv_sm_count() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+static inline int rwkv_sm_count() {       // of the current device
+    static int sms_by_device[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return 148; }
+    if (sms_by_device[dev] == 0) {
+        int sms = 0;
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        sms_by_device[dev] = sms;
     }
-    return sms;
+    return sms_by_device[dev];
 }
 
 template <typename F> __device__ __forceinline__ float to_f32(F v);

@@ -514,11 +514,12 @@ int g_plan_n = 0;
 // Clusters of `S` CTAs (256 threads, `smem` bytes each) that can be resident at once on the
 // current device; 0 if the query fails.  Asked once per (device, S).
 template <typename K>
-static inline int cluster_slots(K kern, int S, int smem) {
-    static int cache[64][kMaxClusterSize + 1] = {};
+static inline int cluster_slots(K kern, int S, int smem, int build) {
+    static int cache[64][2][kMaxClusterSize + 1] = {};         // per device and build (the two builds share a function type)
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return 0; }
-    if (cache[dev][S] != 0) return cache[dev][S] > 0 ? cache[dev][S] : 0;
+    build = build ? 1 : 0;
+    if (cache[dev][build][S] != 0) return cache[dev][build][S] > 0 ? cache[dev][build][S] : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(S) * 64u);
     cfg.blockDim = dim3(kThreads);
@@ -532,13 +533,14 @@ static inline int cluster_slots(K kern, int S, int smem) {
     cfg.numAttrs = 1;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = -1; }
-    cache[dev][S] = n;
+    cache[dev][build][S] = n;
     return n > 0 ? n : 0;
 }
 
 // Launch the validated problems of `plan_b` (mm8_plan filled them in) on the cluster kernel.
 // RWKV_ERR_UNSUPPORTED: this batch is not eligible and the caller should use the ticket kernel.
-static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, int mode, const Exchange* exch, cudaStream_t st) {
+static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, int mode, const Exchange* exch, bool wide_hint,
+                                     cudaStream_t st) {
     if (g_cluster_size < 0) return RWKV_ERR_UNSUPPORTED;
     ClusterBatch cb;
     memset(&cb, 0, sizeof(cb));
@@ -560,13 +562,11 @@ static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, 
     if (g_cluster_size == 0) while (S > 1 && min_n < S * 64) S >>= 1;
     const int rows_needed = ((max_n + S - 1) / S + 7) & ~7;
     if (rows_needed > kWideRowsPerCta) return RWKV_ERR_UNSUPPORTED;
-    // more than 2048 rows per CTA (20480 in-features): the build with the larger x' buffer, fp16 / integer only
-    // Once a launch has needed it, every later launch of the process uses that build too: launches
-    // that alternate between the two builds (different shared-memory footprints) lost their overlap
-    // (14B shape: 241 tok/s alternating, 305 with the wide build throughout).
-    static bool wide_seen = false;
-    if (rows_needed > kMaxRowsPerCta) wide_seen = true;
-    const bool wide = wide_seen && dtype == RWKV_F16 && mode == 2;
+    // more than 2048 rows per CTA (20480 in-features): the build with the larger x' buffer, fp16 / integer only.
+    // `wide_hint` asks for that build although this launch would fit the other one: launches that alternate
+    // between the two builds (different shared-memory footprints) lose their overlap (14B shape: 241 tok/s
+    // alternating, 305 with the wide build throughout), so a model with such a matrix asks for it everywhere.
+    const bool wide = (rows_needed > kMaxRowsPerCta || wide_hint) && dtype == RWKV_F16 && mode == 2;
     if (rows_needed > kMaxRowsPerCta && !wide) return RWKV_ERR_UNSUPPORTED;
     if ((exch != nullptr || wide) && (dtype != RWKV_F16 || mode != 2)) return RWKV_ERR_UNSUPPORTED;
     constexpr int RN = kMaxRowsPerCta, RW = kWideRowsPerCta;
@@ -581,7 +581,7 @@ static inline int mm8_cluster_launch(const Batch& plan_b, int count, int dtype, 
         cudaGetLastError();
         return RWKV_ERR_UNSUPPORTED;
     }
-    int slots = exch ? cluster_slots(kern_x, S, smem) : cluster_slots(kern, S, smem);
+    int slots = exch ? cluster_slots(kern_x, S, smem, wide) : cluster_slots(kern, S, smem, wide);
     if (slots <= 0) return RWKV_ERR_UNSUPPORTED;
     // Plan for four fifths of the resident clusters (26 of 33): the slots left free let the next
     // launch's first clusters become resident, and fill their rings, while this one still streams

@@ -1,6 +1,5 @@
-// Shared pieces of the mm8_one kernels (single launch: mm8_one.cu; persistent chain:
-// mm8_chain.cu): problem descriptors, byte -> fp32 conversion, the fused prologues and
-// epilogues, and the host-side launch planner.
+// Shared pieces of the mm8_one launch kernels (mm8_one.cu, mm8_cluster.cuh): problem descriptors,
+// byte -> fp32 conversion, the fused prologues and epilogues, and the host-side launch planner.
 #pragma once
 #include "common.cuh"
 
@@ -12,7 +11,7 @@ constexpr int kMaxRowsPerCta = 2048; // x' slice kept in shared memory
 constexpr int kWideRowsPerCta = 2560; // the cluster kernel's second build: 20480 in-features (14B shape) / 8 splits
 constexpr int kMaxSplit = 64;
 constexpr int kPanelMin = 128;
-constexpr int kCounterBytes = 4096;  // panel tickets; the last two words belong to the chain kernel
+constexpr int kCounterBytes = 4096;  // panel tickets (the last two words are unused)
 constexpr int kMaxTickets = kCounterBytes / 4 - 2;
 constexpr int kSumsBytes = (kCounterBytes / 4) * kMaxSplit * 4 * sizeof(float);  // [panel ticket][split][4]
 constexpr int kMaxProblems = 4;
@@ -204,8 +203,8 @@ __device__ __forceinline__ float quantize_pairs(float* xs, int rpp, int cpr, int
     return m > 0.f ? m / float(qmax) : 0.f;
 }
 
-// Loads of activations and state go to L2 (ld.global.cg): inside the persistent chain kernel
-// they may have been written by another SM a moment ago, and L1 is not coherent.
+// Loads of activations and state go to L2 (ld.global.cg): under programmatic dependent launch they may
+// have been written by another SM a moment ago, and L1 is not coherent.
 template <typename F>
 __device__ __forceinline__ float ldc(const void* base, int i) { return to_f32<F>(__ldcg(static_cast<const F*>(base) + i)); }
 
@@ -345,7 +344,7 @@ __device__ __forceinline__ float prologue_value(const Problem& P, int j, float m
 // ---------------------------------------------------------------------------------------------
 // Host side: validate up to three problems and lay out one launch (panel width, K-splits,
 // scratch offsets).  `slots` = CTAs that should run at once (CTAs per SM x SMs); `fit_only`
-// forbids plans with more CTAs than slots (the persistent chain kernel needs that).
+// forbids plans with more CTAs than slots.
 // ---------------------------------------------------------------------------------------------
 struct LaunchPlan {
     Batch b;

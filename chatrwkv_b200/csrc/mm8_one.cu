@@ -277,13 +277,26 @@ extern "C" size_t rwkv_mm8_one_batch_workspace_bytes(const rwkv_mm8_problem* pro
     return mm8_batch_ws_bytes(problems, count);
 }
 
+static int mm8_one_batch_impl(const rwkv_mm8_problem* problems, int count, const rwkv_mm8_exchange* exchange, int dtype,
+                              int flags, void* workspace, size_t workspace_bytes, void* stream);
+
 extern "C" int rwkv_mm8_one_batch(const rwkv_mm8_problem* problems, int count, int dtype,
                                   void* workspace, size_t workspace_bytes, void* stream) {
-    return rwkv_mm8_one_batch_exchange(problems, count, nullptr, dtype, workspace, workspace_bytes, stream);
+    return mm8_one_batch_impl(problems, count, nullptr, dtype, 0, workspace, workspace_bytes, stream);
 }
 
 extern "C" int rwkv_mm8_one_batch_exchange(const rwkv_mm8_problem* problems, int count, const rwkv_mm8_exchange* exchange,
                                            int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+    return mm8_one_batch_impl(problems, count, exchange, dtype, 0, workspace, workspace_bytes, stream);
+}
+
+extern "C" int rwkv_mm8_one_batch_flags(const rwkv_mm8_problem* problems, int count, const rwkv_mm8_exchange* exchange,
+                                        int dtype, int flags, void* workspace, size_t workspace_bytes, void* stream) {
+    return mm8_one_batch_impl(problems, count, exchange, dtype, flags, workspace, workspace_bytes, stream);
+}
+
+static int mm8_one_batch_impl(const rwkv_mm8_problem* problems, int count, const rwkv_mm8_exchange* exchange, int dtype,
+                              int flags, void* workspace, size_t workspace_bytes, void* stream) {
     LaunchPlan plan;
     static const int max_rows[3] = {kMaxRowsPerCta, kMaxRowsPerCta, kMaxRowsPerCta};
     const int force_pw = (g_variant & 3) != 0 ? (1024 >> (g_variant & 3)) : 0;
@@ -317,7 +330,7 @@ extern "C" int rwkv_mm8_one_batch_exchange(const rwkv_mm8_problem* problems, int
     if (aligned && (g_variant & 3) == 0 && g_split_override == 0) {
         // K-splits of a panel as one thread-block cluster (mm8_cluster.cuh); falls through to the
         // ticket kernel when the batch is not eligible.
-        const int crc = mm8_cluster_launch(plan.b, count, dtype, (g_variant & 4) ? 0 : (g_variant & 8) ? 1 : 2, exp,
+        const int crc = mm8_cluster_launch(plan.b, count, dtype, (g_variant & 4) ? 0 : (g_variant & 8) ? 1 : 2, exp, (flags & RWKV_MM8_WIDE_BUILD) != 0,
                                            static_cast<cudaStream_t>(stream));
         if (crc != RWKV_ERR_UNSUPPORTED) return crc;
     }

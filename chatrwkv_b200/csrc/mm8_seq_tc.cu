@@ -531,13 +531,15 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
     a.vec_ok = (reinterpret_cast<uintptr_t>(y) % 16 == 0 && y_stride % 8 == 0 && reinterpret_cast<uintptr_t>(rx) % 16 == 0 &&
                 reinterpret_cast<uintptr_t>(mx) % 16 == 0) ? 1 : 0;
     auto kern = mm8_seq_tc_kernel<__half>;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};         // function attributes are per device
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) { cudaGetLastError(); return RWKV_ERR_LAUNCH; }
+    if (dev >= 64 || !configured[dev]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc) != cudaSuccess) {
             cudaGetLastError();
             return RWKV_ERR_LAUNCH;
         }
-        configured = true;
+        if (dev < 64) configured[dev] = true;
     }
     int ks = tc_ksplit(B, N, M);
     a.kb_per = (nkb_all + ks - 1) / ks;

@@ -20,14 +20,15 @@
 //     (LayerNorm + token-shift mix, RWKV-4 WKV step) redundantly.
 //
 // Arithmetic: x' = x * ry is quantised per vector to a 31-bit integer q = sum_n d_n 256^n with four
-// signed base-256 digits.  mma.sync.m16n8k32.s8.u8 multiplies a 16 x 32 tile whose rows 0..3 are the
-// digit planes of 32 consecutive inputs with a 32 x 8 tile of raw codes: D[n][c] = sum_k d_n[k]
-// w[k][c] in exact 32-bit integers (|d w| <= 32640, so 65536 inputs cannot overflow).  The streamed
-// part of mm8_one (operators.cu:224-230) is therefore computed exactly for the quantised x', whose
-// relative error (2^-24 of fp32 for large entries, 2^-30 of the largest entry for small ones) is
-// that of an fp32 product; no result depends on a summation order.  The tensor pipe is used because
-// it takes one instruction per 256 code bytes where dp2a takes eight: the kernel is HBM-bound and
-// the issue slots were what kept the math from catching up after a phase change.
+// signed base-256 digits, stored as digit planes.  dp4a multiplies the four digits-n of four
+// consecutive inputs with the four raw codes of one column: exact 32-bit sums per digit (|d w| <=
+// 32640 per product, so 65536 inputs cannot overflow), weighted by 256^n in 64-bit integers at the
+// end.  The streamed part of mm8_one (operators.cu:224-230) is therefore computed exactly for the
+// quantised x', whose relative error (2^-24 of fp32 for large entries, 2^-30 of the largest entry
+// for small ones) is that of an fp32 product; no result depends on a summation order.
+// (Measured and dropped: the same products on mma.sync.m16n8k32.s8.u8 -- digit planes as the rows of
+// A, eight columns of codes as B -- ran at ~22 clocks per instruction and SM on the B200, half the
+// speed of the dp2a/dp4a forms.)
 #include "common.cuh"
 
 namespace {
@@ -35,13 +36,15 @@ namespace {
 constexpr int kConsumers = 512;
 constexpr int kConsWarps = kConsumers / 32;
 constexpr int kStreamThreads = kConsumers + 32;          // + the producer warp
-constexpr int kSlotBytes = 16384;
-constexpr int kMaxOct = 12;                              // column octets a warp accumulates (24 registers)
-constexpr int kRedBytes = kConsWarps * kMaxOct * 8 * 8;  // [warp][octet][column] 64-bit partial sums
+constexpr int kIter = 2;                                 // 16-byte cells per thread and stage
+constexpr int kSlotBytes = kIter * kConsumers * 16;      // 16 KB
+constexpr int kRedBytes = 128 * 4 * 8;                   // [<= 128 subgroups][4 columns] 64-bit sums
 constexpr int kMaxSlots = 12;
 constexpr int kMaxCtas = 160;
 constexpr int kMaxPhaseProblems = 4;
-constexpr float kQMax = 1.0e9f;                          // |q| <= 1e9 < 2^30
+constexpr int kMaxSegments = 448;                        // matrices per step (the producer's list lives in shared memory)
+// Largest |q| by number of digit planes multiplied: the digits above the last plane are then zero.
+__host__ __device__ constexpr float qmax_for(int planes) { return planes >= 4 ? 1.0e9f : planes == 3 ? 8.0e6f : 32000.0f; }
 constexpr unsigned long long kWaitNs = 2000000000ull;    // every wait gives up after 2 s
 
 struct SProblem {
@@ -63,36 +66,43 @@ struct SProblem {
     float *g0, *g1, *g2;
     int xq_off;         // byte offset of this problem's activations in shared memory
     int share_ln;       // same x and LayerNorm as the previous problem of the phase: statistics reused
+    // the layout of the matrix for a CTA (seg_geom), tabulated by the host: CTAs below `rem` own base + 1 quads
+    int base, rem;
+    int gSG[2], gGPI[2], gTA[2], gcells[2], gstages[2];
 };
 
 struct SPhase {
     int count;
-    int pad;
+    int ln_shared;      // every problem is RWKV_PRO_LN_MIX on the same x and LayerNorm (up to 8192 inputs)
     SProblem p[kMaxPhaseProblems];
+    int pad[2];
 };
+static_assert(sizeof(SPhase) % 16 == 0, "phase records are copied in 16-byte pieces");
 
-struct STable {
+struct STable {      // 16-byte multiple: the phase records that follow are copied in 16-byte pieces
     int n_phases, n_ctas, xq_bytes, n_slots;
+    int planes, n_segments, pad1, pad2; // digit planes the matrices are multiplied with (2, 3 or 4); matrices per step
     long long cta_base[kMaxCtas];       // byte offset of every CTA's region in the weight stream
     // SPhase phases[n_phases] follow
 };
 
-// How one matrix is laid out for one CTA.  Its columns are 4 * Q consecutive ones, grouped in
-// octets (the N dimension of the instruction; the last octet holds 4 columns when Q is odd); its
-// rows in k-blocks of 32 (the K dimension).  One k-block of all the CTA's columns is 128 * Q
-// contiguous bytes: per octet 32 (or 16) cells of 8 bytes, cell `lane` = the B fragment of that lane.
-// The 16 warps are wo groups along the columns (<= kMaxOct octets each) times wk = 16 / wo along K:
-// warp (og, ks) takes the k-blocks kb with kb % wk == ks.
+static_assert(sizeof(STable) % 16 == 0, "phase records start 16-byte aligned");
+
+// How one matrix is laid out for one CTA.  A cell is 16 bytes: 4 consecutive inputs ("k-group") x 4
+// consecutive columns ("quad"), one 32-bit word per column holding the 4 inputs' codes.  The CTA
+// owns Q quads.  A subgroup of SG lanes works on one quad; there are as many subgroups per quad as
+// fit 512 threads, so an iteration of the CTA covers GPI = SG * subgroups k-groups of every quad, and
+// thread t's cell of iteration `it` sits at byte (it * TA + t) * 16 of the matrix's segment.
 struct Geom {
     int Q;              // column quads owned by this CTA
     int u0;             // first quad
-    int n_oct;          // octets, the last one half when Q is odd
-    int wo, opw, wk;
-    int n_kb;           // ceil(N / 32)
-    int kb_bytes;       // 128 * Q
-    int kbs;            // k-blocks per stage
+    int SG;             // lanes that share a quad inside a warp (4, 8, 16 or 32)
+    int GPI;            // k-groups per iteration
+    int TA;             // active threads = Q * GPI
+    int kg;             // k-groups, rounded up to a multiple of SG
+    int cells;          // kg * Q
     int n_stages;
-    long long bytes;
+    long long bytes;    // cells * 16
 };
 
 __host__ __device__ inline Geom seg_geom(int N, int M, int cta, int G) {
@@ -101,18 +111,34 @@ __host__ __device__ inline Geom seg_geom(int N, int M, int cta, int G) {
     const int base = U / G, rem = U % G;
     g.Q = base + (cta < rem ? 1 : 0);
     g.u0 = cta * base + (cta < rem ? cta : rem);
-    g.n_oct = 0; g.wo = 1; g.opw = 0; g.wk = kConsWarps; g.n_kb = 0; g.kb_bytes = 0; g.kbs = 1; g.n_stages = 0; g.bytes = 0;
-    if (g.Q == 0 || g.Q > kSlotBytes / 128) return g;     // more than 128 quads per CTA: not planned (see plan)
-    g.n_oct = (g.Q + 1) >> 1;
-    while ((g.n_oct + g.wo - 1) / g.wo > kMaxOct) g.wo <<= 1;
-    g.opw = (g.n_oct + g.wo - 1) / g.wo;
-    g.wk = kConsWarps / g.wo;
-    g.n_kb = (N + 31) >> 5;
-    g.kb_bytes = 128 * g.Q;
-    g.kbs = kSlotBytes / g.kb_bytes;
-    if (g.kbs >= g.wk) g.kbs = g.kbs / g.wk * g.wk;       // every K group of warps gets the same share of a stage
-    g.n_stages = (g.n_kb + g.kbs - 1) / g.kbs;
-    g.bytes = (long long)g.n_kb * g.kb_bytes;
+    g.SG = 4; g.GPI = 0; g.TA = 0; g.kg = 0; g.cells = 0; g.n_stages = 0; g.bytes = 0;
+    if (g.Q == 0 || g.Q > kConsumers / 4) return g;       // more than 128 quads per CTA: not planned (see plan)
+    int best_ta = 0;
+    for (int sg = 32; sg >= 4; sg >>= 1) {
+        const int nsub = (kConsumers / sg) / g.Q;
+        const int ta = nsub * g.Q * sg;
+        if (ta > best_ta) { best_ta = ta; g.SG = sg; }
+    }
+    g.TA = best_ta;
+    g.GPI = best_ta / g.Q;
+    const int kg = (N + 3) >> 2;
+    g.kg = (kg + g.SG - 1) / g.SG * g.SG;
+    g.cells = g.kg * g.Q;
+    const int per_stage = kIter * g.TA;
+    g.n_stages = (g.cells + per_stage - 1) / per_stage;
+    g.bytes = (long long)g.cells * 16;
+    return g;
+}
+
+// seg_geom from the table the host put into the problem record (no divisions on the device)
+__device__ __forceinline__ Geom seg_geom_dev(const SProblem& P, int cta) {
+    Geom g;
+    const int v = cta < P.rem ? 1 : 0;
+    g.Q = P.base + v;
+    g.u0 = cta * P.base + (v ? cta : P.rem);
+    g.SG = P.gSG[v]; g.GPI = P.gGPI[v]; g.TA = P.gTA[v]; g.cells = P.gcells[v]; g.n_stages = P.gstages[v];
+    g.kg = 0;
+    g.bytes = (long long)g.cells * 16;
     return g;
 }
 
@@ -146,13 +172,35 @@ __device__ __forceinline__ unsigned long long gtime() {
 }
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
 
-// D[16 x 8] (s32) += A[16 x 32] (s8, rows 0..7 in a0 / a2, rows 8..15 zero) * B[32 x 8] (u8).  Only rows
-// 0..7 are kept (d0, d1); the other half of the tile multiplies zeros.
-__device__ __forceinline__ void imma_16832(int& d0, int& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    int z0, z1;
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %10, %10};"
-                 : "+r"(d0), "+r"(d1), "=r"(z0), "=r"(z1)
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "r"(0));
+__device__ __forceinline__ unsigned short ld_cg_u16(const void* p) {
+    unsigned short v;
+    asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ld_cg_f32(const void* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+// c + sum_i a.byte_i (signed digit) * b.byte_i (unsigned code)
+__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// The cells of one stage: acc[column][digit] += digits of 4 inputs . codes of 4 inputs, for P digit planes.
+template <int P>
+__device__ __forceinline__ void stage_math(int (&acc)[4][4], const uint4 (&w)[kIter], const uint4 (&xv)[kIter]) {
+#pragma unroll
+    for (int r = 0; r < kIter; ++r) {
+        const uint32_t wc[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
+        const uint32_t dn[4] = {xv[r].x, xv[r].y, xv[r].z, xv[r].w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int n = 0; n < P; ++n) acc[c][n] = dp4a_su(dn[n], wc[c], acc[c][n]);
+    }
 }
 
 // Bounded wait on an mbarrier phase.  After the first give-up in this CTA (*err set) later waits
@@ -177,26 +225,43 @@ struct SharedCtl {
     long long wsumq[kMaxPhaseProblems][kConsWarps];   // per warp: sum of the quantised activations
     float wsum[kMaxPhaseProblems][kConsWarps][2];     // per warp: sum x, sum x*my
     float inv_scale[kMaxPhaseProblems];
-    float red[kConsWarps][4];
+    float tot_x[kMaxPhaseProblems], tot_xmy[kMaxPhaseProblems];     // sums over all inputs, made once per problem
+    long long tot_q[kMaxPhaseProblems];
+    float red[2][kConsWarps][4];
     int err;
+    int pad[3];
+    alignas(16) SPhase phase[2];        // the current and the next phase's records, copied from the table ahead of use
+    uint2 sched[kMaxSegments];          // the producer's list: {cells, TA | stages << 16} of every matrix for this CTA
 };
 
-// Sums (SUM) or maxima of up to four values over the 512 consumer threads.
-template <bool SUM>
-__device__ __forceinline__ void cons_block_reduce4(float (&v)[4], float (*sh)[4], int warp, int lane) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = SUM ? warp_sum(v[i]) : warp_max(v[i]);
+// Reductions over the 512 consumer threads.  Two scratch buffers alternate (`flip`), so one barrier per
+// reduction is enough: a buffer is rewritten only after every thread has passed the barrier of the
+// reduction in between, i.e. after it has finished reading.
+__device__ __forceinline__ void cons_block_sum2(float& a, float& b, float (*sh)[kConsWarps][4], int& flip, int warp, int lane) {
+    a = warp_sum(a); b = warp_sum(b);
+    float (*buf)[4] = sh[flip];
+    flip ^= 1;
+    if (lane == 0) { buf[warp][0] = a; buf[warp][1] = b; }
     cons_sync();
-    if (lane == 0) {
+    a = 0.f; b = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sh[warp][i] = v[i];
+    for (int w = 0; w < kConsWarps; ++w) { a += buf[w][0]; b += buf[w][1]; }
+}
+// maxima of four non-negative values (their bit patterns order like the values; +inf stays the largest)
+__device__ __forceinline__ void cons_block_max4(float (&v)[4], float (*sh)[kConsWarps][4], int& flip, int warp, int lane) {
+    float (*buf)[4] = sh[flip];
+    flip ^= 1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const unsigned m = __reduce_max_sync(0xffffffffu, __float_as_uint(v[i]));
+        if (lane == 0) buf[warp][i] = __uint_as_float(m);
     }
     cons_sync();
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        float t = SUM ? 0.f : sh[0][i];
+        float t = buf[0][i];
 #pragma unroll
-        for (int w = SUM ? 0 : 1; w < kConsWarps; ++w) t = SUM ? t + sh[w][i] : fmaxf(t, sh[w][i]);
+        for (int w = 1; w < kConsWarps; ++w) t = fmaxf(t, buf[w][i]);
         v[i] = t;
     }
 }
@@ -219,26 +284,8 @@ __device__ __forceinline__ uint4 ldg16(const void* base, int j8) { return __ldg(
 // The W (4 or 8) activations starting at element j are multiplied with ry, written as fp32 x' and
 // added to the running sums.  A NaN anywhere makes the maximum infinite (a NaN does not survive fmaxf).
 template <int W>
-__device__ __forceinline__ void emit(const float (&xv)[W], const SProblem& P, int j, float* xs, float& sx, float& sxmy,
-                                     float& xmax) {
-    float ry[W], my[W];
-    if (W == 8) {
-        float a[8], b[8];
-        h8_to_f(ldg16(P.ry, j), a);
-        h8_to_f(ldg16(P.my, j), b);
-#pragma unroll
-        for (int e = 0; e < W; ++e) { ry[e] = a[e]; my[e] = b[e]; }
-    } else {
-        const uint2 a = __ldg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.ry) + j));
-        const uint2 b = __ldg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.my) + j));
-        const __half2* ha = reinterpret_cast<const __half2*>(&a);
-        const __half2* hb = reinterpret_cast<const __half2*>(&b);
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const float2 fa = __half22float2(ha[e]), fb = __half22float2(hb[e]);
-            ry[2 * e] = fa.x; ry[2 * e + 1] = fa.y; my[2 * e] = fb.x; my[2 * e + 1] = fb.y;
-        }
-    }
+__device__ __forceinline__ void emit_with(const float (&xv)[W], const float (&ry)[W], const float (&my)[W], int j, float* xs,
+                                          float& sx, float& sxmy, float& xmax) {
     float xp[W];
 #pragma unroll
     for (int e = 0; e < W; ++e) {
@@ -249,6 +296,54 @@ __device__ __forceinline__ void emit(const float (&xv)[W], const SProblem& P, in
     }
 #pragma unroll
     for (int e = 0; e < W; e += 4) *reinterpret_cast<float4*>(xs + j + e) = make_float4(xp[e], xp[e + 1], xp[e + 2], xp[e + 3]);
+}
+// The same for 8 activations held as four half2 (xv); ry, my as loaded.  A non-finite activation is caught
+// by the caller through the sum.
+__device__ __forceinline__ void emit_h8(const uint4& xv, const uint4& ryv, const uint4& myv, int j, float* xs,
+                                        float& sx, float& sxmy, float& xmax) {
+    const __half2* hx = reinterpret_cast<const __half2*>(&xv);
+    const __half2* hr = reinterpret_cast<const __half2*>(&ryv);
+    const __half2* hm = reinterpret_cast<const __half2*>(&myv);
+    float xp[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 x = __half22float2(hx[e]), r = __half22float2(hr[e]), m = __half22float2(hm[e]);
+        xp[2 * e] = x.x * r.x; xp[2 * e + 1] = x.y * r.y;
+        sx += x.x + x.y;
+        sxmy = fmaf(x.x, m.x, sxmy); sxmy = fmaf(x.y, m.y, sxmy);
+        xmax = fmaxf(xmax, fmaxf(fabsf(xp[2 * e]), fabsf(xp[2 * e + 1])));
+    }
+    *reinterpret_cast<float4*>(xs + j) = make_float4(xp[0], xp[1], xp[2], xp[3]);
+    *reinterpret_cast<float4*>(xs + j + 4) = make_float4(xp[4], xp[5], xp[6], xp[7]);
+}
+// token-shift mix of 8 LayerNorm outputs xx with the previous token's sv in fp16 arithmetic, one rounding per
+// operation as the reference's tensor ops have: mode 0 xx*mix + sv*(1-mix) (pkg/model.py:986, 1036-1038),
+// mode 1 xx + (sv-xx)*mix (pkg/model.py:1009-1011)
+__device__ __forceinline__ uint4 mix_h8(const uint4& xx, const uint4& sv, const uint4& mv, int mode) {
+    uint4 out;
+    const __half2* a = reinterpret_cast<const __half2*>(&xx);
+    const __half2* b = reinterpret_cast<const __half2*>(&sv);
+    const __half2* m = reinterpret_cast<const __half2*>(&mv);
+    __half2* o = reinterpret_cast<__half2*>(&out);
+    const __half2 one = __floats2half2_rn(1.0f, 1.0f);
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+        o[e] = mode == 0 ? __hadd2(__hmul2(a[e], m[e]), __hmul2(b[e], __hsub2(one, m[e])))
+                         : __hadd2(a[e], __hmul2(__hsub2(b[e], a[e]), m[e]));
+    return out;
+}
+// LayerNorm of 8 inputs: fp32 arithmetic, one rounding to fp16 at the end
+__device__ __forceinline__ uint4 ln_h8(const uint4& x, const uint4& lw, const uint4& lb, float mean, float rstd) {
+    float f[8], w[8], b[8], o[8];
+    h8_to_f(x, f); h8_to_f(lw, w); h8_to_f(lb, b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = (f[e] - mean) * rstd * w[e] + b[e];
+    return f_to_h8(o);
+}
+__device__ __forceinline__ void h4_to_f(const uint2& v, float (&f)[4]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) { const float2 t = __half22float2(h[e]); f[2 * e] = t.x; f[2 * e + 1] = t.y; }
 }
 
 // Ask L2 for this CTA's share of the lines of a vector that the NEXT phase reads right after the grid
@@ -288,6 +383,23 @@ mm8_stream_kernel(const STable* __restrict__ table, const uint8_t* __restrict__ 
         ctl->err = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // The table lives in global memory that the weight stream pushes out of L2 between uses: the producer's
+    // list of matrices and the first phase record go to shared memory now, later phase records one phase ahead.
+    const int n_segments = table->n_segments;
+    {
+        int k = 0;
+        for (int ph = 0; ph < n_phases; ++ph) {
+            const int count = phases[ph].count;
+            for (int z = 0; z < count; ++z, ++k) {
+                if ((k % kStreamThreads) == tid) {
+                    const Geom g = seg_geom_dev(phases[ph].p[z], cta);
+                    ctl->sched[k] = make_uint2((unsigned)g.cells, (unsigned)g.TA | ((unsigned)g.n_stages << 16));
+                }
+            }
+        }
+    }
+    for (int i = tid; i < int(sizeof(SPhase) / 16); i += kStreamThreads)
+        reinterpret_cast<uint4*>(&ctl->phase[0])[i] = __ldg(reinterpret_cast<const uint4*>(&phases[0]) + i);
     __syncthreads();
     volatile int* err = &ctl->err;
 
@@ -297,190 +409,225 @@ mm8_stream_kernel(const STable* __restrict__ table, const uint8_t* __restrict__ 
             const uint8_t* src = wstream + table->cta_base[cta];
             int slot = 0;
             uint32_t parity = 1;            // a fresh mbarrier passes a wait on parity 1: every slot starts empty
-            for (int ph = 0; ph < n_phases; ++ph) {
-                const int count = phases[ph].count;
-                for (int z = 0; z < count; ++z) {
-                    const Geom g = seg_geom(phases[ph].p[z].N, phases[ph].p[z].M, cta, G);
-                    const long long stage_bytes = (long long)g.kbs * g.kb_bytes;
-                    for (int s = 0; s < g.n_stages; ++s) {
-                        const long long left = g.bytes - s * stage_bytes;
-                        const uint32_t bytes = (uint32_t)(left < stage_bytes ? left : stage_bytes);
-                        mbar_wait(s2u(&ctl->empty[slot]), parity, err, gerr);
-                        mbar_expect_tx(s2u(&ctl->full[slot]), bytes);
-                        bulk_g2s(s2u(ring + (size_t)slot * kSlotBytes), src + s * stage_bytes, bytes, s2u(&ctl->full[slot]));
-                        if (++slot == n_slots) { slot = 0; parity ^= 1; }
-                    }
-                    src += g.bytes;
+            for (int k = 0; k < n_segments; ++k) {
+                const uint2 sc = ctl->sched[k];
+                const long long seg_bytes = (long long)sc.x * 16;
+                const long long stage_bytes = (long long)kIter * (sc.y & 0xffffu) * 16;
+                const int n_stages = int(sc.y >> 16);
+                for (int s = 0; s < n_stages; ++s) {
+                    const long long left = seg_bytes - s * stage_bytes;
+                    const uint32_t bytes = (uint32_t)(left < stage_bytes ? left : stage_bytes);
+                    mbar_wait(s2u(&ctl->empty[slot]), parity, err, gerr);
+                    mbar_expect_tx(s2u(&ctl->full[slot]), bytes);
+                    bulk_g2s(s2u(ring + (size_t)slot * kSlotBytes), src + s * stage_bytes, bytes, s2u(&ctl->full[slot]));
+                    if (++slot == n_slots) { slot = 0; parity ^= 1; }
                 }
+                src += seg_bytes;
             }
         }
         return;
     }
 
     // ================= consumers =================
-    const int gid = lane >> 2, tig = lane & 3;      // fragment coordinates of the lane
+    const int planes = table->planes;
+    int flip = 0;
     int slot = 0;
     uint32_t parity = 0;
     for (int ph = 0; ph < n_phases; ++ph) {
-        const SPhase& PH = phases[ph];
+        const SPhase& PH = ctl->phase[ph & 1];
         const int count = PH.count;
 
         // ---- prologue: every CTA builds the full quantised activation vector of each problem ----
-        uint4 lnx[2];
-        float mean = 0.f, rstd = 0.f;
+        // All global loads of a pass are issued before the first use, so that a pass costs one trip to L2.
         float xmax[4] = {0.f, 0.f, 0.f, 0.f};
-        lnx[0] = lnx[1] = make_uint4(0, 0, 0, 0);
+        if (PH.ln_shared) {
+            // LayerNorm + token-shift mixes of one residual vector for up to four matrices (r/k/v(/g), ffn r/k,
+            // head).  Thread t holds inputs [8 t, 8 t + 8) and, above 4096 inputs, [8 t + 4096, ...).
+            const SProblem& P0 = PH.p[0];
+            const int N = P0.N;
+            const bool mixes = P0.mode != 2;
+            uint4 lnx[2];
+            lnx[0] = lnx[1] = make_uint4(0, 0, 0, 0);
+            float sxz[4] = {0.f, 0.f, 0.f, 0.f}, smz[4] = {0.f, 0.f, 0.f, 0.f};
+            const float x0 = __half2float(__ldcg(static_cast<const __half*>(P0.x)));
+            // statistics in one pass, shifted by the first element so that a large mean does not cancel
+            float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-        for (int z = 0; z < kMaxPhaseProblems; ++z) {
-            if (z >= count) break;
-            const SProblem& P = PH.p[z];
-            const int N = P.N;
-            float* xs = reinterpret_cast<float*>(xq_base + P.xq_off);
-            float sx = 0.f, sxmy = 0.f, xm = 0.f;
-            if (P.prologue == RWKV_PRO_LN_MIX) {
-                if (!P.share_ln) {
-                    // LayerNorm statistics in one pass, shifted by the first element so that a large mean does
-                    // not cancel (N <= 8192: two 16-byte loads per thread)
-                    const float x0 = __half2float(__ldcg(static_cast<const __half*>(P.x)));
-                    float st[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int i = 0; i < 2; ++i) {
+                const int j8 = (tid + i * kConsumers) * 8;
+                if (j8 < N) {
+                    lnx[i] = ldcg16(P0.x, j8);
+                    float f[8];
+                    h8_to_f(lnx[i], f);
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const int j8 = (tid + i * kConsumers) * 8;
-                        if (j8 < N) {
-                            lnx[i] = ldcg16(P.x, j8);
-                            float f[8];
-                            h8_to_f(lnx[i], f);
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) { const float d = f[e] - x0; st[0] += d; st[1] = fmaf(d, d, st[1]); }
-                        }
-                    }
-                    cons_block_reduce4<true>(st, ctl->red, warp, lane);
-                    const float md = st[0] / float(N);
-                    mean = x0 + md;
-                    rstd = rsqrtf(fmaxf(st[1] / float(N) - md * md, 0.f) + 1e-5f);
-                }
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int j8 = (tid + i * kConsumers) * 8;
-                    if (j8 < N) {
-                        float f[8], lw[8], lb[8], xv[8];
-                        h8_to_f(lnx[i], f);
-                        h8_to_f(ldg16(P.p0, j8), lw);
-                        h8_to_f(ldg16(P.p1, j8), lb);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) xv[e] = r16((f[e] - mean) * rstd * lw[e] + lb[e]);
-                        if (P.q0 != nullptr && ((j8 >> 3) % G) == cta)
-                            *reinterpret_cast<uint4*>(static_cast<__half*>(P.q0) + j8) = f_to_h8(xv);
-                        if (P.mode != 2) {
-                            float sv[8], mv[8];
-                            h8_to_f(ldcg16(P.p2, j8), sv);
-                            h8_to_f(ldg16(P.p3, j8), mv);
-#pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                xv[e] = P.mode == 0 ? r16(r16(xv[e] * mv[e]) + r16(sv[e] * r16(1.0f - mv[e])))
-                                                    : r16(xv[e] + r16(r16(sv[e] - xv[e]) * mv[e]));
-                        }
-                        emit<8>(xv, P, j8, xs, sx, sxmy, xm);
-                    }
-                }
-            } else if (P.prologue == RWKV_PRO_WKV4) {       // pkg/model.py:1041-1055, four channels per thread and pass
-                for (int j = tid * 4; j < N; j += kConsumers * 4) {
-                    const uint2 r2 = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.x) + j));
-                    const uint2 k2 = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.p0) + j));
-                    const uint2 v2 = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.p1) + j));
-                    const float4 a4 = __ldcg(reinterpret_cast<const float4*>(P.f2 + j));
-                    const float4 b4 = __ldcg(reinterpret_cast<const float4*>(P.f3 + j));
-                    const float4 p4 = __ldcg(reinterpret_cast<const float4*>(P.f4 + j));
-                    const float4 d4 = __ldg(reinterpret_cast<const float4*>(P.f0 + j));
-                    const float4 f4 = __ldg(reinterpret_cast<const float4*>(P.f1 + j));
-                    const float aa[4] = {a4.x, a4.y, a4.z, a4.w}, bb[4] = {b4.x, b4.y, b4.z, b4.w}, pp[4] = {p4.x, p4.y, p4.z, p4.w};
-                    const float td[4] = {d4.x, d4.y, d4.z, d4.w}, tf[4] = {f4.x, f4.y, f4.z, f4.w};
-                    const __half* rh = reinterpret_cast<const __half*>(&r2);
-                    const __half* kh = reinterpret_cast<const __half*>(&k2);
-                    const __half* vh = reinterpret_cast<const __half*>(&v2);
-                    float xv[4], na[4], nb[4], np[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float kk = __half2float(kh[e]), vv = __half2float(vh[e]);
-                        float ww = tf[e] + kk;
-                        float p = fmaxf(pp[e], ww);
-                        float e1 = expf(pp[e] - p), e2 = expf(ww - p);
-                        const float wkv = r16((e1 * aa[e] + e2 * vv) / (e1 * bb[e] + e2));
-                        ww = td[e] + pp[e];
-                        p = fmaxf(ww, kk);
-                        e1 = expf(ww - p); e2 = expf(kk - p);
-                        na[e] = e1 * aa[e] + e2 * vv;
-                        nb[e] = e1 * bb[e] + e2;
-                        np[e] = p;
-                        xv[e] = r16(__half2float(rh[e]) * wkv);
-                    }
-                    if (((j >> 3) % G) == cta) {
-                        *reinterpret_cast<float4*>(P.g0 + j) = make_float4(na[0], na[1], na[2], na[3]);
-                        *reinterpret_cast<float4*>(P.g1 + j) = make_float4(nb[0], nb[1], nb[2], nb[3]);
-                        *reinterpret_cast<float4*>(P.g2 + j) = make_float4(np[0], np[1], np[2], np[3]);
-                    }
-                    emit<4>(xv, P, j, xs, sx, sxmy, xm);
-                }
-            } else {
-                for (int j8 = tid * 8; j8 < N; j8 += kConsumers * 8) {
-                    float xv[8];
-                    h8_to_f(ldcg16(P.x, j8), xv);
-                    emit<8>(xv, P, j8, xs, sx, sxmy, xm);
+                    for (int e = 0; e < 8; ++e) { const float d = f[e] - x0; s1 += d; s2 = fmaf(d, d, s2); }
                 }
             }
-            sx = warp_sum(sx); sxmy = warp_sum(sxmy);
-            if (lane == 0) { ctl->wsum[z][warp][0] = sx; ctl->wsum[z][warp][1] = sxmy; }
-            xmax[z] = xm;
+            cons_block_sum2(s1, s2, ctl->red, flip, warp, lane);
+            if (trace != nullptr && tid == 0 && cta < 2) trace[(ph * 2 + cta) * 16 + 4] = gtime();
+            const float md = s1 / float(N);
+            const float mean = x0 + md;
+            const float rstd = rsqrtf(fmaxf(s2 / float(N) - md * md, 0.f) + 1e-5f);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int j8 = (tid + i * kConsumers) * 8;
+                if (j8 < N) {
+                    const uint4 xx = ln_h8(lnx[i], ldg16(P0.p0, j8), ldg16(P0.p1, j8), mean, rstd);
+                    if (P0.q0 != nullptr && ((j8 >> 3) % G) == cta) *reinterpret_cast<uint4*>(static_cast<__half*>(P0.q0) + j8) = xx;
+                    uint4 sv = make_uint4(0, 0, 0, 0);
+                    if (mixes) sv = ldcg16(P0.p2, j8);
+#pragma unroll
+                    for (int z = 0; z < kMaxPhaseProblems; ++z) {
+                        if (z < count) {
+                            const SProblem& P = PH.p[z];
+                            const uint4 xv = mixes ? mix_h8(xx, sv, ldg16(P.p3, j8), P0.mode) : xx;
+                            emit_h8(xv, ldg16(P.ry, j8), ldg16(P.my, j8), j8, reinterpret_cast<float*>(xq_base + P.xq_off),
+                                    sxz[z], smz[z], xmax[z]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int z = 0; z < kMaxPhaseProblems; ++z) {
+                if (z < count) {
+                    if (!(fabsf(sxz[z]) <= 3.0e38f)) xmax[z] = __int_as_float(0x7f800000);   // an inf or NaN activation
+                    const float a1 = warp_sum(sxz[z]), a2 = warp_sum(smz[z]);
+                    if (lane == 0) { ctl->wsum[z][warp][0] = a1; ctl->wsum[z][warp][1] = a2; }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int z = 0; z < kMaxPhaseProblems; ++z) {
+                if (z >= count) break;
+                const SProblem& P = PH.p[z];
+                const int N = P.N;
+                float* xs = reinterpret_cast<float*>(xq_base + P.xq_off);
+                float sx = 0.f, sxmy = 0.f, xm = 0.f;
+                if (P.prologue == RWKV_PRO_WKV4) {           // pkg/model.py:1041-1055, four channels per thread and pass
+#pragma unroll 1
+                    for (int j = tid * 4; j < N; j += kConsumers * 4) {
+                        const uint2 r2 = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.x) + j));
+                        const uint2 k2 = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.p0) + j));
+                        const uint2 v2 = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.p1) + j));
+                        const float4 a4 = __ldcg(reinterpret_cast<const float4*>(P.f2 + j));
+                        const float4 b4 = __ldcg(reinterpret_cast<const float4*>(P.f3 + j));
+                        const float4 p4 = __ldcg(reinterpret_cast<const float4*>(P.f4 + j));
+                        const float4 d4 = __ldg(reinterpret_cast<const float4*>(P.f0 + j));
+                        const float4 f4 = __ldg(reinterpret_cast<const float4*>(P.f1 + j));
+                        const uint2 ry2 = __ldg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.ry) + j));
+                        const uint2 my2 = __ldg(reinterpret_cast<const uint2*>(static_cast<const __half*>(P.my) + j));
+                        const float aa[4] = {a4.x, a4.y, a4.z, a4.w}, bb[4] = {b4.x, b4.y, b4.z, b4.w}, pp[4] = {p4.x, p4.y, p4.z, p4.w};
+                        const float td[4] = {d4.x, d4.y, d4.z, d4.w}, tf[4] = {f4.x, f4.y, f4.z, f4.w};
+                        float rr[4], kk[4], vv[4], ry[4], my[4], xv[4], na[4], nb[4], np[4];
+                        h4_to_f(r2, rr); h4_to_f(k2, kk); h4_to_f(v2, vv); h4_to_f(ry2, ry); h4_to_f(my2, my);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float ww = tf[e] + kk[e];
+                            float p = fmaxf(pp[e], ww);
+                            float e1 = expf(pp[e] - p), e2 = expf(ww - p);
+                            const float wkv = r16((e1 * aa[e] + e2 * vv[e]) / (e1 * bb[e] + e2));
+                            ww = td[e] + pp[e];
+                            p = fmaxf(ww, kk[e]);
+                            e1 = expf(ww - p); e2 = expf(kk[e] - p);
+                            na[e] = e1 * aa[e] + e2 * vv[e];
+                            nb[e] = e1 * bb[e] + e2;
+                            np[e] = p;
+                            xv[e] = r16(rr[e] * wkv);
+                        }
+                        if (((j >> 3) % G) == cta) {
+                            *reinterpret_cast<float4*>(P.g0 + j) = make_float4(na[0], na[1], na[2], na[3]);
+                            *reinterpret_cast<float4*>(P.g1 + j) = make_float4(nb[0], nb[1], nb[2], nb[3]);
+                            *reinterpret_cast<float4*>(P.g2 + j) = make_float4(np[0], np[1], np[2], np[3]);
+                        }
+                        emit_with<4>(xv, ry, my, j, xs, sx, sxmy, xm);
+                    }
+                } else if (P.prologue == RWKV_PRO_LN_MIX) {   // a LayerNorm problem outside a shared phase: two passes over x
+                    float s1 = 0.f, s2 = 0.f;
+                    const float x0 = __half2float(__ldcg(static_cast<const __half*>(P.x)));
+                    for (int j8 = tid * 8; j8 < N; j8 += kConsumers * 8) {
+                        float f[8];
+                        h8_to_f(ldcg16(P.x, j8), f);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) { const float d = f[e] - x0; s1 += d; s2 = fmaf(d, d, s2); }
+                    }
+                    cons_block_sum2(s1, s2, ctl->red, flip, warp, lane);
+                    const float md = s1 / float(N), mean = x0 + md;
+                    const float rstd = rsqrtf(fmaxf(s2 / float(N) - md * md, 0.f) + 1e-5f);
+                    for (int j8 = tid * 8; j8 < N; j8 += kConsumers * 8) {
+                        uint4 xv = ln_h8(ldcg16(P.x, j8), ldg16(P.p0, j8), ldg16(P.p1, j8), mean, rstd);
+                        if (P.q0 != nullptr && ((j8 >> 3) % G) == cta) *reinterpret_cast<uint4*>(static_cast<__half*>(P.q0) + j8) = xv;
+                        if (P.mode != 2) xv = mix_h8(xv, ldcg16(P.p2, j8), ldg16(P.p3, j8), P.mode);
+                        emit_h8(xv, ldg16(P.ry, j8), ldg16(P.my, j8), j8, xs, sx, sxmy, xm);
+                    }
+                    if (!(fabsf(sx) <= 3.0e38f)) xm = __int_as_float(0x7f800000);
+                } else {
+#pragma unroll 4
+                    for (int j8 = tid * 8; j8 < N; j8 += kConsumers * 8)
+                        emit_h8(ldcg16(P.x, j8), ldg16(P.ry, j8), ldg16(P.my, j8), j8, xs, sx, sxmy, xm);
+                    if (!(fabsf(sx) <= 3.0e38f)) xm = __int_as_float(0x7f800000);
+                }
+                sx = warp_sum(sx); sxmy = warp_sum(sxmy);
+                if (lane == 0) { ctl->wsum[z][warp][0] = sx; ctl->wsum[z][warp][1] = sxmy; }
+                xmax[z] = xm;
+            }
         }
-        cons_block_reduce4<false>(xmax, ctl->red, warp, lane);       // also orders the x' stores before the reads below
-        // quantise in place.  The 16 fp32 x' of inputs [16 g, 16 g + 16) become 64 bytes of digits in the same
-        // place: plane n (the n-th signed base-256 digit) of those inputs at byte 16 n; two such groups are the
-        // k-block whose A fragments the lanes with gid < 4 read as words gid * 4 + tig (+ 16).
+        if (trace != nullptr && tid == 0 && cta < 2) trace[(ph * 2 + cta) * 16 + 5] = gtime();
+        cons_block_max4(xmax, ctl->red, flip, warp, lane);           // its barrier also orders the x' stores before the reads below
+        if (trace != nullptr && tid == 0 && cta < 2) trace[(ph * 2 + cta) * 16 + 6] = gtime();
+        // quantise in place: the 4 fp32 x' of a k-group become its 4 digit planes (word n = the n-th signed
+        // base-256 digit of the 4 inputs), which is what one dp4a multiplies with a column's 4 codes.
+        // q + 0x80808080 has the digits + 128 as its plain bytes; a 4 x 4 byte transpose makes the planes.
+        const float qmax = qmax_for(planes);
 #pragma unroll
         for (int z = 0; z < kMaxPhaseProblems; ++z) {
             if (z >= count) break;
             const SProblem& P = PH.p[z];
-            const int N = P.N, npad = ((N + 31) >> 5) << 5;
+            const int N = P.N, npad = (((N + 3) >> 2) + 31 & ~31) << 2;
             float* xs = reinterpret_cast<float*>(xq_base + P.xq_off);
             const float m = xmax[z];
             const bool finite = m < 3.0e38f;
-            const float scale = (finite && m > 0.f) ? kQMax / m : 0.f;
-            if (tid == 0) ctl->inv_scale[z] = !finite ? __int_as_float(0x7fc00000) : (m > 0.f ? m / kQMax : 0.f);
+            const float scale = (finite && m > 0.f) ? qmax / m : 0.f;
+            if (tid == 0) ctl->inv_scale[z] = !finite ? __int_as_float(0x7fc00000) : (m > 0.f ? m / qmax : 0.f);
             long long sq = 0;
-            for (int j0 = 0; j0 < npad; j0 += kConsumers * 4) {     // whole warps iterate together (npad % 32 == 0)
-                const int j = j0 + tid * 4;
-                uint32_t plane[4] = {0u, 0u, 0u, 0u};
+#pragma unroll 2
+            for (int j = tid * 4; j < npad; j += kConsumers * 4) {
+                uint4 planes4 = make_uint4(0u, 0u, 0u, 0u);
                 if (j < N) {                                        // N % 8 == 0: a group of four is inside or outside
                     const float4 v = *reinterpret_cast<const float4*>(xs + j);
-                    const float f[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        int q = __float2int_rn(f[e] * scale);
-                        sq += q;
-#pragma unroll
-                        for (int n = 0; n < 4; ++n) {
-                            const int d = (int)(signed char)(q & 0xff);
-                            plane[n] |= uint32_t(d & 0xff) << (8 * e);
-                            q = (q - d) >> 8;
-                        }
-                    }
+                    const int q0 = __float2int_rn(v.x * scale), q1 = __float2int_rn(v.y * scale);
+                    const int q2 = __float2int_rn(v.z * scale), q3 = __float2int_rn(v.w * scale);
+                    sq += (long long)q0 + q1 + q2 + q3;
+                    const uint32_t u0 = (uint32_t(q0) + 0x80808080u) ^ 0x80808080u, u1 = (uint32_t(q1) + 0x80808080u) ^ 0x80808080u;
+                    const uint32_t u2 = (uint32_t(q2) + 0x80808080u) ^ 0x80808080u, u3 = (uint32_t(q3) + 0x80808080u) ^ 0x80808080u;
+                    const uint32_t t0 = __byte_perm(u0, u1, 0x5140), t1 = __byte_perm(u2, u3, 0x5140);
+                    const uint32_t t2 = __byte_perm(u0, u1, 0x7362), t3 = __byte_perm(u2, u3, 0x7362);
+                    planes4 = make_uint4(__byte_perm(t0, t1, 0x5410), __byte_perm(t0, t1, 0x7632),
+                                         __byte_perm(t2, t3, 0x5410), __byte_perm(t2, t3, 0x7632));
                 }
-                __syncwarp();                                       // the group's floats are read before its digits land
-                if (j < npad) {
-                    uint32_t* dst = reinterpret_cast<uint32_t*>(xs) + (j >> 4) * 16 + ((j & 15) >> 2);
-#pragma unroll
-                    for (int n = 0; n < 4; ++n) dst[n * 4] = plane[n];
-                }
+                *reinterpret_cast<uint4*>(xs + j) = planes4;
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
             if (lane == 0) ctl->wsumq[z][warp] = sq;
         }
         cons_sync();
-        if (trace != nullptr && tid == 0 && cta < 2) trace[(ph * 2 + cta) * 4 + 2] = gtime();
+        if (warp < count) {             // warp z adds the 16 per-warp sums of problem z (fixed tree: same bits in every CTA)
+            float a1 = lane < kConsWarps ? ctl->wsum[warp][lane][0] : 0.f, a2 = lane < kConsWarps ? ctl->wsum[warp][lane][1] : 0.f;
+            long long aq = lane < kConsWarps ? ctl->wsumq[warp][lane] : 0ll;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) {
+                a1 += __shfl_xor_sync(0xffffffffu, a1, o); a2 += __shfl_xor_sync(0xffffffffu, a2, o);
+                aq += __shfl_xor_sync(0xffffffffu, aq, o);
+            }
+            if (lane == 0) { ctl->tot_x[warp] = a1; ctl->tot_xmy[warp] = a2; ctl->tot_q[warp] = aq; }
+        }
+        if (trace != nullptr && tid == 0 && cta < 2) trace[(ph * 2 + cta) * 16 + 2] = gtime();
 
         // what the next phase reads right after the barrier and nobody writes in this phase
         if (ph + 1 < n_phases) {
+            // the next phase's record, for after the barrier (its buffer was last read in phase ph - 1)
+            for (int i = tid; i < int(sizeof(SPhase) / 16); i += kConsumers)
+                reinterpret_cast<uint4*>(&ctl->phase[(ph + 1) & 1])[i] = __ldg(reinterpret_cast<const uint4*>(&phases[ph + 1]) + i);
             const SPhase& NX = phases[ph + 1];
             for (int z = 0; z < NX.count; ++z) {
                 const SProblem& P = NX.p[z];
@@ -500,80 +647,91 @@ mm8_stream_kernel(const STable* __restrict__ table, const uint8_t* __restrict__ 
         // ---- the matrices of the phase, one after the other ----
         for (int z = 0; z < count; ++z) {
             const SProblem& P = PH.p[z];
-            const Geom g = seg_geom(P.N, P.M, cta, G);
-            const uint32_t* xq = reinterpret_cast<const uint32_t*>(xq_base + P.xq_off);
+            const Geom g = seg_geom_dev(P, cta);
+            const bool tr = trace != nullptr && tid == 0 && cta < 2 && z == 0;
+            if (tr) trace[(ph * 2 + cta) * 16 + 8] = gtime();
             // the epilogue's operands, on their way while the matrix streams
             const int kcol = (g.u0 << 2) + tid;
             const bool fin = tid < 4 * g.Q && kcol < P.M;
             float rxk = 0.f, mxk = 0.f, auxv = 0.f, aux2v = 0.f;
+            // (volatile loads: issued here, not where the values are used after the last stage)
+            unsigned short h_rx = 0, h_mx = 0, h_aux = 0, h_aux2 = 0;
             if (fin) {
-                rxk = __half2float(__ldg(static_cast<const __half*>(P.rx) + kcol));
-                mxk = __half2float(__ldg(static_cast<const __half*>(P.mx) + kcol));
-                if (P.epilogue == RWKV_EPI_RESIDUAL || P.epilogue == RWKV_EPI_MUL_RESIDUAL)
-                    auxv = __half2float(__ldcg(static_cast<const __half*>(P.aux) + kcol));
-                if (P.epilogue == RWKV_EPI_MUL_RESIDUAL) aux2v = __half2float(__ldcg(static_cast<const __half*>(P.aux2) + kcol));
-                if (P.epilogue == RWKV_EPI_ACC_F32) auxv = __ldcg(static_cast<const float*>(P.y) + kcol);
+                h_rx = ld_cg_u16(static_cast<const __half*>(P.rx) + kcol);
+                h_mx = ld_cg_u16(static_cast<const __half*>(P.mx) + kcol);
+                if (P.epilogue == RWKV_EPI_RESIDUAL || P.epilogue == RWKV_EPI_MUL_RESIDUAL) h_aux = ld_cg_u16(static_cast<const __half*>(P.aux) + kcol);
+                if (P.epilogue == RWKV_EPI_MUL_RESIDUAL) h_aux2 = ld_cg_u16(static_cast<const __half*>(P.aux2) + kcol);
+                if (P.epilogue == RWKV_EPI_ACC_F32) auxv = ld_cg_f32(static_cast<const float*>(P.y) + kcol);
             }
-            const int og = warp % g.wo, ks = warp / g.wo;
-            const int o_first = og * g.opw;
-            const int my_oct = max(0, min(g.opw, g.n_oct - o_first));
-            const bool half_last = (g.Q & 1) != 0;                  // the CTA's last octet holds four columns
-            int acc[kMaxOct][2];
+            const uint4* xq = reinterpret_cast<const uint4*>(xq_base + P.xq_off);
+            const int sub = tid / g.SG, lane_in = tid % g.SG;
+            const bool active = tid < g.TA;
+            const int gg = active ? (sub / g.Q) * g.SG + lane_in : 0;      // this thread's k-group within an iteration
+            int acc[4][4];                                                  // [column][digit]
 #pragma unroll
-            for (int o = 0; o < kMaxOct; ++o) acc[o][0] = acc[o][1] = 0;
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int n = 0; n < 4; ++n) acc[c][n] = 0;
+            const int n_full = g.TA > 0 ? g.cells / (kIter * g.TA) : 0;    // stages in which every active thread has kIter cells
+            const uint4* xp = xq + gg;
             for (int s = 0; s < g.n_stages; ++s) {
                 mbar_wait(s2u(&ctl->full[slot]), parity, err, gerr);
-                const uint8_t* sp = ring + (size_t)slot * kSlotBytes;
-                const int kb0 = s * g.kbs;
-                const int nkb = min(g.kbs, g.n_kb - kb0);
-                int kl = (ks - kb0 % g.wk + g.wk) % g.wk;          // first k-block of the stage that is this warp's
-                for (; kl < nkb; kl += g.wk) {
-                    const int kb = kb0 + kl;
-                    uint32_t a0 = 0u, a2 = 0u;
-                    if (gid < 4) { a0 = xq[kb * 32 + gid * 4 + tig]; a2 = xq[kb * 32 + 16 + gid * 4 + tig]; }
-                    const uint2* cells = reinterpret_cast<const uint2*>(sp + (size_t)kl * g.kb_bytes) + o_first * 32 + lane;
+                if (tr && s == 0) trace[(ph * 2 + cta) * 16 + 9] = gtime();
+                const uint4* sp = reinterpret_cast<const uint4*>(ring + (size_t)slot * kSlotBytes) + tid;
+                uint4 w[kIter], xv[kIter];
+                if (s < n_full) {
+                    if (active) {
 #pragma unroll
-                    for (int o = 0; o < kMaxOct; ++o) {
-                        if (o < my_oct) {
-                            const bool whole = !(half_last && o_first + o == g.n_oct - 1);
-                            uint2 b = make_uint2(0u, 0u);
-                            if (whole || lane < 16) b = cells[o * 32];
-                            imma_16832(acc[o][0], acc[o][1], a0, a2, b.x, b.y);
-                        }
+                        for (int r = 0; r < kIter; ++r) { w[r] = sp[r * g.TA]; xv[r] = xp[r * g.GPI]; }
                     }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < kIter; ++r) {
+                        const bool ok = active && (s * kIter + r) * g.TA + tid < g.cells;
+                        w[r] = ok ? sp[r * g.TA] : make_uint4(0, 0, 0, 0);
+                        xv[r] = ok ? xp[r * g.GPI] : make_uint4(0, 0, 0, 0);
+                    }
+                }
+                xp += kIter * g.GPI;
+                if (active) {
+                    if (planes >= 4) stage_math<4>(acc, w, xv);
+                    else if (planes == 3) stage_math<3>(acc, w, xv);
+                    else stage_math<2>(acc, w, xv);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s2u(&ctl->empty[slot]));
                 if (++slot == n_slots) { slot = 0; parity ^= 1; }
             }
-            // lane (gid < 4, tig) holds digit gid of columns 2 tig, 2 tig + 1 of each of its octets: weigh the
-            // digits, add them over gid (lanes 4 and 8 apart), then the K groups of warps through shared memory
-            cons_sync();                    // the previous matrix's partial sums have been read
+            // this thread's exact sums for its four columns; add the lanes of the subgroup, then the
+            // subgroups of a quad through shared memory
+            long long S[4];
 #pragma unroll
-            for (int o = 0; o < kMaxOct; ++o) {
-                if (o < my_oct) {
-                    long long v0 = gid < 4 ? (long long)acc[o][0] << (8 * gid) : 0ll;
-                    long long v1 = gid < 4 ? (long long)acc[o][1] << (8 * gid) : 0ll;
-                    v0 += __shfl_xor_sync(0xffffffffu, v0, 4); v1 += __shfl_xor_sync(0xffffffffu, v1, 4);
-                    v0 += __shfl_xor_sync(0xffffffffu, v0, 8); v1 += __shfl_xor_sync(0xffffffffu, v1, 8);
-                    if (gid == 0) {
-                        red[(warp * kMaxOct + o) * 8 + 2 * tig] = v0;
-                        red[(warp * kMaxOct + o) * 8 + 2 * tig + 1] = v1;
-                    }
-                }
+            for (int c = 0; c < 4; ++c)
+                S[c] = (long long)acc[c][0] + ((long long)acc[c][1] << 8) + ((long long)acc[c][2] << 16) + ((long long)acc[c][3] << 24);
+            for (int o = g.SG >> 1; o > 0; o >>= 1) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) S[c] += __shfl_xor_sync(0xffffffffu, S[c], o);
+            }
+            if (tr) trace[(ph * 2 + cta) * 16 + 10] = gtime();
+            cons_sync();                    // the previous matrix's partial sums have been read
+            if (tr) trace[(ph * 2 + cta) * 16 + 11] = gtime();
+            if (active && lane_in == 0) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) red[sub * 4 + c] = S[c];
             }
             cons_sync();
+            if (tr) trace[(ph * 2 + cta) * 16 + 12] = gtime();
             if (fin) {
-                const int oc = tid >> 3, ogf = oc / g.opw, ol = oc - ogf * g.opw;
+                rxk = __half2float(__ushort_as_half(h_rx));
+                mxk = __half2float(__ushort_as_half(h_mx));
+                if (P.epilogue == RWKV_EPI_RESIDUAL || P.epilogue == RWKV_EPI_MUL_RESIDUAL) auxv = __half2float(__ushort_as_half(h_aux));
+                aux2v = __half2float(__ushort_as_half(h_aux2));
+                const int qq = tid >> 2, i = tid & 3;
+                const int nrep = g.GPI / g.SG;
                 long long tot = 0;
-                for (int k2 = 0; k2 < g.wk; ++k2) tot += red[((k2 * g.wo + ogf) * kMaxOct + ol) * 8 + (tid & 7)];
-                float tx = 0.f, txmy = 0.f;
-                long long sq = 0;
-#pragma unroll
-                for (int w8 = 0; w8 < kConsWarps; ++w8) {
-                    tx += ctl->wsum[z][w8][0]; txmy += ctl->wsum[z][w8][1];
-                    sq += ctl->wsumq[z][w8];
-                }
+                for (int rep = 0; rep < nrep; ++rep) tot += red[(rep * g.Q + qq) * 4 + i];
+                const float tx = ctl->tot_x[z], txmy = ctl->tot_xmy[z];
+                const long long sq = ctl->tot_q[z];
                 // sum_j x'_j (w_jk + 1/2) = inv_scale * (sum q w + sum q / 2): one exact integer, no cancellation
                 const float sdot = __ll2float_rn(2 * tot + sq) * (0.5f * ctl->inv_scale[z]);
                 const float val = fmaf(rxk, sdot, fmaf(mxk, tx, txmy));
@@ -592,15 +750,14 @@ mm8_stream_kernel(const STable* __restrict__ table, const uint8_t* __restrict__ 
                 }
             }
         }
-        if (trace != nullptr && tid == 0 && cta < 2) trace[(ph * 2 + cta) * 4 + 3] = gtime();
+        if (trace != nullptr && tid == 0 && cta < 2) trace[(ph * 2 + cta) * 16 + 3] = gtime();
 
         // ---- grid barrier: the phase's results are complete and visible before anyone reads them ----
         if (ph + 1 < n_phases) {
             cons_sync();
             if (tid == 0) {
-                __threadfence();
-                atomicAdd(gbar, 1u);
-                if (trace != nullptr && cta < 2) trace[(ph * 2 + cta) * 4 + 0] = gtime();
+                asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(gbar) : "memory");
+                if (trace != nullptr && cta < 2) trace[(ph * 2 + cta) * 16 + 0] = gtime();
                 const unsigned target = unsigned(G) * unsigned(ph + 1);
                 const unsigned long long t0 = gtime();
                 for (unsigned it = 0;; ++it) {
@@ -613,7 +770,7 @@ mm8_stream_kernel(const STable* __restrict__ table, const uint8_t* __restrict__ 
                         break;
                     }
                 }
-                if (trace != nullptr && cta < 2) trace[(ph * 2 + cta) * 4 + 1] = gtime();
+                if (trace != nullptr && cta < 2) trace[(ph * 2 + cta) * 16 + 1] = gtime();
             }
             cons_sync();
         }
@@ -630,32 +787,31 @@ struct PackArgs {
     long long off[kMaxCtas];        // where this matrix's segment starts in the stream, per CTA
 };
 
-// One thread per 8-byte cell: k-block kb, octet o, lane -> the B fragment of that lane, i.e. column
-// 8 o + lane / 4 of the CTA, input rows 32 kb + 4 (lane % 4) + {0..3} and the same 16 rows further.
+// One thread per 16-byte cell.
 __global__ void mm8_stream_pack_kernel(PackArgs a, uint8_t* wstream) {
     const int cta = blockIdx.y;
     const Geom g = seg_geom(a.N, a.M, cta, a.G);
     if (g.Q == 0) return;
-    uint2* dst = reinterpret_cast<uint2*>(wstream + a.off[cta]);
-    const int per_kb = 16 * g.Q;
-    const long long cells = (long long)g.n_kb * per_kb;
-    for (long long cell = blockIdx.x * (long long)blockDim.x + threadIdx.x; cell < cells; cell += (long long)gridDim.x * blockDim.x) {
-        const int kb = int(cell / per_kb), rem = int(cell - (long long)kb * per_kb);
-        const int o = rem >> 5, lane = rem & 31;
-        const int col = (g.u0 << 2) + 8 * o + (lane >> 2);
-        const int r0 = 32 * kb + 4 * (lane & 3);
-        uint32_t b[2] = {0u, 0u};
+    uint4* dst = reinterpret_cast<uint4*>(wstream + a.off[cta]);
+    for (int cell = blockIdx.x * blockDim.x + threadIdx.x; cell < g.cells; cell += gridDim.x * blockDim.x) {
+        const int it = cell / g.TA, t = cell - it * g.TA;
+        const int sub = t / g.SG, lane_in = t % g.SG;
+        const int q = sub % g.Q, gg = (sub / g.Q) * g.SG + lane_in;
+        const int r0 = 4 * (it * g.GPI + gg), c0 = (g.u0 + q) * 4;
+        uint32_t wc[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const int row = r0 + 16 * h + i;
-                if (row < a.N && col < a.M) b[h] |= uint32_t(a.w[(long long)row * a.w_stride + col]) << (8 * i);
+                const int row = r0 + i, col = c0 + c;
+                if (row < a.N && col < a.M) wc[c] |= uint32_t(a.w[(long long)row * a.w_stride + col]) << (8 * i);
             }
         }
-        dst[cell] = make_uint2(b[0], b[1]);
+        dst[cell] = make_uint4(wc[0], wc[1], wc[2], wc[3]);
     }
 }
+
+int g_stream_planes = 4;     // digit planes tables are planned with (process-wide tuning hook)
 
 int stream_ctas() {
     int dev = 0, sms = 0;
@@ -668,14 +824,15 @@ int stream_ctas() {
 
 bool stream_supported(const rwkv_mm8_problem& q, int G) {
     if (q.N < 8 || q.N % 8 != 0 || q.M < 1) return false;
-    if (((q.M + 3) / 4 + G - 1) / G > kSlotBytes / 128) return false;
-    if (q.prologue == RWKV_PRO_LN_MIX && q.N > 2 * kConsumers * 8) return false;
+    if (((q.M + 3) / 4 + G - 1) / G > kConsumers / 4) return false;
     return true;
 }
 
 }  // namespace
 
 extern "C" int rwkv_mm8_stream_ctas(void) { return stream_ctas(); }
+
+extern "C" void rwkv_mm8_stream_set_planes(int planes) { g_stream_planes = planes < 2 ? 2 : planes > 4 ? 4 : planes; }
 
 extern "C" size_t rwkv_mm8_stream_weight_bytes(const rwkv_mm8_problem* problems, int n_problems, int n_ctas) {
     if (problems == nullptr || n_problems < 1 || n_ctas < 1 || n_ctas > kMaxCtas) return 0;
@@ -708,7 +865,7 @@ extern "C" int rwkv_mm8_stream_pack(const rwkv_mm8_problem* problems, int n_prob
             const Geom g = seg_geom(q.N, q.M, c, n_ctas);
             a.off[c] = base[c] + run[c];
             run[c] += g.bytes;
-            if (g.bytes / 8 > max_cells) max_cells = g.bytes / 8;
+            if (g.cells > max_cells) max_cells = g.cells;
         }
         if (max_cells == 0) continue;
         const int bx = (max_cells + 255) / 256 > 64 ? 64 : int((max_cells + 255) / 256);
@@ -734,6 +891,13 @@ extern "C" int rwkv_mm8_stream_plan(const rwkv_mm8_problem* problems, const int3
     SPhase* PH = reinterpret_cast<SPhase*>(T + 1);
     T->n_phases = n_phases;
     T->n_ctas = n_ctas;
+    T->planes = g_stream_planes;
+    {
+        int total = 0;
+        for (int ph = 0; ph < n_phases; ++ph) total += counts[ph];
+        if (total > kMaxSegments) return RWKV_ERR_UNSUPPORTED;
+        T->n_segments = total;
+    }
     int xq_max = 0, idx = 0, n_total = 0;
     for (int ph = 0; ph < n_phases; ++ph) {
         RWKV_CHECK_ARG(counts[ph] >= 1 && counts[ph] <= kMaxPhaseProblems);
@@ -768,9 +932,26 @@ extern "C" int rwkv_mm8_stream_plan(const rwkv_mm8_problem* problems, const int3
                 P.p0 = q.k; P.p1 = q.v; P.f0 = q.t_decay; P.f1 = q.t_first; P.f2 = q.aa; P.f3 = q.bb; P.f4 = q.pp;
                 P.g0 = q.aa_out; P.g1 = q.bb_out; P.g2 = q.pp_out;
             }
+            {
+                const int U = (q.M + 3) >> 2;
+                P.base = U / n_ctas; P.rem = U % n_ctas;
+                for (int v = 0; v < 2; ++v) {
+                    // a CTA index that owns base + v quads (any one: the layout depends on the quad count only)
+                    const int c = v ? 0 : n_ctas - 1;
+                    const Geom gg = seg_geom(q.N, q.M, c, n_ctas);
+                    const bool ok = gg.Q == P.base + v;
+                    P.gSG[v] = ok ? gg.SG : 4; P.gGPI[v] = ok ? gg.GPI : 0; P.gTA[v] = ok ? gg.TA : 0;
+                    P.gcells[v] = ok ? gg.cells : 0; P.gstages[v] = ok ? gg.n_stages : 0;
+                }
+            }
             P.xq_off = off;
-            off += ((q.N + 31) >> 5) * 128;        // 4 bytes per input, whole k-blocks of 32
+            off += ((((q.N + 3) >> 2) + 31) & ~31) * 16;       // 4 bytes per input; k-groups padded to 32 so that tails read zeros
         }
+        bool shared = PH[ph].p[0].prologue == RWKV_PRO_LN_MIX && PH[ph].p[0].N <= 2 * kConsumers * 8;
+        for (int z = 1; z < counts[ph] && shared; ++z)
+            shared = PH[ph].p[z].prologue == RWKV_PRO_LN_MIX && PH[ph].p[z].share_ln && PH[ph].p[z].mode == PH[ph].p[0].mode &&
+                     PH[ph].p[z].p2 == PH[ph].p[0].p2 && PH[ph].p[z].q0 == nullptr;
+        PH[ph].ln_shared = shared ? 1 : 0;
         if (off > xq_max) xq_max = off;
         n_total += counts[ph];
     }

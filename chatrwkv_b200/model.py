@@ -11,8 +11,10 @@ and the tensor names in `.w`.  What differs, by design:
   * the loader packs on the GPU (ops.quantize_weight) and keeps `emb.weight` on the GPU;
   * packed matrices have a row stride padded to 16 bytes (their shape is unchanged);
   * a one-token `forward` is a single CUDA-graph replay of fused kernels; the state tensors
-    it returns are persistent buffers that are updated in place by the next call (pass
-    `copy.deepcopy(state)` around to keep a snapshot, as the reference's callers do).
+    it returns are persistent buffers that are updated in place by later calls (pass
+    `copy.deepcopy(state)` around to keep a snapshot, as the reference's callers do).  Passing
+    back a list whose tensors have been reused in between raises instead of computing on the
+    wrong state; RWKV_B200_COPY_STATE=1 returns fresh tensors from every call instead.
 
 `model` may also be a checkpoint dict instead of a file name.
 """
@@ -40,6 +42,17 @@ def _ptr_array(tensors):
     for i, t in enumerate(tensors):
         arr[i] = t.data_ptr()
     return arr
+
+
+class _StateList(list):
+    """The state list a one-token `forward` returns: the runtime's persistent buffers (see the module
+    docstring), stamped with the step that wrote them so that a stale list is recognised."""
+    owner = None
+    step = -1
+
+    def __deepcopy__(self, memo):
+        import copy
+        return [copy.deepcopy(t, memo) for t in self]      # a snapshot: plain list, own tensors
 
 
 class RWKV:
@@ -277,22 +290,22 @@ class RWKV:
         # reads), then the roles swap.  One captured graph per direction.
         self._st = None
         self._cur = 0
+        self._steps = 0
+        # RWKV_B200_COPY_STATE=1: every one-token forward returns fresh state tensors (as the reference does) instead
+        # of the persistent buffers; ~160 small copies per token at the 7B shape
+        self._copy_state = os.environ.get("RWKV_B200_COPY_STATE", "0") == "1"
         self._graphs = [None, None]
         self._locbuf = {}
-        self._chain = [None, None]      # per direction: (device launch table, n_launches, n_ctas)
-        self._head_launch = [None, None]
-        # RWKV_B200_CHAIN=1: run the layers of a token as one persistent cooperative kernel
-        # (csrc/mm8_chain.cu) instead of four launches per layer.  Both reach the same speed on a
-        # B200; the launch-per-matmul path is the default because it contains no wait loop.
-        self._use_chain = os.environ.get("RWKV_B200_CHAIN", "0") == "1"
-        # RWKV-4 decode default: the whole token as ONE persistent kernel over a re-tiled copy of the
-        # packed matrices (csrc/mm8_stream.cu); RWKV_B200_STREAM=0 or RWKV_B200_EXACT=1 keep the launch per
-        # matmul.  Costs a second copy of the codes in HBM (the row-major one still serves prefill).
-        self._use_stream = (self.version == 4 and self._world == 1 and not self._use_chain and
-                            os.environ.get("RWKV_B200_STREAM", "1") != "0" and
-                            os.environ.get("RWKV_B200_EXACT", "0") != "1")
+        # RWKV_B200_STREAM=1 (or set_decode_path("stream")): RWKV-4 decode as ONE persistent kernel per token over
+        # a re-tiled copy of the packed matrices (csrc/mm8_stream.cu) instead of a launch per group of matmuls.
+        # Costs a second copy of the codes in HBM (the row-major one still serves prefill); measured slower than
+        # the launches at the 7B shape, so it is not the default.
+        self._use_stream = (self.version == 4 and self._world == 1 and
+                            os.environ.get("RWKV_B200_STREAM", "0") == "1")
         self._stream = None
         self._mm = {}
+        # a matrix with more than 16384 in-features needs the decode kernel's second build: ask for it on every launch
+        self._gemv_flags = _lib.MM8_WIDE_BUILD if max(a.n_ffn, a.n_att, a.n_embd) > 16384 else 0
 
     def _scales(self, name):
         e = self._mm.get(name)
@@ -307,7 +320,7 @@ class RWKV:
         return ops.make_problem(x, wq, mx, rx, my, ry, y, epi, aux, aux2, out_scale)
 
     def _gemv(self, problems, exchange=None):
-        ops.mm8_one_batch(problems, torch.float16, self.device, self._ws, exchange)
+        ops.mm8_one_batch(problems, torch.float16, self.device, self._ws, exchange, self._gemv_flags)
 
     def _ln_mix(self, T, x, sx, ln_w, ln_b, mode, mixes, outs, xx_out=None, new_state=None, mix_stride=0):
         D = self.args.n_embd
@@ -367,8 +380,19 @@ class RWKV:
             return
         g = self._st[self._cur]
         if len(g) == len(state) and all(a is b for a, b in zip(g, state)):
+            if isinstance(state, _StateList) and state.owner is self and state.step != self._steps:
+                self._stale(state)
             return
+        other = self._st[1 - self._cur]
+        if len(other) == len(state) and len(state) > 0 and state[0] is other[0]:
+            self._stale(state)
         torch._foreach_copy_(g, [s for s in state])
+
+    def _stale(self, state):
+        raise _lib.RwkvB200Error(
+            "this state list was returned by an earlier one-token forward() of this model and its tensors have been "
+            "reused since (they are the runtime's persistent buffers): keep snapshots with copy.deepcopy(state), or set "
+            "RWKV_B200_COPY_STATE=1 to get fresh tensors from every call")
 
     def _forward_one(self, token, state):
         self._bind_state(state)
@@ -415,7 +439,12 @@ class RWKV:
         else:
             self._graphs[cur].replay()
         self._cur = 1 - cur
-        return self._b.logits.clone(), list(self._st[self._cur])
+        self._steps += 1
+        if self._copy_state:
+            return self._b.logits.clone(), [t.clone() for t in self._st[self._cur]]
+        out = _StateList(self._st[self._cur])
+        out.owner, out.step = self, self._steps
+        return self._b.logits.clone(), out
 
     def _launches_v4(self, cur):
         """The GEMV launches of one RWKV-4 token, in order: four per layer plus the head, with
@@ -443,21 +472,6 @@ class RWKV:
             launches.append([P(b.fk, ffn + "value.weight", b.x, EPI_MUL_RESIDUAL, aux=b.x, aux2=b.fr, out_scale=scale)])
         launches.append([ln(P(b.x, "head.weight", b.logits, EPI_STORE_F32), w["ln_out.weight"], w["ln_out.bias"], 2)])
         return launches
-
-    def _build_chain(self, cur):
-        """Lay the layers' launches out for the persistent chain kernel (once per direction).
-        The head (one wide matmul) stays a launch of its own."""
-        import ctypes as C
-        launches = self._launches_v4(cur)[:-1]
-        flat = [p for probs in launches for p in probs]
-        arr = (_lib.Mm8Problem * len(flat))(*flat)
-        counts = (C.c_int32 * len(launches))(*[len(p) for p in launches])
-        n_ctas = lib().rwkv_mm8_chain_ctas()
-        nbytes = lib().rwkv_mm8_chain_table_bytes(len(launches), n_ctas)
-        host = torch.zeros(nbytes, dtype=torch.uint8)
-        check(lib().rwkv_mm8_chain_plan(arr, counts, len(launches), _lib.F16, n_ctas, self._ws.data_ptr(),
-                                        self._ws.numel(), host.data_ptr(), nbytes), "mm8_chain_plan")
-        self._chain[cur] = (host.to(self.device), len(launches), n_ctas)
 
     def _step_one_v4_sharded(self, cur):
         """One RWKV-4 token with every matmul split by output columns over the ranks: the same
@@ -591,18 +605,15 @@ class RWKV:
         return True
 
     def decode_path(self):
-        """Which kernels a one-token forward runs: 'stream' (RWKV-4: one persistent kernel), 'chain', or 'launch'
-        (a launch per group of matmuls)."""
-        if self.version == 4 and self._world == 1 and self._use_stream:
-            return "stream"
-        return "chain" if (self.version == 4 and self._use_chain) else "launch"
+        """Which kernels a one-token forward runs: 'stream' (RWKV-4: one persistent kernel) or 'launch' (a launch
+        per group of matmuls)."""
+        return "stream" if (self.version == 4 and self._world == 1 and self._use_stream) else "launch"
 
     def set_decode_path(self, path):
         """Switch RWKV-4 decode between 'stream' and 'launch'; captured graphs are dropped."""
         if path not in ("stream", "launch"):
             raise ValueError(path)
         self._use_stream = path == "stream" and self.version == 4 and self._world == 1
-        self._use_chain = False
         self._graphs = [None, None]
 
     def launches_per_token(self):
@@ -610,7 +621,7 @@ class RWKV:
         L = self.args.n_layer
         if self.version != 4:
             return L * (5 if self.version == 5.2 else 6) + 1
-        return {"stream": 1, "chain": 2}.get(self.decode_path(), 4 * L + 1)
+        return 1 if self.decode_path() == "stream" else 4 * L + 1
 
     def stream_error(self):
         """1 if a wait inside the persistent decode kernel gave up since the last call (the step's results were
@@ -634,31 +645,11 @@ class RWKV:
             check(lib().rwkv_mm8_stream_run(dev.data_ptr(), host.data_ptr(), st.wstream.data_ptr(), st.sync.data_ptr(),
                                             st.trace.data_ptr() if st.trace is not None else None,
                                             torch.cuda.current_stream(self.device).cuda_stream), "mm8_stream_run")
-        elif self._use_chain:
-            if self._chain[cur] is None:
-                self._build_chain(cur)
-            table, n, n_ctas = self._chain[cur]
-            trace = getattr(self, "_trace", None)
-            check(lib().rwkv_mm8_chain_run(table.data_ptr(), n, n_ctas, self._ws.data_ptr(),
-                                           trace.data_ptr() if trace is not None else None,
-                                           torch.cuda.current_stream(self.device).cuda_stream), "mm8_chain_run")
-            if self._head_launch[cur] is None:
-                self._head_launch[cur] = self._launches_v4(cur)[-1]
-            self._gemv(self._head_launch[cur])
         else:
             if not hasattr(self, "_launch_cache"):
                 self._launch_cache = [self._launches_v4(0), self._launches_v4(1)]   # fixed buffers: built once
             for probs in self._launch_cache[cur]:
                 self._gemv(probs)
-
-    def chain_error(self):
-        """1 if a grid barrier of the persistent decode kernel ever gave up waiting since the
-        last call (its results were then undefined); synchronises the current stream."""
-        import ctypes as C
-        e = C.c_int(0)
-        check(lib().rwkv_mm8_chain_take_error(self._ws.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream,
-                                              C.byref(e)), "mm8_chain_take_error")
-        return e.value
 
     def _plan_v56(self, cur):
         """The launches of one RWKV-5.2 / RWKV-6 token (att_one_v5_1 / att_one_v6_0, ffn_one / ffn_one_v6,

@@ -6,6 +6,7 @@ Registers, with the reference's argument lists (rwkv_pip_package/src/rwkv/cuda/w
     torch.ops.rwkv.mm8_one(N, M, x, w, mx, rx, my, ry, y)
     torch.ops.rwkv.mm8_seq(B, N, M, x, w, mx, rx, my, ry, y)
     torch.ops.rwkv.wkv_forward(B, T, C, w, u, k, v, y, aa, bb, pp)
+    torch.ops.rwkv.gemm_fp16_cublas(a, b, c)
     torch.ops.rwkv5.forward_{bf16,fp16,fp32}(B, T, C, H, state, r, k, v, w, u, y)
     torch.ops.rwkv6.forward_{bf16,fp16,fp32}(B, T, C, H, state, r, k, v, w, u, y)
 
@@ -150,6 +151,24 @@ def wkv_forward_(B, T, C, w, u, k, v, y, aa, bb, pp):
               "wkv_forward")
 
 
+def gemm_fp16_cublas_(a, b, c):
+    """c = a @ b for fp16 a, b (2-D, or 3-D batched) with fp32 accumulation, c fp16 or fp32, written in place: the
+    plain library GEMM the reference keeps for its un-quantised 'cuda fp16' strategy
+    (rwkv_pip_package/src/rwkv/cuda/gemm_fp16_cublas.cpp:28-75, called from model.py:143-162).  It is not on the
+    fp16i8 path (every 2-D weight is uint8 there); it is registered so that code written against the reference's
+    operator set finds the name, and runs on the same library (cuBLAS through torch.matmul)."""
+    _require(a.dtype == torch.float16 and b.dtype == torch.float16, "gemm_fp16_cublas multiplies fp16 tensors")
+    _require(c.dtype in (torch.float16, torch.float32), "c must be fp16 or fp32")
+    _require(a.dim() == b.dim() and a.dim() in (2, 3), "a and b must both be 2-D or both 3-D")
+    _require(a.is_contiguous() and b.is_contiguous() and c.is_contiguous(), "needs contiguous tensors")
+    _require(tuple(c.shape) == tuple(a.shape[:-1]) + (b.shape[-1],) and a.shape[-1] == b.shape[-2], "shape mismatch")
+    with torch.cuda.device(a.device):
+        if c.dtype == torch.float16:
+            torch.matmul(a, b, out=c)
+        else:
+            c.copy_(torch.matmul(a, b))
+
+
 def _wkv56(which, dtype):
     fn_name = f"rwkv_wkv{which}_forward"
 
@@ -178,6 +197,8 @@ def _register():
     rw.define(f"mm8_seq(int B, int N, int M, {T7}) -> ()")
     rw.define("wkv_forward(int B, int T, int C, Tensor w, Tensor u, Tensor k, Tensor v, Tensor(a!) y, "
               "Tensor(b!) aa, Tensor(c!) bb, Tensor(d!) pp) -> ()")
+    rw.define("gemm_fp16_cublas(Tensor a, Tensor b, Tensor(a!) c) -> ()")
+    rw.impl("gemm_fp16_cublas", gemm_fp16_cublas_, "CUDA")
     rw.impl("mm8_one", mm8_one_, "CUDA")
     rw.impl("mm8_seq", mm8_seq_, "CUDA")
     rw.impl("wkv_forward", wkv_forward_, "CUDA")
@@ -246,18 +267,15 @@ def with_wkv4(p, k, v, t_decay, t_first, state_in, state_out):
     return p
 
 
-def mm8_one_batch(problems, dtype, device, ws=None, exchange=None):
+def mm8_one_batch(problems, dtype, device, ws=None, exchange=None, flags=0):
     """One launch for 1..4 GEMVs with fused epilogues.  `ws`: zero-initialised uint8 scratch
     owned by the caller (needed under stream capture); default: the per-stream workspace.
     `exchange` (an `_lib.Mm8Exchange`): column-sharded launch that also stores its results into
-    the other ranks' buffers (shard.PeerRegion.exchange)."""
+    the other ranks' buffers (shard.PeerRegion.exchange).  `flags`: _lib.MM8_WIDE_BUILD (see the header)."""
     import ctypes as C
     n = len(problems)
     arr = (Mm8Problem * n)(*problems)
     if ws is None:
         ws = workspace(device, lib().rwkv_mm8_one_batch_workspace_bytes(arr, n))
-    if exchange is None:
-        check(lib().rwkv_mm8_one_batch(arr, n, _DT[dtype], ws.data_ptr(), ws.numel(), _stream(device)), "mm8_one_batch")
-    else:
-        check(lib().rwkv_mm8_one_batch_exchange(arr, n, C.byref(exchange), _DT[dtype], ws.data_ptr(), ws.numel(),
-                                                _stream(device)), "mm8_one_batch_exchange")
+    check(lib().rwkv_mm8_one_batch_flags(arr, n, C.byref(exchange) if exchange is not None else None, _DT[dtype], flags,
+                                         ws.data_ptr(), ws.numel(), _stream(device)), "mm8_one_batch")

@@ -220,6 +220,13 @@ typedef struct {
     uint32_t wait_seq, signal_seq;
     int32_t world, rank;
 } rwkv_mm8_exchange;
+/* The same launch with flags (`exchange` may be NULL).  RWKV_MM8_WIDE_BUILD: use the kernel build that holds up
+ * to 2560 rows of x per CTA (matrices with up to 20480 in-features need it) for this launch too, although it
+ * would fit the ordinary build: a model with one such matrix passes it on every launch, because launches that
+ * alternate between the two builds overlap worse.  No counterpart in the reference. */
+#define RWKV_MM8_WIDE_BUILD 1
+int rwkv_mm8_one_batch_flags(const rwkv_mm8_problem* problems, int count, const rwkv_mm8_exchange* exchange, int dtype,
+                             int flags, void* workspace, size_t workspace_bytes, void* stream);
 int rwkv_mm8_one_batch_exchange(const rwkv_mm8_problem* problems, int count, const rwkv_mm8_exchange* exchange,
                                 int dtype, void* workspace, size_t workspace_bytes, void* stream);
 int rwkv_peer_alloc(size_t bytes, void** ptr_out);          /* zeroed device memory that can be exported */
@@ -252,46 +259,12 @@ void rwkv_mm8_one_set_plan(int64_t total_columns, int clusters);
 
 
 /* ---------------------------------------------------------------------------------------
- * mm8 chain — a fixed list of dependent mm8_one launches (one decode step: every att/ffn
- * matmul of every layer and the head, with their fused prologues and epilogues) run as ONE
- * persistent cooperative kernel.  Replaces the per-token Python loop of RWKV.forward over
- * att_one / ffn_one (pkg/model.py:1477-1677) for T = 1.  fp16 only; every matrix must meet
- * the 16-byte layout of the fast mm8_one path.
- *
- *   rwkv_mm8_chain_ctas()        CTAs of the persistent grid on the current device.
- *   rwkv_mm8_chain_table_bytes() size of the launch table (one record per launch and CTA).
- *   rwkv_mm8_chain_plan()        HOST-side: lays the launches out into `table_out` (host
- *                                memory).  problems = all launches' problems back to back,
- *                                counts[l] = problems of launch l (1..4).  `workspace` is the
- *                                DEVICE scratch the kernel will use (its address is baked into
- *                                the table): rwkv_mm8_one_batch_workspace_bytes of the largest
- *                                launch, zero-initialised once.  Copy the table to the device.
- *   rwkv_mm8_chain_run()         enqueues one pass over the table (cooperative launch).  trace:
- *                                NULL, or n_launches x 8 uint64 (device) that receive CTA 0's
- *                                %globaltimer stamps per launch: start, barrier passed,
- *                                prologue done, stream done, partials written, ticket taken,
- *                                epilogue done.
- *   rwkv_mm8_chain_take_error()  synchronises `stream`, returns and clears the error word: 1
- *                                when a grid barrier gave up waiting (results undefined).
- * Launch l+1 may read what launch l wrote; results are bit-identical to issuing the same
- * problems through rwkv_mm8_one_batch with the same split plan.
- * ------------------------------------------------------------------------------------- */
-int rwkv_mm8_chain_ctas(void);
-size_t rwkv_mm8_chain_table_bytes(int n_launches, int n_ctas);
-int rwkv_mm8_chain_plan(const rwkv_mm8_problem* problems, const int32_t* counts, int n_launches,
-                        int dtype, int n_ctas, void* workspace, size_t workspace_bytes,
-                        void* table_out, size_t table_bytes);
-int rwkv_mm8_chain_run(const void* table_device, int n_launches, int n_ctas, void* workspace,
-                       void* trace, void* stream);
-int rwkv_mm8_chain_take_error(void* workspace, void* stream, int* error_out);
-
-/* ---------------------------------------------------------------------------------------
  * mm8 stream — one decode step (the same list of dependent mm8_one problems with fused prologues
  * and epilogues that rwkv_mm8_one_batch takes launch by launch) as ONE persistent cooperative
  * kernel, one CTA per SM, over a re-tiled copy of the codes.  Replaces the per-token loop of
  * RWKV.forward over att_one / ffn_one (pkg/model.py:1477-1677) for T = 1; no counterpart in the
  * reference.  fp16 only; every N a multiple of 8; x, ry, my and the prologue vectors 16-byte
- * aligned; LayerNorm prologues up to 8192 features.
+ * aligned.
  *
  * Layout ("weight stream"): the output columns of every matrix are dealt to the CTAs in units of
  * four, so a CTA owns whole dot products (no split-K, no reduction between CTAs).  The bytes a CTA
@@ -300,7 +273,8 @@ int rwkv_mm8_chain_take_error(void* workspace, void* stream, int* error_out);
  * moves the region through a ring of 16 KB shared-memory slots with bulk asynchronous copies and
  * runs ahead of the arithmetic across matrix and phase boundaries.  Between phases the CTAs meet
  * at a grid barrier (every wait is bounded: after 2 s it sets the error word and carries on).
- * Arithmetic: x * ry as 30-bit fixed point, exact 64-bit integer sums (see csrc/mm8_stream.cu).
+ * Arithmetic: x * ry as 30-bit (optionally 24- or 16-bit) fixed point, exact integer sums (see
+ * csrc/mm8_stream.cu).
  *
  *   rwkv_mm8_stream_ctas()          CTAs of the grid on the current device (its SM count).
  *   rwkv_mm8_stream_weight_bytes()  size of the weight stream for `problems` (all phases' problems
@@ -313,12 +287,21 @@ int rwkv_mm8_chain_take_error(void* workspace, void* stream, int* error_out);
  *                                   RWKV_ERR_UNSUPPORTED when a problem does not meet the limits.
  *   rwkv_mm8_stream_run()           enqueues one step.  sync_words: two device words (barrier
  *                                   counter, error); the call clears the counter in stream order.
- *                                   trace: NULL, or n_phases x 2 x 4 uint64 (device) receiving
+ *                                   trace: NULL, or n_phases x 2 x 16 uint64 (device) receiving
  *                                   %globaltimer stamps of CTAs 0 and 1 per phase: barrier
- *                                   arrival, barrier passed, prologue done, matrices done.
+ *                                   arrival, barrier passed, prologue done, matrices done,
+ *                                   LayerNorm statistics done, activations computed, their
+ *                                   maxima reduced, -; then for the phase's first matrix: start,
+ *                                   first stage in shared memory, last stage multiplied, the two
+ *                                   barriers of the column reduction.
  *   rwkv_mm8_stream_take_error()    synchronises `stream`, returns and clears the error word.
  * ------------------------------------------------------------------------------------- */
 int rwkv_mm8_stream_ctas(void);
+/* Tuning hook (process-wide, not thread-safe): digit planes of x * ry the matrices are multiplied with in
+ * tables planned from now on: 4 (default) = 30-bit fixed point, 3 = 24-bit (error per product at most
+ * 2^-24 of the largest |x * ry|, the mantissa of an fp32 product), 2 = 16-bit.  The kernel's speed did not
+ * depend on it when measured (it is bound by the per-phase work, not by the dot products). */
+void rwkv_mm8_stream_set_planes(int planes);
 size_t rwkv_mm8_stream_weight_bytes(const rwkv_mm8_problem* problems, int n_problems, int n_ctas);
 int rwkv_mm8_stream_pack(const rwkv_mm8_problem* problems, int n_problems, int n_ctas, void* wstream,
                          size_t wstream_bytes, void* stream);

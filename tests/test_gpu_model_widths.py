@@ -40,12 +40,12 @@ def _oracle(name):
     return _oracle_runs[name]
 
 
-@pytest.mark.parametrize("name,path", [(n, "default") for n in CASES] + [(n, "launch") for n in CASES if n.startswith("v4")])
+@pytest.mark.parametrize("name,path", [(n, "default") for n in CASES] + [(n, "stream") for n in CASES if n.startswith("v4")])
 def test_real_width_two_layer_model_matches_oracle(name, path, monkeypatch):
-    """`launch`: RWKV-4 decode as four launches per layer instead of the persistent weight-stream kernel."""
+    """`stream`: RWKV-4 decode as one persistent weight-stream kernel per token instead of four launches per layer."""
     from chatrwkv_b200.model import RWKV
-    if path == "launch":
-        monkeypatch.setenv("RWKV_B200_STREAM", "0")
+    if path == "stream":
+        monkeypatch.setenv("RWKV_B200_STREAM", "1")
     ck, tokens, lo, steps, so = _oracle(name)
     model = RWKV(copy.deepcopy(ck), "cuda fp16i8", verbose=False)
     lg, sg = model.forward(tokens[:12], None)

@@ -245,6 +245,23 @@ def test_wkv56_forward(ops, which, dtype, N, H, T):
     torch.testing.assert_close(ds.cpu(), state, rtol=1e-4, atol=1e-4)
 
 
+def test_gemm_fp16_cublas_op(ops):
+    """The reference's fp16 GEMM operator name (gemm_fp16_cublas.cpp:28-75): 2-D and batched, fp16 and fp32 out."""
+    g = torch.Generator().manual_seed(2)
+    a = torch.randn(5, 64, generator=g).half().cuda()
+    b = torch.randn(64, 48, generator=g).half().cuda()
+    for dt in (torch.float16, torch.float32):
+        c = torch.empty((5, 48), dtype=dt, device="cuda")
+        torch.ops.rwkv.gemm_fp16_cublas(a, b, c)
+        ref = a.float() @ b.float()
+        assert (c.float() - ref).abs().max().item() <= (2e-2 if dt == torch.float16 else 1e-3)
+    a3 = torch.randn(3, 5, 64, generator=g).half().cuda()
+    b3 = torch.randn(3, 64, 16, generator=g).half().cuda()
+    c3 = torch.empty((3, 5, 16), dtype=torch.float16, device="cuda")
+    torch.ops.rwkv.gemm_fp16_cublas(a3, b3, c3)
+    assert (c3.float() - torch.bmm(a3.float(), b3.float())).abs().max().item() <= 2e-2
+
+
 def test_op_schemas(ops):
     s = str(torch.ops.rwkv.mm8_one.default._schema)
     assert s.startswith("rwkv::mm8_one(int N, int M, Tensor x, Tensor w, Tensor mx, Tensor rx, Tensor my, Tensor ry")

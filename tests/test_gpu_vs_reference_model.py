@@ -135,16 +135,15 @@ def test_logits_and_greedy_tokens_match_reference_cuda_path(name, tmp_path):
               "reference": {"decode_tok_s": float(ref["decode_tok_s"]), "prefill_ms": float(ref["prefill_ms"]),
                             "noise_max": float(ref["noise_max"]) if "noise_max" in ref else None},
               "product": {"prefill_ms": prefill_ms}}
-    # every decode path of the runtime: the persistent weight-stream kernel (RWKV-4 default), a launch per
-    # matmul with 16-bit fixed-point activations, and the same with fp32 arithmetic
+    # every decode path of the runtime: a launch per group of matmuls with 16-bit fixed-point activations (the
+    # default), the same with fp32 arithmetic, and for RWKV-4 the persistent weight-stream kernel
     paths = [("launch", False, 0), ("launch_fp32", False, 8)]
     if version == 4:
         paths.insert(0, ("stream", True, 0))
     try:
         for label, use_stream, variant in paths:
             _lib.lib().rwkv_mm8_one_set_variant(variant)
-            model._use_stream = use_stream and version == 4
-            model._graphs = [None, None]            # captured graphs hold the kernels of the other path
+            model.set_decode_path("stream" if use_stream and version == 4 else "launch")   # drops the captured graphs
             st = copy.deepcopy(snapshot)
             worst, mismatch, forgiven, min_margin, rate = _decode(model, st, tokens, ref["logits_steps"])
             report["product"][label] = {"max_abs": worst, "argmax_mismatch_steps": mismatch, "forgiven_steps": forgiven,

@@ -1,6 +1,5 @@
 """mm8_one with more than 16384 in-features (the 14B shape's ffn.value: 20480): the cluster kernel's
-build with 2560 rows per CTA.  In a file of its own because the library keeps using that build for
-the rest of the process once a launch has needed it."""
+build with 2560 rows per CTA (taken per launch; rwkv_mm8_one_batch_flags can ask for it on other launches too)."""
 import pytest
 import torch
 
@@ -23,7 +22,7 @@ def test_mm8_one_20480_in_features(N, M):
     torch.ops.rwkv.mm8_one(N, M, x.cuda(), *dev, y2)
     assert (y.cpu() - ref).abs().max().item() <= 2.5e-4 * ref.abs().max().item()
     assert torch.equal(y, y2)
-    # a matrix of ordinary size afterwards runs on the same build
+    # a matrix of ordinary size afterwards runs on the ordinary build again
     cpu2, dev2 = packed_case(4096, 4096, seed=5)
     x2 = torch.randn(4096, generator=g).half()
     ref2 = orc.mm8_kernel(x2, *cpu2)
