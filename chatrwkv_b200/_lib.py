@@ -88,6 +88,10 @@ SIGNATURES = {
     "rwkv_mm8_seq_set_path": (None, [_i32]),
     "rwkv_mm8_seq_tc_take_error": (_i32, [_vp, _vp, C.POINTER(C.c_int)]),
     "rwkv_mm8_seq": (_i32, [_i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _sz, _vp]),
+    "rwkv_mm8_seq_epi": (_i32, [_i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _i32, _vp, _i64, _vp, _i64,
+                                _f, _vp, _sz, _vp]),
+    "rwkv_wkv4_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "rwkv_wkv4_seq": (_i32, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _sz, _vp]),
     "rwkv_wkv4_forward": (_i32, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp]),
     "rwkv_wkv5_forward": (_i32, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp]),
     "rwkv_wkv6_forward": (_i32, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp]),

@@ -7,6 +7,7 @@
 // This file holds the shape-agnostic CUDA-core kernel (any B, N, M, any stride or
 // alignment).  It is the path for ragged or misaligned operands and for small B.
 #include "common.cuh"
+#include "seq_epi.cuh"
 
 namespace {
 
@@ -20,7 +21,7 @@ __global__ void __launch_bounds__(256) mm8_seq_simt(int B, int N, int M,
                                                     const uint8_t* __restrict__ w, long long w_stride,
                                                     const F* __restrict__ mx, const F* __restrict__ rx,
                                                     const F* __restrict__ my, const F* __restrict__ ry,
-                                                    F* __restrict__ y, long long y_stride) {
+                                                    F* y, long long y_stride, const SeqEpi epi) {
     __shared__ float xs[TK][TM + 4];
     __shared__ float ws[TK][TN];
     __shared__ float rsum[3][TM];
@@ -86,7 +87,7 @@ __global__ void __launch_bounds__(256) mm8_seq_simt(int B, int N, int M,
             const int r = ty * 4 + a, i = i0 + r;
             if (i >= B) continue;
             const float val = fmaf(rxk, acc[a][b], fmaf(rxk * 128.5f, rsum[1][r], fmaf(mxk, rsum[0][r], rsum[2][r])));
-            y[(long long)i * y_stride + k] = from_f32<F>(val);
+            y[(long long)i * y_stride + k] = seq_epilogue<F>(epi, i, k, val);
         }
     }
 }
@@ -95,10 +96,10 @@ __global__ void __launch_bounds__(256) mm8_seq_simt(int B, int N, int M,
 
 // tensor-core path (mm8_seq_tc.cu)
 extern "C" size_t rwkv_mm8_seq_tc_workspace_bytes(int64_t B, int64_t N, int64_t M);
-extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
-                               const uint8_t* w, int64_t w_stride, const void* mx, const void* rx,
-                               const void* my, const void* ry, int dtype, void* y, int64_t y_stride,
-                               void* workspace, size_t workspace_bytes, void* stream);
+int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
+                    const uint8_t* w, int64_t w_stride, const void* mx, const void* rx,
+                    const void* my, const void* ry, int dtype, void* y, int64_t y_stride, const SeqEpi& epi,
+                    void* workspace, size_t workspace_bytes, void* stream);
 
 extern "C" void rwkv_mm8_seq_tc_set_single(int single);
 static int g_seq_path = 0;      // 0 = automatic, 1 = CUDA cores only, 2 = tensor cores whenever the layout allows
@@ -116,16 +117,22 @@ extern "C" size_t rwkv_mm8_seq_workspace_bytes(int64_t B, int64_t N, int64_t M) 
     return rwkv_mm8_seq_tc_workspace_bytes(B, N, M);
 }
 
-extern "C" int rwkv_mm8_seq(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
-                            const uint8_t* w, int64_t w_stride,
-                            const void* mx, const void* rx, const void* my, const void* ry, int dtype,
-                            void* y, int64_t y_stride, void* workspace, size_t workspace_bytes, void* stream) {
+extern "C" int rwkv_mm8_seq_epi(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
+                                const uint8_t* w, int64_t w_stride,
+                                const void* mx, const void* rx, const void* my, const void* ry, int dtype,
+                                void* y, int64_t y_stride, int epilogue, const void* aux, int64_t aux_stride,
+                                const void* aux2, int64_t aux2_stride, float out_scale,
+                                void* workspace, size_t workspace_bytes, void* stream) {
     RWKV_CHECK_ARG(B >= 1 && N >= 1 && M >= 1 && N <= INT32_MAX && M <= INT32_MAX && B <= INT32_MAX);
     RWKV_CHECK_ARG(x && w && mx && rx && my && ry && y);
     RWKV_CHECK_ARG(x_stride >= N && w_stride >= M && y_stride >= M);
     RWKV_CHECK_ARG(dtype == RWKV_F16 || dtype == RWKV_F32);
+    SeqEpi epi;
+    epi.mode = epilogue; epi.out_scale = out_scale; epi.aux = aux; epi.aux_stride = aux_stride; epi.aux2 = aux2; epi.aux2_stride = aux2_stride;
+    const int erc = seq_epi_check(epi);
+    if (erc != RWKV_OK) return erc;
     if (g_seq_path != 1 && workspace != nullptr && (B >= kTcMinRows || g_seq_path == 2)) {
-        const int rc = rwkv_mm8_seq_tc(B, N, M, x, x_stride, w, w_stride, mx, rx, my, ry, dtype, y, y_stride,
+        const int rc = rwkv_mm8_seq_tc(B, N, M, x, x_stride, w, w_stride, mx, rx, my, ry, dtype, y, y_stride, epi,
                                        workspace, workspace_bytes, stream);
         if (rc != RWKV_ERR_UNSUPPORTED && rc != RWKV_ERR_WORKSPACE) return rc;   // else: CUDA-core kernel below
     }
@@ -135,10 +142,18 @@ extern "C" int rwkv_mm8_seq(int64_t B, int64_t N, int64_t M, const void* x, int6
     if (dtype == RWKV_F16)
         mm8_seq_simt<__half><<<grid, 256, 0, st>>>(int(B), int(N), int(M), (const __half*)x, x_stride, w, w_stride,
                                                     (const __half*)mx, (const __half*)rx, (const __half*)my,
-                                                    (const __half*)ry, (__half*)y, y_stride);
+                                                    (const __half*)ry, (__half*)y, y_stride, epi);
     else
         mm8_seq_simt<float><<<grid, 256, 0, st>>>(int(B), int(N), int(M), (const float*)x, x_stride, w, w_stride,
                                                    (const float*)mx, (const float*)rx, (const float*)my,
-                                                   (const float*)ry, (float*)y, y_stride);
+                                                   (const float*)ry, (float*)y, y_stride, epi);
     return rwkv_launch_status();
+}
+
+extern "C" int rwkv_mm8_seq(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
+                            const uint8_t* w, int64_t w_stride,
+                            const void* mx, const void* rx, const void* my, const void* ry, int dtype,
+                            void* y, int64_t y_stride, void* workspace, size_t workspace_bytes, void* stream) {
+    return rwkv_mm8_seq_epi(B, N, M, x, x_stride, w, w_stride, mx, rx, my, ry, dtype, y, y_stride, RWKV_EPI_STORE, nullptr, 0,
+                            nullptr, 0, 1.0f, workspace, workspace_bytes, stream);
 }

@@ -21,6 +21,7 @@
 // Synchronisation is by mbarriers only.  Every wait is bounded: on give-up the CTA raises an
 // error word, skips the rest of its work, frees its tensor memory and returns.
 #include "common.cuh"
+#include "seq_epi.cuh"
 #include <algorithm>
 
 namespace {
@@ -214,6 +215,7 @@ struct TcArgs {
     // blocks [z * kb_per, (z + 1) * kb_per) and writes its fp32 sums to partial[z][t][m_pad]
     int ksplit, kb_per, m_pad;
     float* partial;
+    SeqEpi epi;
 };
 
 template <typename F>
@@ -363,13 +365,20 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                             const uint4 m4 = __ldg(reinterpret_cast<const uint4*>(mx + nb) + q);
                             const __half* rh = reinterpret_cast<const __half*>(&r4);
                             const __half* mh = reinterpret_cast<const __half*>(&m4);
-                            uint4 o4;
+                            uint4 o4, x4 = make_uint4(0, 0, 0, 0), z4 = make_uint4(0, 0, 0, 0);
+                            if (a.epi.mode == RWKV_EPI_RESIDUAL || a.epi.mode == RWKV_EPI_MUL_RESIDUAL)
+                                x4 = *(reinterpret_cast<const uint4*>(static_cast<const __half*>(a.epi.aux) + (long long)t * a.epi.aux_stride + nb) + q);
+                            if (a.epi.mode == RWKV_EPI_MUL_RESIDUAL)
+                                z4 = *(reinterpret_cast<const uint4*>(static_cast<const __half*>(a.epi.aux2) + (long long)t * a.epi.aux2_stride + nb) + q);
+                            const __half* xh = reinterpret_cast<const __half*>(&x4);
+                            const __half* zh = reinterpret_cast<const __half*>(&z4);
                             __half* oh = reinterpret_cast<__half*>(&o4);
 #pragma unroll
                             for (int e = 0; e < 8; ++e) {
                                 const float rxn = __half2float(rh[e]);
-                                oh[e] = __float2half_rn(fmaf(rxn, __uint_as_float(v[q * 8 + e]),
-                                                             fmaf(rxn * 128.5f, sxr, fmaf(__half2float(mh[e]), sx, sxmy))));
+                                const float val = fmaf(rxn, __uint_as_float(v[q * 8 + e]),
+                                                       fmaf(rxn * 128.5f, sxr, fmaf(__half2float(mh[e]), sx, sxmy)));
+                                oh[e] = seq_epilogue_with<__half>(a.epi.mode, a.epi.out_scale, val, __half2float(xh[e]), __half2float(zh[e]));
                             }
                             reinterpret_cast<uint4*>(yrow + nb)[q] = o4;
                         }
@@ -380,7 +389,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
                             if (n < a.M) {
                                 const float rxn = to_f32<F>(rx[n]);
                                 const float val = fmaf(rxn, __uint_as_float(v[j]), fmaf(rxn * 128.5f, sxr, fmaf(to_f32<F>(mx[n]), sx, sxmy)));
-                                yrow[n] = from_f32<F>(val);
+                                yrow[n] = seq_epilogue<F>(a.epi, t, n, val);
                             }
                         }
                     }
@@ -448,7 +457,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
 template <typename F>
 __global__ void __launch_bounds__(256) mm8_seq_reduce(int T, int M, int m_pad, int ksplit, const float* __restrict__ partial,
                                                       const float* __restrict__ sums, int nsum, const F* __restrict__ mx,
-                                                      const F* __restrict__ rx, F* __restrict__ y, long long y_stride) {
+                                                      const F* __restrict__ rx, F* y, long long y_stride, const SeqEpi epi) {
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int t = blockIdx.y;
@@ -461,7 +470,7 @@ __global__ void __launch_bounds__(256) mm8_seq_reduce(int T, int M, int m_pad, i
         float s = 0.f;
         for (int z = 0; z < ksplit; ++z) s += partial[((long long)z * T + t) * m_pad + n];
         const float rxn = to_f32<F>(rx[n]);
-        y[(long long)t * y_stride + n] = from_f32<F>(fmaf(rxn, s, fmaf(rxn * 128.5f, sxr, fmaf(to_f32<F>(mx[n]), sx, sxmy))));
+        y[(long long)t * y_stride + n] = seq_epilogue<F>(epi, t, n, fmaf(rxn, s, fmaf(rxn * 128.5f, sxr, fmaf(to_f32<F>(mx[n]), sx, sxmy))));
     }
 }
 
@@ -496,10 +505,10 @@ extern "C" size_t rwkv_mm8_seq_tc_workspace_bytes(int64_t B, int64_t N, int64_t 
 
 // Returns RWKV_ERR_UNSUPPORTED when the operands do not meet the layout the tensor-core kernel
 // needs (the caller then uses the CUDA-core kernel).
-extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
-                               const uint8_t* w, int64_t w_stride, const void* mx, const void* rx,
-                               const void* my, const void* ry, int dtype, void* y, int64_t y_stride,
-                               void* workspace, size_t workspace_bytes, void* stream) {
+int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
+                    const uint8_t* w, int64_t w_stride, const void* mx, const void* rx,
+                    const void* my, const void* ry, int dtype, void* y, int64_t y_stride, const SeqEpi& epi,
+                    void* workspace, size_t workspace_bytes, void* stream) {
     RWKV_CHECK_ARG(B >= 1 && N >= 1 && M >= 1 && x && w && mx && rx && my && ry && y);
     if (dtype != RWKV_F16) return RWKV_ERR_UNSUPPORTED;
     if (reinterpret_cast<uintptr_t>(w) % 8 != 0 || w_stride % 8 != 0 || M % 8 != 0) return RWKV_ERR_UNSUPPORTED;
@@ -528,8 +537,11 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
     a.hi = hi; a.lo = lo; a.sums = sums; a.nsum = shares; a.w = w; a.w_stride = w_stride; a.mx = mx; a.rx = rx;
     a.y = y; a.y_stride = y_stride; a.T = int(B); a.N = int(N); a.M = int(M); a.error_flag = err;
     a.single = g_tc_single;
+    a.epi = epi;
     a.vec_ok = (reinterpret_cast<uintptr_t>(y) % 16 == 0 && y_stride % 8 == 0 && reinterpret_cast<uintptr_t>(rx) % 16 == 0 &&
                 reinterpret_cast<uintptr_t>(mx) % 16 == 0) ? 1 : 0;
+    if (epi.aux != nullptr && (reinterpret_cast<uintptr_t>(epi.aux) % 16 != 0 || epi.aux_stride % 8 != 0)) a.vec_ok = 0;
+    if (epi.aux2 != nullptr && (reinterpret_cast<uintptr_t>(epi.aux2) % 16 != 0 || epi.aux2_stride % 8 != 0)) a.vec_ok = 0;
     auto kern = mm8_seq_tc_kernel<__half>;
     static bool configured[64] = {};         // function attributes are per device
     int dev = 0;
@@ -552,7 +564,7 @@ extern "C" int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, i
     if (rc != RWKV_OK || ks == 1) return rc;
     return rwkv_launch_pdl(mm8_seq_reduce<__half>, dim3((unsigned)((M + 255) / 256), (unsigned)B), dim3(256), 0, st, int(B),
                            int(M), a.m_pad, ks, (const float*)a.partial, (const float*)sums, shares, static_cast<const __half*>(mx),
-                           static_cast<const __half*>(rx), static_cast<__half*>(y), (long long)y_stride);
+                           static_cast<const __half*>(rx), static_cast<__half*>(y), (long long)y_stride, epi);
 }
 
 // 1: one tensor-core pass with fp16(x*ry) instead of the exact hi + lo pair (about 1e-4 of the output RMS less

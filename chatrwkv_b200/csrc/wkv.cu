@@ -7,61 +7,133 @@
 namespace {
 
 // ---------------------------------------------------------------------------------------
-// RWKV-4: one thread per channel, sequential in t (reference: operators.cu:11-50).  k and v
-// are fetched eight steps ahead of the dependent chain.
+// RWKV-4 (the recurrence of operators.cu:30-46 / pkg/model.py:1069-1084), parallel in time.
+//
+// Per channel the state is (aa, bb, pp): A = aa e^pp = sum_s e^{(t-1-s) w + k_s} v_s and B likewise
+// without v.  A step multiplies A, B by e^w and adds e^{k_t} (v_t, 1): an affine map, so T steps
+// split into chunks of Lc: (1) every (chunk, channel) runs its Lc steps from the empty state and
+// keeps the chunk's own sums (a_c, b_c, p_c); (2) every (chunk, channel) folds the summaries of the
+// chunks before it into the caller's state -- state' = e^{w Lc} state + summary, in the same
+// max-shifted form as a step -- and then (3) runs its Lc steps again from that state, now writing
+// y.  Twice the arithmetic, T / Lc times the threads: 1024 tokens x 4096 channels keep 131072
+// threads busy instead of 4096, each with 32 dependent steps instead of 1024.  With one chunk
+// (T <= Lc) only the second kernel runs and nothing is recomputed.
+// MULR: y is multiplied by r (the receptance) with the reference's roundings, y -> dtype, then
+// r * y -> dtype (cuda_att_seq, pkg/model.py:1359-1360).
 // ---------------------------------------------------------------------------------------
+constexpr int kWkv4Threads = 128;
+constexpr int kWkv4MaxChunks = 64;
+
+struct Wkv4State { float aa, bb, pp; };
+
+__device__ __forceinline__ void wkv4_step(Wkv4State& s, float w, float kk, float vv) {
+    const float ww = w + s.pp;
+    const float p = fmaxf(ww, kk);
+    const float e1 = expf(ww - p), e2 = expf(kk - p);
+    s.aa = e1 * s.aa + e2 * vv;
+    s.bb = e1 * s.bb + e2;
+    s.pp = p;
+}
+
+// summaries of chunks 0 .. NC-2 (the last chunk's is never needed) and a copy of the caller's state
 template <typename F>
-__global__ void __launch_bounds__(32) wkv4_seq_kernel(int B, int T, int C,
-                                                      const float* __restrict__ w_, const float* __restrict__ u_,
-                                                      const F* __restrict__ k_, const F* __restrict__ v_,
-                                                      F* __restrict__ y_, float* __restrict__ aa_,
-                                                      float* __restrict__ bb_, float* __restrict__ pp_) {
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= B * C) return;
-    const int b = idx / C, c = idx % C;
-    const long long off = (long long)b * T * C + c;
-    const F* k = k_ + off;
-    const F* v = v_ + off;
-    F* y = y_ + off;
-    const float u = u_[c], w = w_[c];
-    float aa = aa_[idx], bb = bb_[idx], pp = pp_[idx];
-    constexpr int U = 8;
+__global__ void __launch_bounds__(kWkv4Threads) wkv4_summary_kernel(int T, int C, int Lc, int NC, const float* __restrict__ w_,
+                                                                    const F* __restrict__ k_, const F* __restrict__ v_,
+                                                                    const float* __restrict__ aa_, const float* __restrict__ bb_,
+                                                                    const float* __restrict__ pp_, float* __restrict__ summ,
+                                                                    float* __restrict__ init) {
+    const int c = blockIdx.x * kWkv4Threads + threadIdx.x, chunk = blockIdx.y, b = blockIdx.z;
+    if (c >= C) return;
+    if (chunk == 0) {
+        float* ini = init + (size_t)b * 3 * C;
+        ini[c] = aa_[(size_t)b * C + c]; ini[C + c] = bb_[(size_t)b * C + c]; ini[2 * C + c] = pp_[(size_t)b * C + c];
+    }
+    const float w = w_[c];
+    const int t0 = chunk * Lc, t1 = min(T, t0 + Lc);
+    const F* k = k_ + ((size_t)b * T + t0) * C + c;
+    const F* v = v_ + ((size_t)b * T + t0) * C + c;
+    Wkv4State s = {0.f, 0.f, -1e30f};
+    const int n = t1 - t0;
     int t = 0;
-    for (; t + U <= T; t += U) {
-        float kk[U], vv[U];
+    for (; t + 4 <= n; t += 4) {
+        float kk[4], vv[4];
 #pragma unroll
-        for (int i = 0; i < U; ++i) {
-            kk[i] = to_f32<F>(k[(long long)(t + i) * C]);
-            vv[i] = to_f32<F>(v[(long long)(t + i) * C]);
-        }
+        for (int i = 0; i < 4; ++i) { kk[i] = to_f32<F>(k[(size_t)(t + i) * C]); vv[i] = to_f32<F>(v[(size_t)(t + i) * C]); }
 #pragma unroll
-        for (int i = 0; i < U; ++i) {
-            float ww = u + kk[i];
-            float p = fmaxf(pp, ww);
-            float e1 = expf(pp - p), e2 = expf(ww - p);
-            y[(long long)(t + i) * C] = from_f32<F>((e1 * aa + e2 * vv[i]) / (e1 * bb + e2));
-            ww = w + pp;
-            p = fmaxf(ww, kk[i]);
-            e1 = expf(ww - p); e2 = expf(kk[i] - p);
-            aa = e1 * aa + e2 * vv[i];
-            bb = e1 * bb + e2;
-            pp = p;
+        for (int i = 0; i < 4; ++i) wkv4_step(s, w, kk[i], vv[i]);
+    }
+    for (; t < n; ++t) wkv4_step(s, w, to_f32<F>(k[(size_t)t * C]), to_f32<F>(v[(size_t)t * C]));
+    float* out = summ + ((size_t)b * NC + chunk) * 3 * C;
+    out[c] = s.aa; out[C + c] = s.bb; out[2 * C + c] = s.pp;
+}
+
+template <typename F, bool MULR>
+__global__ void __launch_bounds__(kWkv4Threads) wkv4_apply_kernel(int T, int C, int Lc, int NC, const float* __restrict__ w_,
+                                                                  const float* __restrict__ u_, const F* __restrict__ k_,
+                                                                  const F* __restrict__ v_, const F* __restrict__ r_, F* __restrict__ y_,
+                                                                  float* aa_, float* bb_, float* pp_,
+                                                                  const float* __restrict__ summ, const float* __restrict__ init) {
+    const int c = blockIdx.x * kWkv4Threads + threadIdx.x, chunk = blockIdx.y, b = blockIdx.z;
+    if (c >= C) return;
+    const float w = w_[c], u = u_[c];
+    Wkv4State s;
+    if (NC == 1) {
+        s.aa = aa_[(size_t)b * C + c]; s.bb = bb_[(size_t)b * C + c]; s.pp = pp_[(size_t)b * C + c];
+    } else {
+        const float* ini = init + (size_t)b * 3 * C;
+        s.aa = ini[c]; s.bb = ini[C + c]; s.pp = ini[2 * C + c];
+        const float wl = w * float(Lc);
+        for (int j = 0; j < chunk; ++j) {       // state after chunk j = e^{w Lc} state + summary_j
+            const float* sm = summ + ((size_t)b * NC + j) * 3 * C;
+            const float sa = sm[c], sb = sm[C + c], sp = sm[2 * C + c];
+            const float ww = wl + s.pp;
+            const float p = fmaxf(ww, sp);
+            const float e1 = expf(ww - p), e2 = expf(sp - p);
+            s.aa = e1 * s.aa + e2 * sa;
+            s.bb = e1 * s.bb + e2 * sb;
+            s.pp = p;
         }
     }
-    for (; t < T; ++t) {
-        const float kk = to_f32<F>(k[(long long)t * C]), vv = to_f32<F>(v[(long long)t * C]);
-        float ww = u + kk;
-        float p = fmaxf(pp, ww);
-        float e1 = expf(pp - p), e2 = expf(ww - p);
-        y[(long long)t * C] = from_f32<F>((e1 * aa + e2 * vv) / (e1 * bb + e2));
-        ww = w + pp;
-        p = fmaxf(ww, kk);
-        e1 = expf(ww - p); e2 = expf(kk - p);
-        aa = e1 * aa + e2 * vv;
-        bb = e1 * bb + e2;
-        pp = p;
+    const int t0 = chunk * Lc, t1 = min(T, t0 + Lc);
+    const size_t base = ((size_t)b * T + t0) * C + c;
+    const F* k = k_ + base;
+    const F* v = v_ + base;
+    const F* r = MULR ? r_ + base : nullptr;
+    F* y = y_ + base;
+    const int n = t1 - t0;
+    int t = 0;
+    for (; t + 4 <= n; t += 4) {
+        float kk[4], vv[4], rr[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            kk[i] = to_f32<F>(k[(size_t)(t + i) * C]); vv[i] = to_f32<F>(v[(size_t)(t + i) * C]);
+            rr[i] = MULR ? to_f32<F>(r[(size_t)(t + i) * C]) : 1.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float ww = u + kk[i];
+            const float p = fmaxf(s.pp, ww);
+            const float e1 = expf(s.pp - p), e2 = expf(ww - p);
+            const float yv = (e1 * s.aa + e2 * vv[i]) / (e1 * s.bb + e2);
+            y[(size_t)(t + i) * C] = MULR ? from_f32<F>(rr[i] * to_f32<F>(from_f32<F>(yv))) : from_f32<F>(yv);
+            wkv4_step(s, w, kk[i], vv[i]);
+        }
     }
-    aa_[idx] = aa; bb_[idx] = bb; pp_[idx] = pp;
+    for (; t < n; ++t) {
+        const float kk = to_f32<F>(k[(size_t)t * C]), vv = to_f32<F>(v[(size_t)t * C]);
+        const float ww = u + kk;
+        const float p = fmaxf(s.pp, ww);
+        const float e1 = expf(s.pp - p), e2 = expf(ww - p);
+        const float yv = (e1 * s.aa + e2 * vv) / (e1 * s.bb + e2);
+        y[(size_t)t * C] = MULR ? from_f32<F>(to_f32<F>(r[(size_t)t * C]) * to_f32<F>(from_f32<F>(yv))) : from_f32<F>(yv);
+        wkv4_step(s, w, kk, vv);
+    }
+    if (chunk == NC - 1) { aa_[(size_t)b * C + c] = s.aa; bb_[(size_t)b * C + c] = s.bb; pp_[(size_t)b * C + c] = s.pp; }
+}
+
+static inline void wkv4_chunks(int64_t T, int& Lc, int& NC) {
+    Lc = T <= 32 * kWkv4MaxChunks ? 32 : int((T + kWkv4MaxChunks - 1) / kWkv4MaxChunks);
+    NC = int((T + Lc - 1) / Lc);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -169,22 +241,52 @@ int forward56(int64_t B, int64_t T, int64_t C, int64_t H, float* state, const vo
 
 }  // namespace
 
+extern "C" size_t rwkv_wkv4_workspace_bytes(int64_t B, int64_t T, int64_t C) {
+    if (B < 1 || T < 1 || C < 1) return 0;
+    int Lc, NC;
+    wkv4_chunks(T, Lc, NC);
+    return NC == 1 ? 0 : size_t(B) * size_t(NC + 1) * 3 * size_t(C) * sizeof(float);
+}
+
+template <typename F>
+static int wkv4_launch(int64_t B, int64_t T, int64_t C, const float* w, const float* u, const F* k, const F* v, const F* r, F* y,
+                       float* aa, float* bb, float* pp, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    int Lc, NC;
+    wkv4_chunks(T, Lc, NC);
+    if (NC > 1 && (workspace == nullptr || workspace_bytes < rwkv_wkv4_workspace_bytes(B, T, C))) { Lc = int(T); NC = 1; }   // one chunk: sequential
+    float* summ = static_cast<float*>(workspace);
+    float* init = NC > 1 ? summ + size_t(B) * NC * 3 * C : nullptr;
+    const dim3 grid((unsigned)((C + kWkv4Threads - 1) / kWkv4Threads), (unsigned)NC, (unsigned)B);
+    if (NC > 1) {
+        const dim3 g1(grid.x, (unsigned)(NC - 1), grid.z);
+        wkv4_summary_kernel<F><<<g1, kWkv4Threads, 0, st>>>(int(T), int(C), Lc, NC, w, k, v, aa, bb, pp, summ, init);
+    }
+    if (r != nullptr)
+        wkv4_apply_kernel<F, true><<<grid, kWkv4Threads, 0, st>>>(int(T), int(C), Lc, NC, w, u, k, v, r, y, aa, bb, pp, summ, init);
+    else
+        wkv4_apply_kernel<F, false><<<grid, kWkv4Threads, 0, st>>>(int(T), int(C), Lc, NC, w, u, k, v, r, y, aa, bb, pp, summ, init);
+    return rwkv_launch_status();
+}
+
+extern "C" int rwkv_wkv4_seq(int64_t B, int64_t T, int64_t C, const float* w, const float* u,
+                             const void* k, const void* v, const void* r, void* y, int kv_dtype,
+                             float* aa, float* bb, float* pp, void* workspace, size_t workspace_bytes, void* stream) {
+    RWKV_CHECK_ARG(B >= 1 && T >= 1 && C >= 1 && B <= 65535 && B * C <= INT32_MAX && T <= INT32_MAX);
+    RWKV_CHECK_ARG(w && u && k && v && y && aa && bb && pp);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (kv_dtype == RWKV_F16)
+        return wkv4_launch<__half>(B, T, C, w, u, (const __half*)k, (const __half*)v, (const __half*)r, (__half*)y, aa, bb, pp,
+                                   workspace, workspace_bytes, st);
+    if (kv_dtype == RWKV_F32)
+        return wkv4_launch<float>(B, T, C, w, u, (const float*)k, (const float*)v, (const float*)r, (float*)y, aa, bb, pp,
+                                  workspace, workspace_bytes, st);
+    return RWKV_ERR_INVALID_ARG;
+}
+
 extern "C" int rwkv_wkv4_forward(int64_t B, int64_t T, int64_t C, const float* w, const float* u,
                                  const void* k, const void* v, void* y, int kv_dtype,
                                  float* aa, float* bb, float* pp, void* stream) {
-    RWKV_CHECK_ARG(B >= 1 && T >= 1 && C >= 1 && B * C <= INT32_MAX && T <= INT32_MAX);
-    RWKV_CHECK_ARG(w && u && k && v && y && aa && bb && pp);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int blocks = int((B * C + 31) / 32);
-    if (kv_dtype == RWKV_F16)
-        wkv4_seq_kernel<__half><<<blocks, 32, 0, st>>>(int(B), int(T), int(C), w, u, (const __half*)k,
-                                                       (const __half*)v, (__half*)y, aa, bb, pp);
-    else if (kv_dtype == RWKV_F32)
-        wkv4_seq_kernel<float><<<blocks, 32, 0, st>>>(int(B), int(T), int(C), w, u, (const float*)k,
-                                                      (const float*)v, (float*)y, aa, bb, pp);
-    else
-        return RWKV_ERR_INVALID_ARG;
-    return rwkv_launch_status();
+    return rwkv_wkv4_seq(B, T, C, w, u, k, v, nullptr, y, kv_dtype, aa, bb, pp, nullptr, 0, stream);
 }
 
 extern "C" int rwkv_wkv5_forward(int64_t B, int64_t T, int64_t C, int64_t H, float* state,

@@ -752,8 +752,15 @@ class RWKV:
             torch.ops.rwkv.mm8_seq(T, N, M, x, wq, mx, rx, my, ry, y)
         return y if out_dtype is None else y.to(out_dtype)
 
+    def _mm_epi(self, x, name, epilogue, aux=None, aux2=None, out_scale=1.0, out=None):
+        """mm8_seq with the reference's next pointwise op(s) fused into the store (single-GPU path)."""
+        wq, mx, rx, my, ry = self._scales(name)
+        y = out if out is not None else torch.empty((x.shape[0], wq.shape[1]), dtype=torch.float16, device=x.device)
+        return ops.mm8_seq_epi(x, wq, mx, rx, my, ry, y, epilogue, aux, aux2, out_scale)
+
     def _att_seq_v4(self, x, st, i):
-        """cuda_att_seq (model.py:1346-1360)."""
+        """cuda_att_seq (model.py:1346-1360): LayerNorm + mixes, r/k/v matmuls (sigmoid in the store), the WKV
+        recurrence parallel in time with r * wkv in its store, output matmul with the residual in the store."""
         w, a = self.w, self.args
         T, C = x.shape
         bb, att = f"blocks.{i}.", f"blocks.{i}.att."
@@ -762,6 +769,13 @@ class RWKV:
         self._ln_mix(T, x, st[i * 5 + 0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 0,
                      [w[att + "time_mix_k"], w[att + "time_mix_v"], w[att + "time_mix_r"]], [kx, vx, rx],
                      new_state=new_sx)
+        if self._world == 1:
+            r = self._mm_epi(rx, att + "receptance.weight", EPI_SIGMOID)
+            k = self._mm_epi(kx, att + "key.weight", EPI_STORE)             # fp16 k, v: the kernel widens them, as
+            v = self._mm_epi(vx, att + "value.weight", EPI_STORE)           # model.py:1355-1356 does before the op
+            ops.wkv4_seq(w[att + "time_decay"], w[att + "time_first"], k, v, k, st[i * 5 + 1], st[i * 5 + 2], st[i * 5 + 3], r=r)
+            st[i * 5 + 0] = new_sx
+            return self._mm_epi(k, att + "output.weight", EPI_RESIDUAL, aux=x, out=x)
         r = torch.sigmoid(self._mm_seq(rx, att + "receptance.weight"))
         k = self._mm_seq(kx, att + "key.weight", torch.float32)
         v = self._mm_seq(vx, att + "value.weight", torch.float32)
@@ -832,6 +846,13 @@ class RWKV:
         else:
             self._ln_mix(T, x, sx, w[bb + "ln2.weight"], w[bb + "ln2.bias"], 0,
                          [w[ffn + "time_mix_k"], w[ffn + "time_mix_r"]], [kx, rx], new_state=new_sx)
+        if self._world == 1:
+            r = self._mm_epi(rx, ffn + "receptance.weight", EPI_SIGMOID)
+            vx = self._mm_epi(kx, ffn + "key.weight", EPI_RELU_SQ)
+            # x + r * (vx @ Wv), and the halving after every RESCALE_LAYER-th layer (model.py:1660-1662), in the store
+            half = self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0
+            return self._mm_epi(vx, ffn + "value.weight", EPI_MUL_RESIDUAL, aux=x, aux2=r, out_scale=0.5 if half else 1.0,
+                                out=x), new_sx
         r = torch.sigmoid(self._mm_seq(rx, ffn + "receptance.weight"))
         vx = torch.relu(self._mm_seq(kx, ffn + "key.weight")) ** 2
         out = r * self._mm_seq(vx, ffn + "value.weight")
@@ -851,8 +872,8 @@ class RWKV:
                 x = self._att_seq_v56(x, st2, i)
                 state[i * 3 + 0], state[i * 3 + 1] = st2
                 x, state[i * 3 + 2] = self._ffn_seq(x, state[i * 3 + 2], i)
-            if self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0:
-                x = x / 2
+            if self._world > 1 and self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0:
+                x = x / 2           # (single GPU: fused into the ffn.value store)
         if not full_output:
             x = x[-1:, :]
         xln = torch.empty_like(x)

@@ -139,6 +139,49 @@ def mm8_seq_(B, N, M, x, w, mx, rx, my, ry, y):
                                  ws.numel() if ws is not None else 0, _stream(dev)), "mm8_seq")
 
 
+def mm8_seq_epi(x, w, mx, rx, my, ry, y, epilogue, aux=None, aux2=None, out_scale=1.0):
+    """mm8_seq with a fused epilogue (`_lib.EPI_*`; rwkv_mm8_seq_epi in the header): y[B, M] = epilogue(x[B, N] @ W).
+    aux / aux2: [B, M] tensors of y's dtype (row strides honoured); y may alias aux."""
+    _check_mm8(x, w, mx, rx, my, ry, y)
+    _require(y.dtype == x.dtype, "mm8_seq writes y in x.dtype")
+    for t in (aux, aux2):
+        _require(t is None or (t.dtype == y.dtype and t.shape == y.shape and t.stride(-1) == 1), "aux must look like y")
+    B, N = x.shape
+    M = w.shape[1]
+    dev = w.device
+    with torch.cuda.device(dev):
+        nbytes = lib().rwkv_mm8_seq_workspace_bytes(B, N, M)
+        ws = workspace(dev, nbytes, "mm8_seq")
+        check(lib().rwkv_mm8_seq_epi(B, N, M, x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0),
+                                     mx.data_ptr(), rx.data_ptr(), my.data_ptr(), ry.data_ptr(), _DT[x.dtype],
+                                     y.data_ptr(), y.stride(0), epilogue,
+                                     aux.data_ptr() if aux is not None else None, aux.stride(0) if aux is not None else 0,
+                                     aux2.data_ptr() if aux2 is not None else None, aux2.stride(0) if aux2 is not None else 0,
+                                     float(out_scale), ws.data_ptr() if ws is not None else None,
+                                     ws.numel() if ws is not None else 0, _stream(dev)), "mm8_seq_epi")
+    return y
+
+
+def wkv4_seq(w, u, k, v, y, aa, bb, pp, r=None):
+    """WKV-v4 over k, v [T, C] (or [B, T, C]) with the state aa, bb, pp updated in place, parallel in time from 33
+    steps on; with `r`, y = r * wkv rounded as cuda_att_seq does (rwkv_wkv4_seq in the header)."""
+    _require(k.dtype in (torch.float16, torch.float32) and k.dtype == v.dtype == y.dtype, "Only FP16 and FP32 are currently supported")
+    _require(r is None or r.dtype == k.dtype, "r must have k's dtype")
+    _require(all(t.dtype == torch.float32 for t in (w, u, aa, bb, pp)), "w, u and the state must be fp32")
+    _require(all(t is None or t.is_contiguous() for t in (w, u, k, v, y, aa, bb, pp, r)), "wkv needs contiguous tensors")
+    B = k.shape[0] if k.dim() == 3 else 1
+    T, C = k.shape[-2], k.shape[-1]
+    dev = w.device
+    with torch.cuda.device(dev):
+        nbytes = lib().rwkv_wkv4_workspace_bytes(B, T, C)
+        ws = workspace(dev, nbytes, "wkv4")
+        check(lib().rwkv_wkv4_seq(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                  r.data_ptr() if r is not None else None, y.data_ptr(), _DT[k.dtype],
+                                  aa.data_ptr(), bb.data_ptr(), pp.data_ptr(), ws.data_ptr() if ws is not None else None,
+                                  ws.numel() if ws is not None else 0, _stream(dev)), "wkv4_seq")
+    return y
+
+
 def wkv_forward_(B, T, C, w, u, k, v, y, aa, bb, pp):
     _require(k.dtype in (torch.float16, torch.float32) and k.dtype == v.dtype == y.dtype,
              "Only FP16 and FP32 are currently supported")
@@ -146,8 +189,11 @@ def wkv_forward_(B, T, C, w, u, k, v, y, aa, bb, pp):
     _require(all(t.is_contiguous() for t in (w, u, k, v, y, aa, bb, pp)), "wkv_forward needs contiguous tensors")
     dev = w.device
     with torch.cuda.device(dev):
-        check(lib().rwkv_wkv4_forward(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(),
-                                      _DT[k.dtype], aa.data_ptr(), bb.data_ptr(), pp.data_ptr(), _stream(dev)),
+        nbytes = lib().rwkv_wkv4_workspace_bytes(B, T, C)
+        ws = workspace(dev, nbytes, "wkv4")
+        check(lib().rwkv_wkv4_seq(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(), None, y.data_ptr(),
+                                  _DT[k.dtype], aa.data_ptr(), bb.data_ptr(), pp.data_ptr(),
+                                  ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, _stream(dev)),
               "wkv_forward")
 
 

@@ -334,6 +334,16 @@ int rwkv_mm8_stream_take_error(uint32_t* sync_words, void* stream, int* error_ou
 void rwkv_mm8_seq_set_path(int path);
 int rwkv_mm8_seq_tc_take_error(void* workspace, void* stream, int* error_out);
 size_t rwkv_mm8_seq_workspace_bytes(int64_t B, int64_t N, int64_t M);
+/* mm8_seq with a fused epilogue: RWKV_EPI_STORE, _SIGMOID, _RELU_SQ, _RESIDUAL (aux), _MUL_RESIDUAL (aux, aux2)
+ * or _SILU applied to the fp32 sums with the roundings listed for rwkv_mm8_one_batch; aux, aux2: [B, M] in
+ * `dtype`, rows aux_stride / aux2_stride elements apart; y may alias aux.  What ffn_seq / cuda_att_seq apply
+ * between matmuls (pkg/model.py:995-1004, 1346-1360). */
+int rwkv_mm8_seq_epi(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
+                     const uint8_t* w, int64_t w_stride,
+                     const void* mx, const void* rx, const void* my, const void* ry, int dtype,
+                     void* y, int64_t y_stride, int epilogue, const void* aux, int64_t aux_stride,
+                     const void* aux2, int64_t aux2_stride, float out_scale,
+                     void* workspace, size_t workspace_bytes, void* stream);
 int rwkv_mm8_seq(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_stride,
                  const uint8_t* w, int64_t w_stride,
                  const void* mx, const void* rx, const void* my, const void* ry, int dtype,
@@ -344,7 +354,17 @@ int rwkv_mm8_seq(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_strid
  * torch.ops.rwkv.wkv_forward (pkg/cuda/wrapper.cpp:27-48).
  * w = -exp(time_decay), u = time_first: fp32 [C].  k, v, y: [B, T, C] in kv_dtype
  * (RWKV_F16 or RWKV_F32).  aa, bb, pp: fp32 [B, C] state, updated in place.
+ * rwkv_wkv4_seq is the same with two additions.  `workspace` (rwkv_wkv4_workspace_bytes, 16-byte aligned;
+ * may be NULL) lets sequences of more than 32 steps run parallel in time: chunks of 32 steps are
+ * summarised from the empty state, every chunk folds the summaries before it into the caller's state
+ * and then runs its own steps (results equal the sequential recurrence up to fp32 rounding of that
+ * fold).  Without it the steps run one after the other, as rwkv_wkv4_forward does.  `r` (may be NULL;
+ * [B, T, C] in kv_dtype): y = r * wkv with the roundings of cuda_att_seq (pkg/model.py:1359-1360).
  * ------------------------------------------------------------------------------------- */
+size_t rwkv_wkv4_workspace_bytes(int64_t B, int64_t T, int64_t C);
+int rwkv_wkv4_seq(int64_t B, int64_t T, int64_t C, const float* w, const float* u,
+                  const void* k, const void* v, const void* r, void* y, int kv_dtype,
+                  float* aa, float* bb, float* pp, void* workspace, size_t workspace_bytes, void* stream);
 int rwkv_wkv4_forward(int64_t B, int64_t T, int64_t C, const float* w, const float* u,
                       const void* k, const void* v, void* y, int kv_dtype,
                       float* aa, float* bb, float* pp, void* stream);

@@ -474,3 +474,66 @@ def test_mm8_seq_single_pass_option(ops):
         lib().rwkv_mm8_seq_set_path(0)
     err = (y.float().cpu() - ref).abs()
     assert (err <= 2 * 2.0 ** -10 * ref.abs().clamp(min=1.0)).all(), err.max().item()
+
+
+# ------------------------------------------------------------------- fused seq epilogues, time-parallel WKV-v4
+@pytest.mark.parametrize("T", [3, 40, 200])
+def test_mm8_seq_fused_epilogues(ops, T):
+    """rwkv_mm8_seq_epi against the oracle's matmul followed by the torch ops of ffn_seq / cuda_att_seq
+    (pkg/model.py:995-1004, 1346-1360) in fp16, on all three kernels (CUDA cores, tensor cores, split K)."""
+    from chatrwkv_b200 import _lib
+    from tests.util import packed_case
+    N, M = 512, 768
+    cpu, dev = packed_case(N, M, seed=T)
+    g = torch.Generator().manual_seed(T)
+    x = torch.randn(T, N, generator=g).half()
+    aux = torch.randn(T, M, generator=g).half()
+    aux2 = torch.rand(T, M, generator=g).half()
+    base = orc.mm8_kernel(x, *cpu).half()
+    want = {
+        _lib.EPI_STORE: base,
+        _lib.EPI_SIGMOID: torch.sigmoid(base.float()).half(),
+        _lib.EPI_RELU_SQ: (torch.relu(base.float()) ** 2).half(),
+        _lib.EPI_RESIDUAL: ((aux.float() + base.float()).half().float() * 0.5).half(),
+        _lib.EPI_MUL_RESIDUAL: (aux.float() + (aux2.float() * base.float()).half().float()).half(),
+        _lib.EPI_SILU: (base.float() * torch.sigmoid(base.float())).half(),
+    }
+    for epi, ref in want.items():
+        a = aux.cuda().clone()
+        y = a if epi == _lib.EPI_RESIDUAL else torch.empty((T, M), dtype=torch.float16, device="cuda")   # in place over aux
+        ops.mm8_seq_epi(x.cuda(), *dev, y, epi, aux=a if epi in (_lib.EPI_RESIDUAL, _lib.EPI_MUL_RESIDUAL) else None,
+                        aux2=aux2.cuda() if epi == _lib.EPI_MUL_RESIDUAL else None,
+                        out_scale=0.5 if epi == _lib.EPI_RESIDUAL else 1.0)
+        d = (y.float().cpu() - ref.float()).abs()
+        assert (d <= ref.float().abs() * 2 ** -9 + 3e-3).all(), (epi, d.max().item())
+        assert (y.cpu() != ref).float().mean().item() < 0.06, epi
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("T", [33, 100, 1024, 2500])
+def test_wkv4_time_parallel_matches_sequential_oracle(ops, dtype, T):
+    """More than 32 steps run as chunks folded through their summaries; the oracle runs the recurrence step by
+    step.  Carried state, a second call, and the fused receptance product."""
+    C = 320
+    g = torch.Generator().manual_seed(T)
+    w = -torch.exp(torch.empty(C).uniform_(-5, 1, generator=g))
+    u = torch.empty(C).uniform_(-1, 1, generator=g)
+    aa, bb, pp = torch.zeros(C), torch.zeros(C), torch.zeros(C) - 1e30
+    daa, dbb, dpp = aa.cuda(), bb.cuda(), pp.cuda()
+    tol = 3e-3 if dtype == torch.float16 else 5e-5
+    for rep in range(2):
+        k = torch.randn(T, C, generator=g).to(dtype)
+        v = torch.randn(T, C, generator=g).to(dtype)
+        ref = orc.wkv4_forward(T, C, w, u, k, v, aa, bb, pp)
+        y = torch.empty((T, C), dtype=dtype, device="cuda")
+        if rep == 0:
+            torch.ops.rwkv.wkv_forward(1, T, C, w.cuda(), u.cuda(), k.cuda(), v.cuda(), y, daa, dbb, dpp)
+            torch.testing.assert_close(y.cpu().float(), ref.float(), rtol=tol, atol=tol)
+        else:
+            r = torch.rand(T, C, generator=g).to(dtype)
+            ops.wkv4_seq(w.cuda(), u.cuda(), k.cuda(), v.cuda(), y, daa, dbb, dpp, r=r.cuda())
+            want = (r.float() * ref.to(dtype).float()).to(dtype)
+            torch.testing.assert_close(y.cpu().float(), want.float(), rtol=tol, atol=tol)
+        torch.testing.assert_close(daa.cpu(), aa, rtol=2e-4, atol=2e-5)
+        torch.testing.assert_close(dbb.cpu(), bb, rtol=2e-4, atol=2e-5)
+        torch.testing.assert_close(dpp.cpu(), pp, rtol=1e-5, atol=1e-5)
