@@ -137,52 +137,82 @@ static inline void wkv4_chunks(int64_t T, int& Lc, int& NC) {
 }
 
 // ---------------------------------------------------------------------------------------
-// RWKV-5 / RWKV-6 (reference: rwkv5.cu:8-72, rwkv6.cu:8-71).
-// State S[h][i][j] (i = value index, j = key index).  A CTA owns one head and a slice of
-// ROWS value indices; a thread owns (i, quarter of j): N/4 state values in registers, and
-// the four quarters of y_t[i] = sum_j r[j] (u[j] k[j] v[i] + S[i][j]) meet by two shuffles.
-// r, k, (w,) v of TC time steps are staged in shared memory per barrier pair.
+// RWKV-5 / RWKV-6 (the recurrences of rwkv5.cu:32-68, rwkv6.cu:30-67 / pkg/model.py:1245-1251, 1324-1333).
+// State S[h][i][j] (i = value index, j = key index):
+//     y_t[i] = sum_j r_t[j] (u[j] k_t[j] v_t[i] + S[i][j]);   S[i][j] <- w_t[j] S[i][j] + k_t[j] v_t[i]
+// A CTA owns one head and a slice of ROWS value indices; a thread owns (i, quarter of j): N/4 state
+// values in registers, and the four quarters of y_t[i] meet by two shuffles.  r, k, (w,) v of TC time
+// steps are staged in shared memory per barrier pair.
+//
+// Parallel in time (more than one chunk): S_t is affine in S_{t-1}, so (1) every chunk runs its steps
+// from S = 0 and keeps its own sum and the product P[j] of its decays (PASS_SUM); (2) a scan kernel
+// turns the sums into the state at the start of every chunk, S <- P (.) S + sum, chunk after chunk
+// (64 cheap steps instead of T); (3) every chunk runs its steps again from that state and writes y
+// (PASS_OUT).  No division by decay products, so decays that underflow to 0 are harmless.
+// `model_layout`: the caller's state is [h][j][i] (the transpose: what RWKV.forward keeps in its state
+// list, pkg/model.py:1376, 1384) instead of the operator's [h][i][j].
 // ---------------------------------------------------------------------------------------
 constexpr int TC = 16;
+constexpr int kWkv56MaxChunks = 64;
+enum { PASS_WHOLE = 0, PASS_SUM = 1, PASS_OUT = 2 };
 
-template <typename F, int N, bool PER_TOKEN_W>
-__global__ void __launch_bounds__(128) wkv56_seq_kernel(int T, int C, int H, float* __restrict__ state,
-                                                        const F* __restrict__ r_, const F* __restrict__ k_,
-                                                        const F* __restrict__ v_, const float* __restrict__ w_,
-                                                        const F* __restrict__ u_, F* __restrict__ y_) {
+struct Wkv56Args {
+    int T, C, H, Lc, NC, model_layout;
+    const float* state;     // the caller's state
+    float* state_out;       // where the new state goes (PASS_WHOLE, last chunk of PASS_OUT); may be `state`
+    float* sums;            // [NC][H][N][N]: PASS_SUM writes chunk sums; the scan leaves the state after chunk c in [c]
+    float* prods;           // [NC][H][N]
+    float* start;           // [H][N][N] copy of the caller's state in operator layout (made by the scan)
+};
+
+template <typename FI, typename FO, int N, bool PER_TOKEN_W, int PASS>
+__global__ void __launch_bounds__(128) wkv56_seq_kernel(const Wkv56Args a, const FI* __restrict__ r_, const FI* __restrict__ k_,
+                                                        const FI* __restrict__ v_, const float* __restrict__ w_,
+                                                        const FO* __restrict__ u_, FO* __restrict__ y_) {
     constexpr int JQ = 4, NJ = N / JQ;
     constexpr int ROWS = (N >= 32) ? 32 : N;       // value indices per CTA
     constexpr int THREADS = ROWS * JQ;
-    const int slices = N / ROWS;
+    const int slices = N / ROWS, C = a.C;
     const int h = blockIdx.x / slices, i0 = (blockIdx.x % slices) * ROWS;
+    const int chunk = blockIdx.y;
     const int tid = threadIdx.x;
     if (tid >= THREADS) return;
     const int il = tid / JQ, jq = tid % JQ, i = i0 + il, jb = jq * NJ;
+    const int t_begin = PASS == PASS_WHOLE ? 0 : chunk * a.Lc;
+    const int t_end = PASS == PASS_WHOLE ? a.T : min(a.T, t_begin + a.Lc);
 
     __shared__ float sr[TC][N], sk[TC][N], sw[PER_TOKEN_W ? TC : 1][N], sv[TC][ROWS], su[N];
 
-    float S[NJ];
-    float* sp = state + ((long long)h * N + i) * N + jb;
+    float S[NJ], P[NJ];
+    // where this thread's state values live in the caller's buffer
+    auto state_at = [&](int j) -> long long {
+        return a.model_layout ? ((long long)h * N + jb + j) * N + i : ((long long)h * N + i) * N + jb + j;
+    };
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) S[j] = sp[j];
+    for (int j = 0; j < NJ; ++j) {
+        P[j] = 1.f;
+        if (PASS == PASS_SUM) S[j] = 0.f;
+        else if (PASS == PASS_WHOLE) S[j] = a.state[state_at(j)];
+        else S[j] = (chunk == 0 ? a.start : a.sums + (long long)(chunk - 1) * a.H * N * N)[((long long)h * N + i) * N + jb + j];
+    }
     for (int j = tid; j < N; j += THREADS) {
-        su[j] = to_f32<F>(u_[h * N + j]);
+        su[j] = to_f32<FO>(u_[h * N + j]);
         if (!PER_TOKEN_W) sw[0][j] = w_[h * N + j];
     }
 
-    for (int t0 = 0; t0 < T; t0 += TC) {
-        const int nt = min(TC, T - t0);
+    for (int t0 = t_begin; t0 < t_end; t0 += TC) {
+        const int nt = min(TC, t_end - t0);
         __syncthreads();
         for (int e = tid; e < nt * N; e += THREADS) {
             const int tt = e / N, j = e % N;
             const long long g = (long long)(t0 + tt) * C + h * N + j;
-            sr[tt][j] = to_f32<F>(r_[g]);
-            sk[tt][j] = to_f32<F>(k_[g]);
+            sr[tt][j] = to_f32<FI>(r_[g]);
+            sk[tt][j] = to_f32<FI>(k_[g]);
             if (PER_TOKEN_W) sw[tt][j] = w_[g];
         }
         for (int e = tid; e < nt * ROWS; e += THREADS) {
             const int tt = e / ROWS, ii = e % ROWS;
-            sv[tt][ii] = to_f32<F>(v_[(long long)(t0 + tt) * C + h * N + i0 + ii]);
+            sv[tt][ii] = to_f32<FI>(v_[(long long)(t0 + tt) * C + h * N + i0 + ii]);
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
@@ -192,27 +222,99 @@ __global__ void __launch_bounds__(128) wkv56_seq_kernel(int T, int C, int H, flo
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {
                 const float x = sk[tt][jb + j] * v;
-                y = fmaf(sr[tt][jb + j], fmaf(su[jb + j], x, S[j]), y);
+                if (PASS != PASS_SUM) y = fmaf(sr[tt][jb + j], fmaf(su[jb + j], x, S[j]), y);
                 S[j] = fmaf(S[j], wrow[jb + j], x);
+                if (PASS == PASS_SUM) P[j] *= wrow[jb + j];
             }
-            y += __shfl_xor_sync(0xffffffffu, y, 1);
-            y += __shfl_xor_sync(0xffffffffu, y, 2);
-            if (jq == 0) y_[(long long)(t0 + tt) * C + h * N + i] = from_f32<F>(y);
+            if (PASS != PASS_SUM) {
+                y += __shfl_xor_sync(0xffffffffu, y, 1);
+                y += __shfl_xor_sync(0xffffffffu, y, 2);
+                if (jq == 0) y_[(long long)(t0 + tt) * C + h * N + i] = from_f32<FO>(y);
+            }
         }
     }
+    if (PASS == PASS_SUM) {
+        float* out = a.sums + (long long)chunk * a.H * N * N + ((long long)h * N + i) * N + jb;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) sp[j] = S[j];
+        for (int j = 0; j < NJ; ++j) out[j] = S[j];
+        if (i == 0) {
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) a.prods[((long long)chunk * a.H + h) * N + jb + j] = P[j];
+        }
+    } else if (PASS == PASS_WHOLE || chunk == a.NC - 1) {
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) a.state_out[state_at(j)] = S[j];
+    }
 }
 
-template <typename F, bool PER_TOKEN_W>
-int launch56(int T, int C, int H, float* state, const void* r, const void* k, const void* v,
-             const float* w, const void* u, void* y, cudaStream_t st) {
+// start <- the caller's state (operator layout); sums[c] <- state after chunk c, for c = 0 .. NC - 2
+template <int N>
+__global__ void __launch_bounds__(128) wkv56_scan_kernel(const Wkv56Args a) {
+    constexpr int JQ = 4, NJ = N / JQ;
+    constexpr int ROWS = (N >= 32) ? 32 : N;
+    constexpr int THREADS = ROWS * JQ;
+    const int slices = N / ROWS;
+    const int h = blockIdx.x / slices, i0 = (blockIdx.x % slices) * ROWS;
+    const int tid = threadIdx.x;
+    if (tid >= THREADS) return;
+    const int il = tid / JQ, jq = tid % JQ, i = i0 + il, jb = jq * NJ;
+    float S[NJ];
+    const long long at = ((long long)h * N + i) * N + jb;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        S[j] = a.model_layout ? a.state[((long long)h * N + jb + j) * N + i] : a.state[at + j];
+        a.start[at + j] = S[j];
+    }
+    for (int c = 0; c + 1 < a.NC; ++c) {
+        float* sm = a.sums + (long long)c * a.H * N * N + at;
+        const float* pr = a.prods + ((long long)c * a.H + h) * N + jb;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            S[j] = fmaf(S[j], pr[j], sm[j]);
+            sm[j] = S[j];
+        }
+    }
+}
+
+static inline void wkv56_chunks(int64_t T, int& Lc, int& NC) {
+    Lc = T <= 64 * kWkv56MaxChunks ? 64 : int((T + kWkv56MaxChunks - 1) / kWkv56MaxChunks);
+    Lc = (Lc + TC - 1) / TC * TC;
+    NC = int((T + Lc - 1) / Lc);
+}
+
+static inline size_t wkv56_ws_bytes(int64_t T, int64_t C, int64_t H) {
+    int Lc, NC;
+    wkv56_chunks(T, Lc, NC);
+    if (NC == 1) return 0;
+    const size_t N = size_t(C / H);
+    return (size_t(NC) * size_t(H) * N * N + size_t(NC) * size_t(H) * N + size_t(H) * N * N) * sizeof(float);
+}
+
+template <typename FI, typename FO, bool PER_TOKEN_W>
+int launch56(int T, int C, int H, const float* state, float* state_out, const void* r, const void* k, const void* v,
+             const float* w, const void* u, void* y, int model_layout, void* workspace, size_t workspace_bytes, cudaStream_t st) {
     const int N = C / H;
-#define RWKV_L56(NN)                                                                               \
-    {                                                                                              \
-        constexpr int ROWS = (NN >= 32) ? 32 : NN;                                                 \
-        wkv56_seq_kernel<F, NN, PER_TOKEN_W><<<H * (NN / ROWS), ROWS * 4, 0, st>>>(               \
-            T, C, H, state, (const F*)r, (const F*)k, (const F*)v, w, (const F*)u, (F*)y);        \
+    Wkv56Args a;
+    a.T = T; a.C = C; a.H = H; a.model_layout = model_layout; a.state = state; a.state_out = state_out;
+    wkv56_chunks(T, a.Lc, a.NC);
+    if (a.NC > 1 && (workspace == nullptr || workspace_bytes < wkv56_ws_bytes(T, C, H))) { a.NC = 1; a.Lc = T; }
+    a.sums = static_cast<float*>(workspace);
+    a.prods = a.NC > 1 ? a.sums + (size_t)a.NC * H * N * N : nullptr;
+    a.start = a.NC > 1 ? a.prods + (size_t)a.NC * H * N : nullptr;
+#define RWKV_L56(NN)                                                                                          \
+    {                                                                                                         \
+        constexpr int ROWS = (NN >= 32) ? 32 : NN;                                                            \
+        const unsigned gx = unsigned(H * (NN / ROWS));                                                        \
+        if (a.NC == 1) {                                                                                      \
+            wkv56_seq_kernel<FI, FO, NN, PER_TOKEN_W, PASS_WHOLE><<<gx, ROWS * 4, 0, st>>>(                  \
+                a, (const FI*)r, (const FI*)k, (const FI*)v, w, (const FO*)u, (FO*)y);                        \
+        } else {                                                                                              \
+            wkv56_seq_kernel<FI, FO, NN, PER_TOKEN_W, PASS_SUM><<<dim3(gx, unsigned(a.NC - 1)), ROWS * 4, 0, st>>>( \
+                a, (const FI*)r, (const FI*)k, (const FI*)v, w, (const FO*)u, (FO*)y);                        \
+            wkv56_scan_kernel<NN><<<gx, ROWS * 4, 0, st>>>(a);                                                \
+            wkv56_seq_kernel<FI, FO, NN, PER_TOKEN_W, PASS_OUT><<<dim3(gx, unsigned(a.NC)), ROWS * 4, 0, st>>>(   \
+                a, (const FI*)r, (const FI*)k, (const FI*)v, w, (const FO*)u, (FO*)y);                        \
+        }                                                                                                     \
     }
     switch (N) {
     case 16: RWKV_L56(16) break;
@@ -225,18 +327,21 @@ int launch56(int T, int C, int H, float* state, const void* r, const void* k, co
     return rwkv_launch_status();
 }
 
+// in_dtype: r, k, v; out_dtype: u, y (the reference's operators use one dtype for all five)
 template <bool PER_TOKEN_W>
-int forward56(int64_t B, int64_t T, int64_t C, int64_t H, float* state, const void* r, const void* k,
-              const void* v, const float* w, const void* u, void* y, int dtype, void* stream) {
+int forward56(int64_t B, int64_t T, int64_t C, int64_t H, const float* state, float* state_out, const void* r, const void* k,
+              const void* v, const float* w, const void* u, void* y, int in_dtype, int out_dtype, int model_layout,
+              void* workspace, size_t workspace_bytes, void* stream) {
     RWKV_CHECK_ARG(B == 1 && T >= 1 && C >= 1 && H >= 1 && C % H == 0 && T * C <= (int64_t)INT32_MAX * 16);
-    RWKV_CHECK_ARG(state && r && k && v && w && u && y);
+    RWKV_CHECK_ARG(state && state_out && r && k && v && w && u && y);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    switch (dtype) {
-    case RWKV_F32: return launch56<float, PER_TOKEN_W>(int(T), int(C), int(H), state, r, k, v, w, u, y, st);
-    case RWKV_F16: return launch56<__half, PER_TOKEN_W>(int(T), int(C), int(H), state, r, k, v, w, u, y, st);
-    case RWKV_BF16: return launch56<__nv_bfloat16, PER_TOKEN_W>(int(T), int(C), int(H), state, r, k, v, w, u, y, st);
-    default: return RWKV_ERR_INVALID_ARG;
-    }
+#define RWKV_F56(FI, FO) return launch56<FI, FO, PER_TOKEN_W>(int(T), int(C), int(H), state, state_out, r, k, v, w, u, y, model_layout, workspace, workspace_bytes, st)
+    if (in_dtype == RWKV_F32 && out_dtype == RWKV_F32) RWKV_F56(float, float);
+    if (in_dtype == RWKV_F16 && out_dtype == RWKV_F16) RWKV_F56(__half, __half);
+    if (in_dtype == RWKV_BF16 && out_dtype == RWKV_BF16) RWKV_F56(__nv_bfloat16, __nv_bfloat16);
+    if (in_dtype == RWKV_F16 && out_dtype == RWKV_F32) RWKV_F56(__half, float);
+#undef RWKV_F56
+    return RWKV_ERR_INVALID_ARG;
 }
 
 }  // namespace
@@ -292,11 +397,23 @@ extern "C" int rwkv_wkv4_forward(int64_t B, int64_t T, int64_t C, const float* w
 extern "C" int rwkv_wkv5_forward(int64_t B, int64_t T, int64_t C, int64_t H, float* state,
                                  const void* r, const void* k, const void* v, const float* w, const void* u,
                                  void* y, int dtype, void* stream) {
-    return forward56<false>(B, T, C, H, state, r, k, v, w, u, y, dtype, stream);
+    return forward56<false>(B, T, C, H, state, state, r, k, v, w, u, y, dtype, dtype, 0, nullptr, 0, stream);
 }
 
 extern "C" int rwkv_wkv6_forward(int64_t B, int64_t T, int64_t C, int64_t H, float* state,
                                  const void* r, const void* k, const void* v, const float* w, const void* u,
                                  void* y, int dtype, void* stream) {
-    return forward56<true>(B, T, C, H, state, r, k, v, w, u, y, dtype, stream);
+    return forward56<true>(B, T, C, H, state, state, r, k, v, w, u, y, dtype, dtype, 0, nullptr, 0, stream);
+}
+
+extern "C" size_t rwkv_wkv56_workspace_bytes(int64_t T, int64_t C, int64_t H) {
+    if (T < 1 || C < 1 || H < 1 || C % H != 0) return 0;
+    return wkv56_ws_bytes(T, C, H);
+}
+
+extern "C" int rwkv_wkv56_seq(int per_token_w, int64_t T, int64_t C, int64_t H, const float* state, float* state_out, int model_layout,
+                              const void* r, const void* k, const void* v, const float* w, const void* u, void* y,
+                              int in_dtype, int out_dtype, void* workspace, size_t workspace_bytes, void* stream) {
+    return per_token_w ? forward56<true>(1, T, C, H, state, state_out, r, k, v, w, u, y, in_dtype, out_dtype, model_layout, workspace, workspace_bytes, stream)
+                       : forward56<false>(1, T, C, H, state, state_out, r, k, v, w, u, y, in_dtype, out_dtype, model_layout, workspace, workspace_bytes, stream);
 }

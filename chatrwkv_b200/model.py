@@ -787,51 +787,67 @@ class RWKV:
         return x + out
 
     def _att_seq_v56(self, x, st2, i):
-        """cuda_att_seq_v5_2 / cuda_att_seq_v6_0 (model.py:1363-1439) and, with T = 1, the
-        one-step forms.  `st2` = [att_xx, att_kv]; both entries are replaced."""
-        w, a = self.w, self.args
-        T, C = x.shape
+        """cuda_att_seq_v5_2 / cuda_att_seq_v6_0 (model.py:1363-1439).  `st2` = [att_xx, att_kv]; the first entry is
+        replaced, the matrix state is updated in place in the model's [H, key, value] layout.  Kernels of this
+        library throughout; the four small low-rank products of RWKV-6 (ranks 32..160) are plain fp16 library GEMMs
+        as in the reference (`@`, `bmm`)."""
+        import ctypes as C
+        w, a, L = self.w, self.args, lib()
+        T, D = x.shape
         H = a.n_head
+        N = a.n_att // H
+        dev = x.device
         bb, att = f"blocks.{i}.", f"blocks.{i}.att."
+        stream = torch.cuda.current_stream(dev).cuda_stream
         new_sx = torch.empty_like(st2[0])
+        h = lambda *shape: torch.empty(shape, dtype=torch.float16, device=dev)
         if self.version == 6:
-            xx = torch.empty_like(x)
-            xxx = torch.empty_like(x)
+            xx, xxx = h(T, D), h(T, D)
             self._ln_mix(T, x, st2[0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 1, [w[att + "time_maa_x"]], [xxx],
                          xx_out=xx, new_state=new_sx)
-            sx = torch.cat((st2[0].unsqueeze(0), xx[:-1, :])) - xx
-            xxx = torch.tanh(xxx @ w[att + "time_maa_w1"]).view(T, 5, -1).transpose(0, 1)
-            xxx = torch.bmm(xxx, w[att + "time_maa_w2"]).view(5, T, -1)
-            mw, mk, mv, mr, mg = xxx.unbind(dim=0)
-            wx = xx + sx * (w[att + "time_maa_w"] + mw)
-            kx = xx + sx * (w[att + "time_maa_k"] + mk)
-            vx = xx + sx * (w[att + "time_maa_v"] + mv)
-            rx = xx + sx * (w[att + "time_maa_r"] + mr)
-            gx = xx + sx * (w[att + "time_maa_g"] + mg)
+            # low-rank offsets of the five mixes: tanh(xxx @ w1) as [5, T, Lm], times w2 [5, Lm, D]
+            w1, w2 = w[att + "time_maa_w1"], w[att + "time_maa_w2"]
+            Lm = w2.shape[1]
+            h1, h1t = h(T, 5 * Lm), h(5, T, Lm)
+            torch.ops.rwkv.gemm_fp16_cublas(xxx, w1, h1)
+            check(L.rwkv_tanh_regroup_f16(T, 5, Lm, h1.data_ptr(), h1t.data_ptr(), stream), "tanh")
+            m5 = h(5, T, D)
+            torch.ops.rwkv.gemm_fp16_cublas(h1t, w2, m5)
+            mixes = h(5, T, D)
+            maa5 = (C.c_void_p * 5)(*[w[att + "time_maa_" + n].data_ptr() for n in "wkvrg"])
+            out5 = (C.c_void_p * 5)(*[mixes[j].data_ptr() for j in range(5)])
+            check(L.rwkv_v6_seq_mix(T, D, xx.data_ptr(), xx.stride(0), st2[0].data_ptr(), m5.data_ptr(), maa5, out5, stream),
+                  "v6_seq_mix")
+            wx, kx, vx, rx, gx = mixes.unbind(0)
+            # per-token decay exp(-exp(time_decay + tanh(wx @ dw1) @ dw2))
+            dw1, dw2 = w[att + "time_decay_w1"], w[att + "time_decay_w2"]
+            h2 = h(T, dw1.shape[1])
+            torch.ops.rwkv.gemm_fp16_cublas(wx, dw1, h2)
+            check(L.rwkv_tanh_regroup_f16(T, 1, h2.shape[1], h2.data_ptr(), h2.data_ptr(), stream), "tanh")
+            d2 = h(T, D)
+            torch.ops.rwkv.gemm_fp16_cublas(h2, dw2, d2)
+            decay = torch.empty((T, D), dtype=torch.float32, device=dev)
+            check(L.rwkv_v6_seq_decay(T, D, w[att + "time_decay"].data_ptr(), d2.data_ptr(), decay.data_ptr(), stream), "v6_seq_decay")
         else:
             kx, vx, rx, gx = (torch.empty_like(x) for _ in range(4))
             self._ln_mix(T, x, st2[0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 0,
                          [w[att + f"time_mix_{n}"] for n in "kvrg"], [kx, vx, rx, gx], new_state=new_sx)
-        r = self._mm_seq(rx, att + "receptance.weight", torch.float32)
-        k = self._mm_seq(kx, att + "key.weight", torch.float32)
-        v = self._mm_seq(vx, att + "value.weight", torch.float32)
-        g = F.silu(self._mm_seq(gx, att + "gate.weight"))
-        S = st2[1].transpose(-1, -2).contiguous()          # kernel layout [H, value, key]
-        y = torch.empty((T, C), dtype=torch.float32, device=x.device)
-        u = w[att + "time_first"]
-        if self.version == 6:
-            ww = w[att + "time_decay"].view(1, C) + (torch.tanh(wx @ w[att + "time_decay_w1"]) @ w[att + "time_decay_w2"]).float()
-            eew = torch.exp(-torch.exp(ww.float())).contiguous()
-            torch.ops.rwkv6.forward_fp32(1, T, C, H, S, r, k, v, eew, u.reshape(-1).contiguous(), y)
-        else:
-            torch.ops.rwkv5.forward_fp32(1, T, C, H, S, r, k, v, w[att + "time_decay"].reshape(-1).contiguous(),
-                                         u.reshape(-1).contiguous(), y)
-        out = F.group_norm(y, num_groups=H, weight=w[att + "ln_x.weight"], bias=w[att + "ln_x.bias"], eps=64e-5)
-        out = out.to(dtype=x.dtype) * g
-        out = self._mm_seq(out, att + "output.weight")
+            decay = w[att + "time_decay"].reshape(-1)
+        r = self._mm_epi(rx, att + "receptance.weight", EPI_STORE)        # fp16-rounded r, k, v: the kernel widens them
+        k = self._mm_epi(kx, att + "key.weight", EPI_STORE)               # (model.py:1413, 1425-1427)
+        v = self._mm_epi(vx, att + "value.weight", EPI_STORE)
+        g = self._mm_epi(gx, att + "gate.weight", EPI_SILU)
+        y = torch.empty((T, D), dtype=torch.float32, device=dev)
+        S_in = st2[1] if st2[1].is_contiguous() else st2[1].contiguous()
+        S = torch.empty_like(S_in)                  # the caller's state stays as it is, as with the reference's copy
+        ops.wkv56_seq(self.version == 6, H, S_in, r, k, v, decay, w[att + "time_first"].reshape(-1), y, model_layout=True,
+                      state_out=S)
+        out = h(T, D)
+        check(L.rwkv_v56_seq_gn_gate(T, H, N, y.data_ptr(), w[att + "ln_x.weight"].data_ptr(), w[att + "ln_x.bias"].data_ptr(),
+                                     g.data_ptr(), out.data_ptr(), 64e-5, stream), "gn_gate")
         st2[0] = new_sx
-        st2[1] = S.transpose(-1, -2)
-        return x + out
+        st2[1] = S
+        return self._mm_epi(out, att + "output.weight", EPI_RESIDUAL, aux=x, out=x)
 
     def _ffn_seq(self, x, sx, i):
         """ffn_seq / ffn_seq_v6 (model.py:995-1004, 1019-1029)."""

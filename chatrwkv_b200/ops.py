@@ -222,12 +222,27 @@ def _wkv56(which, dtype):
         _require(state.dtype == torch.float32 and w.dtype == torch.float32, "state and w must be fp32")
         _require(r.dtype == k.dtype == v.dtype == u.dtype == y.dtype == dtype, f"r, k, v, u, y must be {dtype}")
         _require(all(t.is_contiguous() for t in (state, r, k, v, w, u, y)), "needs contiguous tensors")
-        dev = state.device
-        with torch.cuda.device(dev):
-            check(getattr(lib(), fn_name)(B, T, C, H, state.data_ptr(), r.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                          w.data_ptr(), u.data_ptr(), y.data_ptr(), _DT[dtype], _stream(dev)),
-                  fn_name)
+        _require(B == 1, "B must be 1 (the reference's kernels are wrong for B > 1 as well, rwkv6.cu:17)")
+        wkv56_seq(which == 6, H, state, r, k, v, w, u, y, model_layout=False)
     return impl
+
+
+def wkv56_seq(per_token_w, H, state, r, k, v, w, u, y, model_layout=False, state_out=None):
+    """WKV5 (w [H*N]) or WKV6 (w [T, C]) over r, k, v [T, C]; state fp32 [H, N, N] updated in place, in the operators'
+    [H, value, key] layout or, with `model_layout`, the [H, key, value] layout of the model's state list.  r, k, v
+    may be fp16 with fp32 u, y (the model's sequence path).  `state_out`: where the new state goes (default: in
+    place).  Parallel in time from 65 steps on."""
+    T, C = r.shape[-2], r.shape[-1]
+    dev = state.device
+    with torch.cuda.device(dev):
+        nbytes = lib().rwkv_wkv56_workspace_bytes(T, C, H)
+        ws = workspace(dev, nbytes, "wkv56")
+        check(lib().rwkv_wkv56_seq(1 if per_token_w else 0, T, C, H, state.data_ptr(),
+                                   (state_out if state_out is not None else state).data_ptr(), 1 if model_layout else 0,
+                                   r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(), y.data_ptr(),
+                                   _DT[r.dtype], _DT[y.dtype], ws.data_ptr() if ws is not None else None,
+                                   ws.numel() if ws is not None else 0, _stream(dev)), "wkv56_seq")
+    return y
 
 
 # ---------------------------------------------------------------------------------------

@@ -370,6 +370,36 @@ int rwkv_wkv4_forward(int64_t B, int64_t T, int64_t C, const float* w, const flo
                       float* aa, float* bb, float* pp, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * WKV5 / WKV6 for the model's sequence path, and the pointwise pieces around them — replace what
+ * cuda_att_seq_v5_2 / cuda_att_seq_v6_0 do in torch between the matmuls (pkg/model.py:1379-1439).
+ *
+ * rwkv_wkv56_seq: the recurrence of rwkv_wkv5_forward (per_token_w = 0, w [H*N]) or rwkv_wkv6_forward
+ * (per_token_w = 1, w [T, C]) with r, k, v in in_dtype and u, y in out_dtype (the operators' three
+ * uniform dtypes, or fp16 in / fp32 out: the model's fp16-rounded r, k, v without a widened copy,
+ * pkg/model.py:1413, 1425-1427).  model_layout = 1: `state` is [H, key, value], the transpose the model
+ * keeps in its state list (pkg/model.py:1376, 1384).  The new state goes to state_out (may be `state`:
+ * in place; a separate buffer leaves the caller's state untouched, as the reference's copy does).  With `workspace`
+ * (rwkv_wkv56_workspace_bytes, 16-byte aligned; NULL allowed) sequences of more than 64 steps run
+ * parallel in time: chunk sums from an empty state, a scan of the chunk-start states, the chunks again
+ * for y (results equal the sequential recurrence up to fp32 rounding).
+ * rwkv_v6_seq_mix: the five token-shift mixes from xx [T, D] (LayerNorm output), the previous token's
+ * xx (`state` [D]), the low-rank offsets m [5, T, D] and time_maa_{w,k,v,r,g}; out5: five [T, D].
+ * rwkv_tanh_regroup_f16: out[g, t, r] = tanh(in[t, g, r]) (G = 1: plain tanh, in place allowed).  rwkv_v6_seq_decay: out[T, D] = exp(-exp(time_decay + float(d2))) in fp32.
+ * rwkv_v56_seq_gn_gate: group-norm of y [T, H*N] over each head's N channels (eps), ln_x weight / bias in
+ * fp32, rounded to fp16 and multiplied with the gate g [T, H*N] in fp16.
+ * ------------------------------------------------------------------------------------- */
+size_t rwkv_wkv56_workspace_bytes(int64_t T, int64_t C, int64_t H);
+int rwkv_wkv56_seq(int per_token_w, int64_t T, int64_t C, int64_t H, const float* state, float* state_out, int model_layout,
+                   const void* r, const void* k, const void* v, const float* w, const void* u, void* y,
+                   int in_dtype, int out_dtype, void* workspace, size_t workspace_bytes, void* stream);
+int rwkv_v6_seq_mix(int64_t T, int64_t D, const void* xx, int64_t xx_stride, const void* state, const void* m,
+                    const void* const* maa5, void* const* out5, void* stream);
+int rwkv_tanh_regroup_f16(int64_t T, int64_t G, int64_t R, const void* in, void* out, void* stream);
+int rwkv_v6_seq_decay(int64_t T, int64_t D, const float* time_decay, const void* d2, float* out, void* stream);
+int rwkv_v56_seq_gn_gate(int64_t T, int64_t H, int64_t N, const float* y, const float* ln_w, const float* ln_b,
+                         const void* g, void* out, float eps, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * WKV5 / WKV6 — replace cuda_forward_{bf16,fp16,fp32} of pkg/cuda/rwkv5.cu:8-88 and
  * pkg/cuda/rwkv6.cu:8-87 behind rwkv5.forward_* / rwkv6.forward_*
  * (pkg/cuda/rwkv5_op.cpp:12-34, pkg/cuda/rwkv6_op.cpp:12-34).
