@@ -189,6 +189,9 @@ def main():
     ap.add_argument("--sequences", type=int, default=0,
                     help="S independent sequences dealt to the ranks (s mod N), each with its own prefill of --prompt "
                          "tokens and --steps greedy tokens; value = decoded tokens of all sequences / time")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="batched decode: B sequences per GPU advance one token per step through RWKV.forward_batch; "
+                         "value = B x GPUs x steps / time")
     ap.add_argument("--layers", type=int, default=0,
                     help="profiling aid: build only this many layers of the shape (the line is then not a bench result)")
     a = ap.parse_args()
@@ -253,6 +256,41 @@ def main():
             logits, state = model.forward(tok, state)
             tok = torch.argmax(logits).reshape(1)
         return tok, state
+
+    if a.batch > 0:
+        # ---- batched decode: B sequences per GPU, one token each per step, no prefill (zero states) ----
+        B = a.batch
+        tok = torch.tensor(synth.make_tokens(B, V, 2000 + rank), dtype=torch.int64, device=dev)
+        logits, bstate = model.forward_batch(tok, None)
+        for _ in range(a.warmup):
+            logits, bstate = model.forward_batch(torch.argmax(logits, dim=-1), bstate)
+        sampler = ClockSampler(local_rank)
+        barrier()
+        sampler.start()
+        ev0.record()
+        for _ in range(a.steps):
+            logits, bstate = model.forward_batch(torch.argmax(logits, dim=-1), bstate)
+        ev1.record()
+        barrier()
+        clocks = sampler.stop()
+        ms = ev0.elapsed_time(ev1)
+        times = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        ms = times.item()
+        if rank == 0:
+            line = {"metric": metric.replace("decode_tokens", f"batch{B}_decode_tokens"), "unit": "tokens/s", "n_gpus": world,
+                    "value": world * B * a.steps / (ms / 1e3), "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps,
+                    "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                    "config": {"workload": f"rwkv{a.shape} shape 'cuda fp16i8': {B} independent sequences per GPU decoded one token "
+                                           f"per step together (RWKV.forward_batch), greedy, from empty states",
+                               "parallelism": "independent batches, one per GPU, no collective",
+                               "l2": f"inputs larger than L2 ({weight_gb:.2f} GB of packed weights streamed per step)"},
+                    "per_sequence_tokens_per_s": a.steps / (ms / 1e3), "clocks": clocks, "graph": False}
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     if a.sequences > 0:
         # ---- S independent sequences over the ranks, each prefill + greedy decode, one after the other ----

@@ -97,11 +97,13 @@ SIGNATURES = {
     "rwkv_wkv6_forward": (_i32, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp]),
     "rwkv_wkv56_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "rwkv_wkv56_seq": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _sz, _vp]),
-    "rwkv_v6_seq_mix": (_i32, [_i64, _i64, _vp, _i64, _vp, _vp, C.POINTER(_vp), C.POINTER(_vp), _vp]),
+    "rwkv_v6_seq_mix": (_i32, [_i64, _i64, _vp, _i64, _vp, _i64, _vp, C.POINTER(_vp), C.POINTER(_vp), _vp]),
     "rwkv_tanh_regroup_f16": (_i32, [_i64, _i64, _i64, _vp, _vp, _vp]),
     "rwkv_v6_seq_decay": (_i32, [_i64, _i64, _vp, _vp, _vp, _vp]),
     "rwkv_v56_seq_gn_gate": (_i32, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _f, _vp]),
     "rwkv_ln_mix": (_i32, [_i64, _i64, _vp, _i64, _vp, _vp, _vp, _i32, _i32, C.POINTER(_vp), _i64, C.POINTER(_vp), _i64, _vp, _i64, _vp, _vp]),
+    "rwkv_ln_mix_rows": (_i32, [_i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i32, _i32, C.POINTER(_vp), _i64, C.POINTER(_vp), _i64, _vp, _i64,
+                                _vp, _vp]),
     "rwkv_wkv4_one": (_i32, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "rwkv_v6_scratch_bytes": (_sz, [_i64, _i64]),
     "rwkv_v6_att_pre": (_i32, [_i64, _i64, _i64] + [_vp] * 17),

@@ -53,6 +53,8 @@ __device__ __forceinline__ void layer_norm_row(const __half* __restrict__ x, int
 struct LnMixArgs {
     const __half* x; long long x_stride;      // [T, D]
     const __half* sx;                          // [D] previous token's LayerNorm output (state)
+    long long sx_stride;                       // 0: the rows are consecutive tokens of one sequence; else row t is a
+                                               // sequence of its own whose previous token's output is sx + t * sx_stride
     const __half* ln_w; const __half* ln_b;
     const __half* mix[5];                      // [D] each (or [T, D] when mix_stride != 0)
     long long mix_stride;
@@ -73,11 +75,11 @@ __global__ void __launch_bounds__(kLnThreads) ln_mix_kernel(const LnMixArgs a) {
     float xx[PER], prev[PER];
     layer_norm_row<PER>(a.x + (long long)t * a.x_stride, a.D, a.ln_w, a.ln_b, xx, sh);
     if (a.n_mix > 0) {
-        if (t == 0) {
+        if (t == 0 || a.sx_stride != 0) {
 #pragma unroll
             for (int i = 0; i < PER; ++i) {
                 const int d = threadIdx.x + i * kLnThreads;
-                prev[i] = d < a.D ? __half2float(a.sx[d]) : 0.f;
+                prev[i] = d < a.D ? __half2float(a.sx[(long long)t * a.sx_stride + d]) : 0.f;
             }
         } else {
             layer_norm_row<PER>(a.x + (long long)(t - 1) * a.x_stride, a.D, a.ln_w, a.ln_b, prev, sh);
@@ -130,11 +132,19 @@ extern "C" int rwkv_ln_mix(int64_t T, int64_t D, const void* x, int64_t x_stride
                            const void* ln_w, const void* ln_b, int mode, int n_mix,
                            const void* const* mix, int64_t mix_stride, void* const* out, int64_t out_stride,
                            void* xx_out, int64_t xx_stride, void* new_state, void* stream) {
+    return rwkv_ln_mix_rows(T, D, x, x_stride, sx, 0, ln_w, ln_b, mode, n_mix, mix, mix_stride, out, out_stride, xx_out, xx_stride,
+                            new_state, stream);
+}
+
+extern "C" int rwkv_ln_mix_rows(int64_t T, int64_t D, const void* x, int64_t x_stride, const void* sx, int64_t sx_stride,
+                                const void* ln_w, const void* ln_b, int mode, int n_mix,
+                                const void* const* mix, int64_t mix_stride, void* const* out, int64_t out_stride,
+                                void* xx_out, int64_t xx_stride, void* new_state, void* stream) {
     RWKV_CHECK_ARG(T >= 1 && T <= INT32_MAX && D >= 1 && D <= kLnThreads * kLnMaxPer);
     RWKV_CHECK_ARG(x && ln_w && ln_b && n_mix >= 0 && n_mix <= 5 && (mode == 0 || mode == 1));
     RWKV_CHECK_ARG(n_mix == 0 || (sx && mix && out));
     LnMixArgs a;
-    a.x = (const __half*)x; a.x_stride = x_stride; a.sx = (const __half*)sx;
+    a.x = (const __half*)x; a.x_stride = x_stride; a.sx = (const __half*)sx; a.sx_stride = sx_stride;
     a.ln_w = (const __half*)ln_w; a.ln_b = (const __half*)ln_b;
     for (int m = 0; m < 5; ++m) {
         a.mix[m] = m < n_mix ? (const __half*)mix[m] : nullptr;

@@ -9,9 +9,11 @@ constexpr int kPw = 256;
 
 // The five data-dependent token-shift mixes of RWKV-6 for T rows:
 //   sx_t = (t == 0 ? state : xx_{t-1}) - xx_t;  out_j[t] = xx_t + sx_t * (maa_j + m_j[t])     j = w, k, v, r, g
-// (pkg/model.py:1407, 1414-1420); m = the low-rank product [5, T, D].
+// (pkg/model.py:1407, 1414-1420); m = the low-rank product [5, T, D].  state_stride != 0: every row is a
+// sequence of its own with its previous token's xx at state + t * state_stride (batched decode).
 __global__ void __launch_bounds__(kPw) v6_seq_mix_kernel(int T, int D, const __half* __restrict__ xx, long long xx_stride,
-                                                         const __half* __restrict__ state, const __half* __restrict__ m,
+                                                         const __half* __restrict__ state, long long state_stride,
+                                                         const __half* __restrict__ m,
                                                          const __half* m0, const __half* m1, const __half* m2, const __half* m3,
                                                          const __half* m4, __half* o0, __half* o1, __half* o2, __half* o3, __half* o4) {
     const long long idx = (long long)blockIdx.x * kPw + threadIdx.x;       // over T * D / 2 pairs
@@ -19,7 +21,7 @@ __global__ void __launch_bounds__(kPw) v6_seq_mix_kernel(int T, int D, const __h
     if (idx >= (long long)T * D2) return;
     const int t = int(idx / D2), d = int(idx % D2) * 2;
     const __half2 cur = *reinterpret_cast<const __half2*>(xx + (long long)t * xx_stride + d);
-    const __half2 prev = t == 0 ? *reinterpret_cast<const __half2*>(state + d)
+    const __half2 prev = (t == 0 || state_stride != 0) ? *reinterpret_cast<const __half2*>(state + t * state_stride + d)
                                 : *reinterpret_cast<const __half2*>(xx + (long long)(t - 1) * xx_stride + d);
     const __half2 sx = __hsub2(prev, cur);
     const __half* maa[5] = {m0, m1, m2, m3, m4};
@@ -88,13 +90,14 @@ __global__ void __launch_bounds__(kPw) v56_seq_gn_gate_kernel(int T, int H, int 
 
 }  // namespace
 
-extern "C" int rwkv_v6_seq_mix(int64_t T, int64_t D, const void* xx, int64_t xx_stride, const void* state, const void* m,
-                               const void* const* maa5, void* const* out5, void* stream) {
-    RWKV_CHECK_ARG(T >= 1 && D >= 2 && D % 2 == 0 && xx && state && m && maa5 && out5 && xx_stride >= D && xx_stride % 2 == 0);
+extern "C" int rwkv_v6_seq_mix(int64_t T, int64_t D, const void* xx, int64_t xx_stride, const void* state, int64_t state_stride,
+                               const void* m, const void* const* maa5, void* const* out5, void* stream) {
+    RWKV_CHECK_ARG(T >= 1 && D >= 2 && D % 2 == 0 && xx && state && m && maa5 && out5 && xx_stride >= D && xx_stride % 2 == 0 &&
+                   state_stride % 2 == 0);
     for (int j = 0; j < 5; ++j) RWKV_CHECK_ARG(maa5[j] != nullptr && out5[j] != nullptr);
     const long long n = T * (D / 2);
     v6_seq_mix_kernel<<<(unsigned)((n + kPw - 1) / kPw), kPw, 0, static_cast<cudaStream_t>(stream)>>>(
-        int(T), int(D), (const __half*)xx, xx_stride, (const __half*)state, (const __half*)m, (const __half*)maa5[0],
+        int(T), int(D), (const __half*)xx, xx_stride, (const __half*)state, state_stride, (const __half*)m, (const __half*)maa5[0],
         (const __half*)maa5[1], (const __half*)maa5[2], (const __half*)maa5[3], (const __half*)maa5[4], (__half*)out5[0],
         (__half*)out5[1], (__half*)out5[2], (__half*)out5[3], (__half*)out5[4]);
     return rwkv_launch_status();

@@ -140,9 +140,8 @@ static inline void wkv4_chunks(int64_t T, int& Lc, int& NC) {
 // RWKV-5 / RWKV-6 (the recurrences of rwkv5.cu:32-68, rwkv6.cu:30-67 / pkg/model.py:1245-1251, 1324-1333).
 // State S[h][i][j] (i = value index, j = key index):
 //     y_t[i] = sum_j r_t[j] (u[j] k_t[j] v_t[i] + S[i][j]);   S[i][j] <- w_t[j] S[i][j] + k_t[j] v_t[i]
-// A CTA owns one head and a slice of ROWS value indices; a thread owns (i, quarter of j): N/4 state
-// values in registers, and the four quarters of y_t[i] meet by two shuffles.  r, k, (w,) v of TC time
-// steps are staged in shared memory per barrier pair.
+// A CTA owns one head; its N x N state lives in the registers of (N / TL)^2 threads as TL x TL tiles (see
+// Wkv56Tile).  r, k, v (, w) of TC time steps are staged in shared memory per barrier pair.
 //
 // Parallel in time (more than one chunk): S_t is affine in S_{t-1}, so (1) every chunk runs its steps
 // from S = 0 and keeps its own sum and the product P[j] of its decays (PASS_SUM); (2) a scan kernel
@@ -153,7 +152,7 @@ static inline void wkv4_chunks(int64_t T, int& Lc, int& NC) {
 // list, pkg/model.py:1376, 1384) instead of the operator's [h][i][j].
 // ---------------------------------------------------------------------------------------
 constexpr int TC = 16;
-constexpr int kWkv56MaxChunks = 64;
+constexpr int kWkv56MaxChunks = 16;
 enum { PASS_WHOLE = 0, PASS_SUM = 1, PASS_OUT = 2 };
 
 struct Wkv56Args {
@@ -165,40 +164,45 @@ struct Wkv56Args {
     float* start;           // [H][N][N] copy of the caller's state in operator layout (made by the scan)
 };
 
+// Thread tile of the N x N state: TL x TL values in registers (8 x 8 for the usual N = 64: 64 threads per
+// head).  Per step a thread reads r, k, w of its TL key indices and v of its TL value indices from shared
+// memory (4 * TL words for 3 * TL * TL multiply-adds), and
+//     y[i] = sum_j r[j] S[i][j] + v[i] * sum_j r[j] u[j] k[j]
+// is completed across the N / TL threads that share a value index by log2(N / TL) shuffles.
+template <int N> struct Wkv56Tile { static constexpr int TL = N >= 64 ? 8 : N >= 32 ? 4 : 2; static constexpr int NT = N / TL; };
+
+template <int N, int TL>
+__device__ __forceinline__ long long wkv56_state_index(int model_layout, int h, int i, int j) {
+    return model_layout ? ((long long)h * N + j) * N + i : ((long long)h * N + i) * N + j;
+}
+
 template <typename FI, typename FO, int N, bool PER_TOKEN_W, int PASS>
-__global__ void __launch_bounds__(128) wkv56_seq_kernel(const Wkv56Args a, const FI* __restrict__ r_, const FI* __restrict__ k_,
-                                                        const FI* __restrict__ v_, const float* __restrict__ w_,
-                                                        const FO* __restrict__ u_, FO* __restrict__ y_) {
-    constexpr int JQ = 4, NJ = N / JQ;
-    constexpr int ROWS = (N >= 32) ? 32 : N;       // value indices per CTA
-    constexpr int THREADS = ROWS * JQ;
-    const int slices = N / ROWS, C = a.C;
-    const int h = blockIdx.x / slices, i0 = (blockIdx.x % slices) * ROWS;
-    const int chunk = blockIdx.y;
-    const int tid = threadIdx.x;
-    if (tid >= THREADS) return;
-    const int il = tid / JQ, jq = tid % JQ, i = i0 + il, jb = jq * NJ;
+__global__ void __launch_bounds__(Wkv56Tile<N>::NT * Wkv56Tile<N>::NT)
+wkv56_seq_kernel(const Wkv56Args a, const FI* __restrict__ r_, const FI* __restrict__ k_, const FI* __restrict__ v_,
+                 const float* __restrict__ w_, const FO* __restrict__ u_, FO* __restrict__ y_) {
+    constexpr int TL = Wkv56Tile<N>::TL, NT = Wkv56Tile<N>::NT, THREADS = NT * NT;
+    const int C = a.C, h = blockIdx.x, chunk = blockIdx.y, tid = threadIdx.x;
+    const int ti = tid / NT, tj = tid % NT, i0 = ti * TL, j0 = tj * TL;
     const int t_begin = PASS == PASS_WHOLE ? 0 : chunk * a.Lc;
     const int t_end = PASS == PASS_WHOLE ? a.T : min(a.T, t_begin + a.Lc);
 
-    __shared__ float sr[TC][N], sk[TC][N], sw[PER_TOKEN_W ? TC : 1][N], sv[TC][ROWS], su[N];
+    __shared__ __align__(16) float sr[TC][N], sk[TC][N], sv[TC][N], sw[PER_TOKEN_W ? TC : 1][N];
 
-    float S[NJ], P[NJ];
-    // where this thread's state values live in the caller's buffer
-    auto state_at = [&](int j) -> long long {
-        return a.model_layout ? ((long long)h * N + jb + j) * N + i : ((long long)h * N + i) * N + jb + j;
-    };
+    float S[TL][TL], P[TL], u[TL];
+    const float* src = PASS == PASS_OUT ? (chunk == 0 ? a.start : a.sums + (long long)(chunk - 1) * a.H * N * N) : a.state;
+    const int src_layout = PASS == PASS_OUT ? 0 : a.model_layout;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-        P[j] = 1.f;
-        if (PASS == PASS_SUM) S[j] = 0.f;
-        else if (PASS == PASS_WHOLE) S[j] = a.state[state_at(j)];
-        else S[j] = (chunk == 0 ? a.start : a.sums + (long long)(chunk - 1) * a.H * N * N)[((long long)h * N + i) * N + jb + j];
+    for (int jj = 0; jj < TL; ++jj) {
+        P[jj] = 1.f;
+        u[jj] = to_f32<FO>(u_[h * N + j0 + jj]);
     }
-    for (int j = tid; j < N; j += THREADS) {
-        su[j] = to_f32<FO>(u_[h * N + j]);
-        if (!PER_TOKEN_W) sw[0][j] = w_[h * N + j];
-    }
+#pragma unroll
+    for (int ii = 0; ii < TL; ++ii)
+#pragma unroll
+        for (int jj = 0; jj < TL; ++jj)
+            S[ii][jj] = PASS == PASS_SUM ? 0.f : src[wkv56_state_index<N, TL>(src_layout, h, i0 + ii, j0 + jj)];
+    if (!PER_TOKEN_W)
+        for (int j = tid; j < N; j += THREADS) sw[0][j] = w_[h * N + j];
 
     for (int t0 = t_begin; t0 < t_end; t0 += TC) {
         const int nt = min(TC, t_end - t0);
@@ -208,76 +212,87 @@ __global__ void __launch_bounds__(128) wkv56_seq_kernel(const Wkv56Args a, const
             const long long g = (long long)(t0 + tt) * C + h * N + j;
             sr[tt][j] = to_f32<FI>(r_[g]);
             sk[tt][j] = to_f32<FI>(k_[g]);
+            sv[tt][j] = to_f32<FI>(v_[g]);
             if (PER_TOKEN_W) sw[tt][j] = w_[g];
-        }
-        for (int e = tid; e < nt * ROWS; e += THREADS) {
-            const int tt = e / ROWS, ii = e % ROWS;
-            sv[tt][ii] = to_f32<FI>(v_[(long long)(t0 + tt) * C + h * N + i0 + ii]);
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            const float v = sv[tt][il];
+            float r[TL], k[TL], w[TL], v[TL];
             const float* wrow = PER_TOKEN_W ? sw[tt] : sw[0];
-            float y = 0.f;
 #pragma unroll
-            for (int j = 0; j < NJ; ++j) {
-                const float x = sk[tt][jb + j] * v;
-                if (PASS != PASS_SUM) y = fmaf(sr[tt][jb + j], fmaf(su[jb + j], x, S[j]), y);
-                S[j] = fmaf(S[j], wrow[jb + j], x);
-                if (PASS == PASS_SUM) P[j] *= wrow[jb + j];
-            }
+            for (int q = 0; q < TL; ++q) { r[q] = sr[tt][j0 + q]; k[q] = sk[tt][j0 + q]; w[q] = wrow[j0 + q]; v[q] = sv[tt][i0 + q]; }
             if (PASS != PASS_SUM) {
-                y += __shfl_xor_sync(0xffffffffu, y, 1);
-                y += __shfl_xor_sync(0xffffffffu, y, 2);
-                if (jq == 0) y_[(long long)(t0 + tt) * C + h * N + i] = from_f32<FO>(y);
+                float ruk = 0.f;
+#pragma unroll
+                for (int jj = 0; jj < TL; ++jj) ruk = fmaf(r[jj] * u[jj], k[jj], ruk);
+                float y[TL];
+#pragma unroll
+                for (int ii = 0; ii < TL; ++ii) {
+                    float acc = v[ii] * ruk;
+#pragma unroll
+                    for (int jj = 0; jj < TL; ++jj) acc = fmaf(r[jj], S[ii][jj], acc);
+                    y[ii] = acc;
+                }
+#pragma unroll
+                for (int o = NT >> 1; o > 0; o >>= 1) {
+#pragma unroll
+                    for (int ii = 0; ii < TL; ++ii) y[ii] += __shfl_xor_sync(0xffffffffu, y[ii], o);
+                }
+                if (tj == 0) {
+                    FO* yo = y_ + (long long)(t0 + tt) * C + h * N + i0;
+#pragma unroll
+                    for (int ii = 0; ii < TL; ++ii) yo[ii] = from_f32<FO>(y[ii]);
+                }
+            }
+#pragma unroll
+            for (int ii = 0; ii < TL; ++ii)
+#pragma unroll
+                for (int jj = 0; jj < TL; ++jj) S[ii][jj] = fmaf(S[ii][jj], w[jj], k[jj] * v[ii]);
+            if (PASS == PASS_SUM) {
+#pragma unroll
+                for (int jj = 0; jj < TL; ++jj) P[jj] *= w[jj];
             }
         }
     }
     if (PASS == PASS_SUM) {
-        float* out = a.sums + (long long)chunk * a.H * N * N + ((long long)h * N + i) * N + jb;
+        float* out = a.sums + (long long)chunk * a.H * N * N;
 #pragma unroll
-        for (int j = 0; j < NJ; ++j) out[j] = S[j];
-        if (i == 0) {
+        for (int ii = 0; ii < TL; ++ii)
 #pragma unroll
-            for (int j = 0; j < NJ; ++j) a.prods[((long long)chunk * a.H + h) * N + jb + j] = P[j];
+            for (int jj = 0; jj < TL; ++jj) out[wkv56_state_index<N, TL>(0, h, i0 + ii, j0 + jj)] = S[ii][jj];
+        if (ti == 0) {
+#pragma unroll
+            for (int jj = 0; jj < TL; ++jj) a.prods[((long long)chunk * a.H + h) * N + j0 + jj] = P[jj];
         }
     } else if (PASS == PASS_WHOLE || chunk == a.NC - 1) {
 #pragma unroll
-        for (int j = 0; j < NJ; ++j) a.state_out[state_at(j)] = S[j];
+        for (int ii = 0; ii < TL; ++ii)
+#pragma unroll
+            for (int jj = 0; jj < TL; ++jj) a.state_out[wkv56_state_index<N, TL>(a.model_layout, h, i0 + ii, j0 + jj)] = S[ii][jj];
     }
 }
 
 // start <- the caller's state (operator layout); sums[c] <- state after chunk c, for c = 0 .. NC - 2
 template <int N>
-__global__ void __launch_bounds__(128) wkv56_scan_kernel(const Wkv56Args a) {
-    constexpr int JQ = 4, NJ = N / JQ;
-    constexpr int ROWS = (N >= 32) ? 32 : N;
-    constexpr int THREADS = ROWS * JQ;
-    const int slices = N / ROWS;
-    const int h = blockIdx.x / slices, i0 = (blockIdx.x % slices) * ROWS;
-    const int tid = threadIdx.x;
-    if (tid >= THREADS) return;
-    const int il = tid / JQ, jq = tid % JQ, i = i0 + il, jb = jq * NJ;
-    float S[NJ];
-    const long long at = ((long long)h * N + i) * N + jb;
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-        S[j] = a.model_layout ? a.state[((long long)h * N + jb + j) * N + i] : a.state[at + j];
-        a.start[at + j] = S[j];
-    }
-    for (int c = 0; c + 1 < a.NC; ++c) {
-        float* sm = a.sums + (long long)c * a.H * N * N + at;
-        const float* pr = a.prods + ((long long)c * a.H + h) * N + jb;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-            S[j] = fmaf(S[j], pr[j], sm[j]);
-            sm[j] = S[j];
+__global__ void __launch_bounds__(256) wkv56_scan_kernel(const Wkv56Args a) {
+    const int h = blockIdx.x;
+    for (int e = threadIdx.x; e < N * N; e += 256) {
+        const int i = e / N, j = e % N;
+        const long long at = ((long long)h * N + i) * N + j;
+        float S = a.state[wkv56_state_index<N, 1>(a.model_layout, h, i, j)];
+        a.start[at] = S;
+        for (int c = 0; c + 1 < a.NC; ++c) {
+            float* sm = a.sums + (long long)c * a.H * N * N + at;
+            S = fmaf(S, a.prods[((long long)c * a.H + h) * N + j], *sm);
+            *sm = S;
         }
     }
 }
 
 static inline void wkv56_chunks(int64_t T, int& Lc, int& NC) {
-    Lc = T <= 64 * kWkv56MaxChunks ? 64 : int((T + kWkv56MaxChunks - 1) / kWkv56MaxChunks);
+    // chunks of 128 steps, at most 16 of them: every pass then has a few CTAs per SM, and the steps a CTA runs
+    // one after the other stay a small multiple of what the parallel passes cost
+    Lc = T <= 128 * kWkv56MaxChunks ? 128 : int((T + kWkv56MaxChunks - 1) / kWkv56MaxChunks);
     Lc = (Lc + TC - 1) / TC * TC;
     NC = int((T + Lc - 1) / Lc);
 }
@@ -303,16 +318,16 @@ int launch56(int T, int C, int H, const float* state, float* state_out, const vo
     a.start = a.NC > 1 ? a.prods + (size_t)a.NC * H * N : nullptr;
 #define RWKV_L56(NN)                                                                                          \
     {                                                                                                         \
-        constexpr int ROWS = (NN >= 32) ? 32 : NN;                                                            \
-        const unsigned gx = unsigned(H * (NN / ROWS));                                                        \
+        constexpr int THR = Wkv56Tile<NN>::NT * Wkv56Tile<NN>::NT;                                            \
+        const unsigned gx = unsigned(H);                                                                      \
         if (a.NC == 1) {                                                                                      \
-            wkv56_seq_kernel<FI, FO, NN, PER_TOKEN_W, PASS_WHOLE><<<gx, ROWS * 4, 0, st>>>(                  \
+            wkv56_seq_kernel<FI, FO, NN, PER_TOKEN_W, PASS_WHOLE><<<gx, THR, 0, st>>>(                       \
                 a, (const FI*)r, (const FI*)k, (const FI*)v, w, (const FO*)u, (FO*)y);                        \
         } else {                                                                                              \
-            wkv56_seq_kernel<FI, FO, NN, PER_TOKEN_W, PASS_SUM><<<dim3(gx, unsigned(a.NC - 1)), ROWS * 4, 0, st>>>( \
+            wkv56_seq_kernel<FI, FO, NN, PER_TOKEN_W, PASS_SUM><<<dim3(gx, unsigned(a.NC - 1)), THR, 0, st>>>( \
                 a, (const FI*)r, (const FI*)k, (const FI*)v, w, (const FO*)u, (FO*)y);                        \
-            wkv56_scan_kernel<NN><<<gx, ROWS * 4, 0, st>>>(a);                                                \
-            wkv56_seq_kernel<FI, FO, NN, PER_TOKEN_W, PASS_OUT><<<dim3(gx, unsigned(a.NC)), ROWS * 4, 0, st>>>(   \
+            wkv56_scan_kernel<NN><<<gx, 256, 0, st>>>(a);                                                     \
+            wkv56_seq_kernel<FI, FO, NN, PER_TOKEN_W, PASS_OUT><<<dim3(gx, unsigned(a.NC)), THR, 0, st>>>(    \
                 a, (const FI*)r, (const FI*)k, (const FI*)v, w, (const FO*)u, (FO*)y);                        \
         }                                                                                                     \
     }

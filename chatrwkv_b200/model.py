@@ -304,6 +304,7 @@ class RWKV:
                             os.environ.get("RWKV_B200_STREAM", "0") == "1")
         self._stream = None
         self._mm = {}
+        self._tile_cache = {}
         # a matrix with more than 16384 in-features needs the decode kernel's second build: ask for it on every launch
         self._gemv_flags = _lib.MM8_WIDE_BUILD if max(a.n_ffn, a.n_att, a.n_embd) > 16384 else 0
 
@@ -322,10 +323,12 @@ class RWKV:
     def _gemv(self, problems, exchange=None):
         ops.mm8_one_batch(problems, torch.float16, self.device, self._ws, exchange, self._gemv_flags)
 
-    def _ln_mix(self, T, x, sx, ln_w, ln_b, mode, mixes, outs, xx_out=None, new_state=None, mix_stride=0):
+    def _ln_mix(self, T, x, sx, ln_w, ln_b, mode, mixes, outs, xx_out=None, new_state=None, mix_stride=0, rows=False):
+        """`rows`: every row of x is a sequence of its own (batched decode) and sx holds their states [T, D]."""
         D = self.args.n_embd
-        check(lib().rwkv_ln_mix(T, D, x.data_ptr(), x.stride(0) if x.dim() == 2 else D,
-                                sx.data_ptr() if sx is not None else None, ln_w.data_ptr(), ln_b.data_ptr(),
+        check(lib().rwkv_ln_mix_rows(T, D, x.data_ptr(), x.stride(0) if x.dim() == 2 else D,
+                                sx.data_ptr() if sx is not None else None, (sx.stride(0) if rows and sx is not None else 0),
+                                ln_w.data_ptr(), ln_b.data_ptr(),
                                 mode, len(mixes), _ptr_array(mixes), mix_stride, _ptr_array(outs),
                                 outs[0].stride(0) if (outs and outs[0].dim() == 2) else D,
                                 xx_out.data_ptr() if xx_out is not None else None,
@@ -758,7 +761,7 @@ class RWKV:
         y = out if out is not None else torch.empty((x.shape[0], wq.shape[1]), dtype=torch.float16, device=x.device)
         return ops.mm8_seq_epi(x, wq, mx, rx, my, ry, y, epilogue, aux, aux2, out_scale)
 
-    def _att_seq_v4(self, x, st, i):
+    def _att_seq_v4(self, x, st, i, rows=False):
         """cuda_att_seq (model.py:1346-1360): LayerNorm + mixes, r/k/v matmuls (sigmoid in the store), the WKV
         recurrence parallel in time with r * wkv in its store, output matmul with the residual in the store."""
         w, a = self.w, self.args
@@ -768,12 +771,16 @@ class RWKV:
         new_sx = torch.empty_like(st[i * 5 + 0])
         self._ln_mix(T, x, st[i * 5 + 0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 0,
                      [w[att + "time_mix_k"], w[att + "time_mix_v"], w[att + "time_mix_r"]], [kx, vx, rx],
-                     new_state=new_sx)
+                     new_state=None if rows else new_sx, xx_out=new_sx if rows else None, rows=rows)
         if self._world == 1:
             r = self._mm_epi(rx, att + "receptance.weight", EPI_SIGMOID)
             k = self._mm_epi(kx, att + "key.weight", EPI_STORE)             # fp16 k, v: the kernel widens them, as
             v = self._mm_epi(vx, att + "value.weight", EPI_STORE)           # model.py:1355-1356 does before the op
-            ops.wkv4_seq(w[att + "time_decay"], w[att + "time_first"], k, v, k, st[i * 5 + 1], st[i * 5 + 2], st[i * 5 + 3], r=r)
+            if rows:        # T sequences of one step each: the operator's batch dimension, state [T, C]
+                ops.wkv4_seq(w[att + "time_decay"], w[att + "time_first"], k.view(T, 1, C), v.view(T, 1, C), k.view(T, 1, C),
+                             st[i * 5 + 1], st[i * 5 + 2], st[i * 5 + 3], r=r.view(T, 1, C))
+            else:
+                ops.wkv4_seq(w[att + "time_decay"], w[att + "time_first"], k, v, k, st[i * 5 + 1], st[i * 5 + 2], st[i * 5 + 3], r=r)
             st[i * 5 + 0] = new_sx
             return self._mm_epi(k, att + "output.weight", EPI_RESIDUAL, aux=x, out=x)
         r = torch.sigmoid(self._mm_seq(rx, att + "receptance.weight"))
@@ -786,7 +793,7 @@ class RWKV:
         st[i * 5 + 0] = new_sx
         return x + out
 
-    def _att_seq_v56(self, x, st2, i):
+    def _att_seq_v56(self, x, st2, i, rows=False):
         """cuda_att_seq_v5_2 / cuda_att_seq_v6_0 (model.py:1363-1439).  `st2` = [att_xx, att_kv]; the first entry is
         replaced, the matrix state is updated in place in the model's [H, key, value] layout.  Kernels of this
         library throughout; the four small low-rank products of RWKV-6 (ranks 32..160) are plain fp16 library GEMMs
@@ -804,7 +811,9 @@ class RWKV:
         if self.version == 6:
             xx, xxx = h(T, D), h(T, D)
             self._ln_mix(T, x, st2[0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 1, [w[att + "time_maa_x"]], [xxx],
-                         xx_out=xx, new_state=new_sx)
+                         xx_out=xx, new_state=None if rows else new_sx, rows=rows)
+            if rows:
+                new_sx = xx
             # low-rank offsets of the five mixes: tanh(xxx @ w1) as [5, T, Lm], times w2 [5, Lm, D]
             w1, w2 = w[att + "time_maa_w1"], w[att + "time_maa_w2"]
             Lm = w2.shape[1]
@@ -816,7 +825,8 @@ class RWKV:
             mixes = h(5, T, D)
             maa5 = (C.c_void_p * 5)(*[w[att + "time_maa_" + n].data_ptr() for n in "wkvrg"])
             out5 = (C.c_void_p * 5)(*[mixes[j].data_ptr() for j in range(5)])
-            check(L.rwkv_v6_seq_mix(T, D, xx.data_ptr(), xx.stride(0), st2[0].data_ptr(), m5.data_ptr(), maa5, out5, stream),
+            check(L.rwkv_v6_seq_mix(T, D, xx.data_ptr(), xx.stride(0), st2[0].data_ptr(), st2[0].stride(0) if rows else 0,
+                                    m5.data_ptr(), maa5, out5, stream),
                   "v6_seq_mix")
             wx, kx, vx, rx, gx = mixes.unbind(0)
             # per-token decay exp(-exp(time_decay + tanh(wx @ dw1) @ dw2))
@@ -831,7 +841,8 @@ class RWKV:
         else:
             kx, vx, rx, gx = (torch.empty_like(x) for _ in range(4))
             self._ln_mix(T, x, st2[0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 0,
-                         [w[att + f"time_mix_{n}"] for n in "kvrg"], [kx, vx, rx, gx], new_state=new_sx)
+                         [w[att + f"time_mix_{n}"] for n in "kvrg"], [kx, vx, rx, gx],
+                         new_state=None if rows else new_sx, xx_out=new_sx if rows else None, rows=rows)
             decay = w[att + "time_decay"].reshape(-1)
         r = self._mm_epi(rx, att + "receptance.weight", EPI_STORE)        # fp16-rounded r, k, v: the kernel widens them
         k = self._mm_epi(kx, att + "key.weight", EPI_STORE)               # (model.py:1413, 1425-1427)
@@ -840,8 +851,16 @@ class RWKV:
         y = torch.empty((T, D), dtype=torch.float32, device=dev)
         S_in = st2[1] if st2[1].is_contiguous() else st2[1].contiguous()
         S = torch.empty_like(S_in)                  # the caller's state stays as it is, as with the reference's copy
-        ops.wkv56_seq(self.version == 6, H, S_in, r, k, v, decay, w[att + "time_first"].reshape(-1), y, model_layout=True,
-                      state_out=S)
+        u = w[att + "time_first"].reshape(-1)
+        if rows:
+            # T sequences of one step each = T * H independent heads of one step; the per-head vectors repeat per sequence
+            u = self._tiled(att + "time_first", u, T)
+            if self.version != 6:
+                decay = self._tiled(att + "time_decay", decay, T)
+            ops.wkv56_seq(self.version == 6, T * H, S_in, r.view(1, T * D), k.view(1, T * D), v.view(1, T * D), decay.view(-1) if
+                          self.version != 6 else decay.view(1, T * D), u, y.view(1, T * D), model_layout=True, state_out=S)
+        else:
+            ops.wkv56_seq(self.version == 6, H, S_in, r, k, v, decay, u, y, model_layout=True, state_out=S)
         out = h(T, D)
         check(L.rwkv_v56_seq_gn_gate(T, H, N, y.data_ptr(), w[att + "ln_x.weight"].data_ptr(), w[att + "ln_x.bias"].data_ptr(),
                                      g.data_ptr(), out.data_ptr(), 64e-5, stream), "gn_gate")
@@ -849,19 +868,25 @@ class RWKV:
         st2[1] = S
         return self._mm_epi(out, att + "output.weight", EPI_RESIDUAL, aux=x, out=x)
 
-    def _ffn_seq(self, x, sx, i):
+    def _tiled(self, name, t, reps):
+        """A per-head / per-channel model vector repeated for `reps` sequences (cached: made once per batch size)."""
+        key = (name, reps)
+        c = self._tile_cache.get(key)
+        if c is None:
+            c = self._tile_cache[key] = t.reshape(-1).repeat(reps).contiguous()
+        return c
+
+    def _ffn_seq(self, x, sx, i, rows=False):
         """ffn_seq / ffn_seq_v6 (model.py:995-1004, 1019-1029)."""
         w = self.w
         T = x.shape[0]
         bb, ffn = f"blocks.{i}.", f"blocks.{i}.ffn."
         kx, rx = torch.empty_like(x), torch.empty_like(x)
         new_sx = torch.empty_like(sx)
-        if self.version == 6:
-            self._ln_mix(T, x, sx, w[bb + "ln2.weight"], w[bb + "ln2.bias"], 1,
-                         [w[ffn + "time_maa_k"], w[ffn + "time_maa_r"]], [kx, rx], new_state=new_sx)
-        else:
-            self._ln_mix(T, x, sx, w[bb + "ln2.weight"], w[bb + "ln2.bias"], 0,
-                         [w[ffn + "time_mix_k"], w[ffn + "time_mix_r"]], [kx, rx], new_state=new_sx)
+        v6 = self.version == 6
+        self._ln_mix(T, x, sx, w[bb + "ln2.weight"], w[bb + "ln2.bias"], 1 if v6 else 0,
+                     [w[ffn + ("time_maa_k" if v6 else "time_mix_k")], w[ffn + ("time_maa_r" if v6 else "time_mix_r")]], [kx, rx],
+                     new_state=None if rows else new_sx, xx_out=new_sx if rows else None, rows=rows)
         if self._world == 1:
             r = self._mm_epi(rx, ffn + "receptance.weight", EPI_SIGMOID)
             vx = self._mm_epi(kx, ffn + "key.weight", EPI_RELU_SQ)
@@ -873,6 +898,49 @@ class RWKV:
         vx = torch.relu(self._mm_seq(kx, ffn + "key.weight")) ** 2
         out = r * self._mm_seq(vx, ffn + "value.weight")
         return x + out, new_sx
+
+    # ----- batched decode: B independent sequences, one token each ---------------------------
+    def zero_batch_state(self, B):
+        """The state of B fresh sequences: the entries of the ordinary state list with a leading batch dimension."""
+        return [torch.stack([t] * B).contiguous() for t in self._zero_state()]
+
+    @staticmethod
+    def stack_states(states):
+        """B ordinary state lists (e.g. after B separate prefills) -> one batch state."""
+        return [torch.stack([s[j].contiguous() for s in states]).contiguous() for j in range(len(states[0]))]
+
+    @staticmethod
+    def unstack_states(batch_state):
+        B = batch_state[0].shape[0]
+        return [[t[b] for t in batch_state] for b in range(B)]
+
+    def forward_batch(self, tokens, state):
+        """One decode step for B independent sequences at once (an addition to the reference's API, which has no batch
+        dimension: its kernels carry a B they cannot use, rwkv6.cu:13-17).  `tokens`: B token ids; `state`: None, a batch
+        state returned by an earlier call (or by zero_batch_state / stack_states).  Returns (logits fp32 [B, V],
+        batch state).  The B sequences are the rows of the tensor-core mm8_seq kernel, so the packed weights are
+        streamed once per step for all of them; every sequence follows the arithmetic of the prefill path with T = 1.
+        The RWKV-4 WKV states (aa, bb, pp) are updated in place, everything else is returned in new tensors."""
+        if self._world > 1:
+            raise NotImplementedError("forward_batch: single-GPU models only")
+        with torch.no_grad(), torch.cuda.device(self.device):
+            w, a = self.w, self.args
+            B = len(tokens)
+            state = self.zero_batch_state(B) if state is None else list(state)
+            idx = tokens if torch.is_tensor(tokens) else torch.tensor([int(t) for t in tokens], dtype=torch.int64, device=self.device)
+            x = w["emb.weight"].index_select(0, idx.to(self.device))
+            for i in range(a.n_layer):
+                if self.version == 4:
+                    x = self._att_seq_v4(x, state, i, rows=True)
+                    x, state[i * 5 + 4] = self._ffn_seq(x, state[i * 5 + 4], i, rows=True)
+                else:
+                    st2 = [state[i * 3 + 0], state[i * 3 + 1]]
+                    x = self._att_seq_v56(x, st2, i, rows=True)
+                    state[i * 3 + 0], state[i * 3 + 1] = st2
+                    x, state[i * 3 + 2] = self._ffn_seq(x, state[i * 3 + 2], i, rows=True)
+            xln = torch.empty_like(x)
+            self._ln_mix(B, x, None, w["ln_out.weight"], w["ln_out.bias"], 0, [], [], xx_out=xln)
+            return self._mm_epi(xln, "head.weight", EPI_STORE).float(), state
 
     def _forward_seq(self, tokens, state, full_output):
         w, a = self.w, self.args

@@ -383,7 +383,8 @@ int rwkv_wkv4_forward(int64_t B, int64_t T, int64_t C, const float* w, const flo
  * parallel in time: chunk sums from an empty state, a scan of the chunk-start states, the chunks again
  * for y (results equal the sequential recurrence up to fp32 rounding).
  * rwkv_v6_seq_mix: the five token-shift mixes from xx [T, D] (LayerNorm output), the previous token's
- * xx (`state` [D]), the low-rank offsets m [5, T, D] and time_maa_{w,k,v,r,g}; out5: five [T, D].
+ * xx (`state` [D]; with state_stride != 0 every row is its own sequence with its state at state + t *
+ * state_stride: batched decode), the low-rank offsets m [5, T, D] and time_maa_{w,k,v,r,g}; out5: five [T, D].
  * rwkv_tanh_regroup_f16: out[g, t, r] = tanh(in[t, g, r]) (G = 1: plain tanh, in place allowed).  rwkv_v6_seq_decay: out[T, D] = exp(-exp(time_decay + float(d2))) in fp32.
  * rwkv_v56_seq_gn_gate: group-norm of y [T, H*N] over each head's N channels (eps), ln_x weight / bias in
  * fp32, rounded to fp16 and multiplied with the gate g [T, H*N] in fp16.
@@ -392,8 +393,8 @@ size_t rwkv_wkv56_workspace_bytes(int64_t T, int64_t C, int64_t H);
 int rwkv_wkv56_seq(int per_token_w, int64_t T, int64_t C, int64_t H, const float* state, float* state_out, int model_layout,
                    const void* r, const void* k, const void* v, const float* w, const void* u, void* y,
                    int in_dtype, int out_dtype, void* workspace, size_t workspace_bytes, void* stream);
-int rwkv_v6_seq_mix(int64_t T, int64_t D, const void* xx, int64_t xx_stride, const void* state, const void* m,
-                    const void* const* maa5, void* const* out5, void* stream);
+int rwkv_v6_seq_mix(int64_t T, int64_t D, const void* xx, int64_t xx_stride, const void* state, int64_t state_stride,
+                    const void* m, const void* const* maa5, void* const* out5, void* stream);
 int rwkv_tanh_regroup_f16(int64_t T, int64_t G, int64_t R, const void* in, void* out, void* stream);
 int rwkv_v6_seq_decay(int64_t T, int64_t D, const float* time_decay, const void* d2, float* out, void* stream);
 int rwkv_v56_seq_gn_gate(int64_t T, int64_t H, int64_t N, const float* y, const float* ln_w, const float* ln_b,
@@ -433,6 +434,13 @@ int rwkv_ln_mix(int64_t T, int64_t D, const void* x, int64_t x_stride, const voi
                 const void* ln_w, const void* ln_b, int mode, int n_mix,
                 const void* const* mix, int64_t mix_stride, void* const* out, int64_t out_stride,
                 void* xx_out, int64_t xx_stride, void* new_state, void* stream);
+/* The same for rows that are independent sequences (batched decode, one token each; no counterpart in the
+ * reference, which has no batch dimension): prev of row t = sx + t * sx_stride (sx_stride != 0; 0 = rwkv_ln_mix);
+ * take the new per-sequence states from xx_out. */
+int rwkv_ln_mix_rows(int64_t T, int64_t D, const void* x, int64_t x_stride, const void* sx, int64_t sx_stride,
+                     const void* ln_w, const void* ln_b, int mode, int n_mix,
+                     const void* const* mix, int64_t mix_stride, void* const* out, int64_t out_stride,
+                     void* xx_out, int64_t xx_stride, void* new_state, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * RWKV-4 one-step WKV — the fp32 island of att_one (pkg/model.py:1044-1055).

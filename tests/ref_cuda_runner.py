@@ -77,6 +77,20 @@ def main(inp, outp):
         out[f"{p}/y"], out[f"{p}/state"] = y.cpu().numpy(), s.cpu().numpy()
         s2 = s.clone()
         out[f"{p}/t_us"] = np.float64(_time(lambda: fn(1, T, C, H, s2, r, k, v, w, u, y), 5))
+    # timing only, at the 7B width (64 heads of 64, 2048 steps): what the product's kernels are compared with
+    if "time/wkv_T" in d.files:
+        T, C, H = int(d["time/wkv_T"]), 4096, 64
+        g = torch.Generator(device="cuda").manual_seed(3001)
+        k, v, r = (torch.randn(T, C, generator=g, device="cuda") for _ in range(3))
+        w6 = torch.exp(-torch.exp(torch.rand(T, C, generator=g, device="cuda") * 6 - 5))
+        w4 = -torch.exp(torch.rand(C, generator=g, device="cuda") * 6 - 5)
+        u = torch.rand(C, generator=g, device="cuda") * 2 - 1
+        y = torch.empty(T, C, device="cuda")
+        aa, bb, pp = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda"), torch.full((C,), -1e30, device="cuda")
+        S = torch.zeros(H, C // H, C // H, device="cuda")
+        out["time/wkv4_us"] = np.float64(_time(lambda: torch.ops.rwkv.wkv_forward(1, T, C, w4, u, k, v, y, aa, bb, pp), 5))
+        out["time/wkv5_us"] = np.float64(_time(lambda: torch.ops.rwkv5.forward_fp32(1, T, C, H, S, r, k, v, w6[0].contiguous(), u, y), 5))
+        out["time/wkv6_us"] = np.float64(_time(lambda: torch.ops.rwkv6.forward_fp32(1, T, C, H, S, r, k, v, w6, u, y), 5))
     np.savez(outp, **out)
 
 

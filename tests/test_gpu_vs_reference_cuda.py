@@ -55,6 +55,7 @@ def ref_outputs(tmp_path_factory):
         inp[f"{p}/w"] = torch.exp(-torch.exp(torch.empty(shape).uniform_(-5, 1, generator=g))).numpy()
         inp[f"{p}/u"] = torch.empty(Cc).uniform_(-1, 1, generator=g).numpy()
         inp[f"{p}/state"] = (torch.randn(H, N64, N64, generator=g) * 0.1).numpy()
+    inp["time/wkv_T"] = np.int64(2048)
     fin, fout = str(tmp / "in.npz"), str(tmp / "out.npz")
     np.savez(fin, **inp)
     r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "ref_cuda_runner.py"), fin, fout],
@@ -93,9 +94,13 @@ def test_mm8_against_reference_kernels(ref_outputs):
         report[name] = {"N": N, "M": M, "ref_mm8_one_us": float(out[f"mm8/{name}/t_one_us"]),
                         "ref_mm8_seq_us": float(out[f"mm8/{name}/t_seq_us"]), "seq_rows": int(xs.shape[0]),
                         "mismatch_frac_fp16_seq": float((ys.cpu() != refs).float().mean())}
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    with open(os.path.join(ROOT, "gpurun_out", "reference_cuda_ops.json"), "w") as f:
-        json.dump(report, f, indent=1)
+    for name in ("wkv4", "wkv5", "wkv6"):
+        report[f"ref_{name}_T2048_C4096_us"] = float(out[f"time/{name}_us"])
+    rdir = os.environ.get("RWKV_B200_REPORT_DIR")          # the reference kernels' times on this GPU, for the record
+    if rdir:
+        os.makedirs(rdir, exist_ok=True)
+        with open(os.path.join(rdir, "reference_cuda_ops.json"), "w") as f:
+            json.dump(report, f, indent=1)
 
 
 def test_wkv_against_reference_kernels(ref_outputs):
