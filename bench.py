@@ -257,7 +257,7 @@ def main():
             tok = torch.argmax(logits).reshape(1)
         return tok, state
 
-    if a.batch > 0:
+    if a.batch > 0 and a.sequences == 0:
         # ---- batched decode: B sequences per GPU, one token each per step, no prefill (zero states) ----
         B = a.batch
         tok = torch.tensor(synth.make_tokens(B, V, 2000 + rank), dtype=torch.int64, device=dev)
@@ -286,7 +286,7 @@ def main():
                                            f"per step together (RWKV.forward_batch), greedy, from empty states",
                                "parallelism": "independent batches, one per GPU, no collective",
                                "l2": f"inputs larger than L2 ({weight_gb:.2f} GB of packed weights streamed per step)"},
-                    "per_sequence_tokens_per_s": a.steps / (ms / 1e3), "clocks": clocks, "graph": False}
+                    "per_sequence_tokens_per_s": a.steps / (ms / 1e3), "clocks": clocks, "graph": bool(model._use_graph)}
             print(json.dumps(line), flush=True)
         if world > 1:
             dist.destroy_process_group()
@@ -303,7 +303,30 @@ def main():
         sampler.start()
         ev0.record()
         pre_ms = 0.0
-        for sq in mine:
+        if a.batch > 0:
+            # prefill one by one, then groups of --batch sequences decode together (RWKV.forward_batch)
+            import copy
+            for g0 in range(0, len(mine), a.batch):
+                group = mine[g0:g0 + a.batch]
+                p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                p0.record()
+                states, first = [], []
+                for sq in group:
+                    logits, state = model.forward(synth.make_tokens(a.prompt, V, 2000 + sq), None)
+                    states.append(state)
+                    first.append(torch.argmax(logits).reshape(1))
+                bstate = model.stack_states(states)
+                p1.record()
+                tok = torch.cat(first)
+                for _ in range(a.steps):
+                    logits, bstate = model.forward_batch(tok, bstate)
+                    tok = torch.argmax(logits, dim=-1)
+                torch.cuda.synchronize(dev)
+                pre_ms += p0.elapsed_time(p1)
+            mine_iter = []
+        else:
+            mine_iter = mine
+        for sq in mine_iter:
             prompt = synth.make_tokens(a.prompt, V, 2000 + sq)
             p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             p0.record()
@@ -324,11 +347,13 @@ def main():
             dec_tokens = a.sequences * a.steps
             line = {"metric": metric.replace("decode_tokens", "sequences_decode_tokens"), "unit": "tokens/s", "n_gpus": world,
                     "value": dec_tokens / ((total_ms - pre_ms) / 1e3), "steps": a.steps, "warmup": a.warmup,
-                    "ms_per_step": (total_ms - pre_ms) / (a.steps * max(1, len(mine))), "higher_is_better": True,
+                    "ms_per_step": (total_ms - pre_ms) / (a.steps * max(1, -(-len(mine) // a.batch) if a.batch > 0 else len(mine))),
+                    "higher_is_better": True,
                     "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                     "config": {"workload": f"rwkv{a.shape} shape 'cuda fp16i8': {a.sequences} independent sequences dealt to "
                                            f"{world} GPU(s) (s mod N), each a {a.prompt}-token prefill then {a.steps} greedy "
-                                           f"tokens, one sequence at a time per GPU",
+                                           f"tokens; " + (f"prefill one by one, decode in batches of {a.batch} (forward_batch)"
+                                                           if a.batch > 0 else "one sequence at a time per GPU"),
                                "parallelism": "independent sequences, no collective",
                                "l2": f"inputs larger than L2 ({weight_gb:.2f} GB of packed weights streamed per step)"},
                     "whole_job": {"seconds": total_ms / 1e3, "prefill_seconds_max_rank": pre_ms / 1e3,

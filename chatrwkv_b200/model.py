@@ -305,6 +305,7 @@ class RWKV:
         self._stream = None
         self._mm = {}
         self._tile_cache = {}
+        self._batch_graphs = {}
         # a matrix with more than 16384 in-features needs the decode kernel's second build: ask for it on every launch
         self._gemv_flags = _lib.MM8_WIDE_BUILD if max(a.n_ffn, a.n_att, a.n_embd) > 16384 else 0
 
@@ -924,11 +925,57 @@ class RWKV:
         if self._world > 1:
             raise NotImplementedError("forward_batch: single-GPU models only")
         with torch.no_grad(), torch.cuda.device(self.device):
-            w, a = self.w, self.args
             B = len(tokens)
-            state = self.zero_batch_state(B) if state is None else list(state)
             idx = tokens if torch.is_tensor(tokens) else torch.tensor([int(t) for t in tokens], dtype=torch.int64, device=self.device)
-            x = w["emb.weight"].index_select(0, idx.to(self.device))
+            idx = idx.to(self.device).reshape(B)
+            if self._use_graph and os.environ.get("RWKV_B200_BATCH_GRAPH", "1") != "0":
+                return self._forward_batch_graph(idx, state)
+            return self._forward_batch_eager(idx, state)
+
+    def _forward_batch_graph(self, idx, state):
+        """forward_batch as one CUDA-graph replay per batch size.  The graph reads the state from fixed input tensors
+        and leaves the new state in fixed output tensors (its first node copies outputs back to inputs), so the list
+        it returns is overwritten by the next call with the same batch size: pass copy.deepcopy(state) around to keep
+        a snapshot, as with the one-token forward."""
+        B = idx.numel()
+        g = self._batch_graphs.get(B)
+        if g is None:
+            g = types.SimpleNamespace(tok=torch.zeros(B, dtype=torch.int64, device=self.device),
+                                      inp=self.zero_batch_state(B), out=None, logits=None, graph=None)
+            # one eager step on the capture stream warms every kernel up and sizes the per-stream operator workspaces
+            side = torch.cuda.Stream(self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self._forward_batch_eager(g.tok, [t.clone() for t in g.inp])
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                g.logits, g.out = self._forward_batch_eager(g.tok, g.inp)
+            # the previous step's outputs become the next step's inputs (entries updated in place are their own output)
+            moved = [(i, o) for i, o in zip(g.inp, g.out) if i is not o]
+            g.graph, g.moved = graph, moved
+            self._batch_graphs[B] = g
+            state_is_ours = False
+        else:
+            state_is_ours = state is not None and len(state) == len(g.out) and all(a is b for a, b in zip(state, g.out))
+        if state is None:
+            state = self.zero_batch_state(B)
+            state_is_ours = False
+        if state_is_ours:
+            if g.moved:
+                torch._foreach_copy_([i for i, _ in g.moved], [o for _, o in g.moved])
+        else:
+            torch._foreach_copy_(g.inp, [t for t in state])
+        g.tok.copy_(idx)
+        g.graph.replay()
+        return g.logits.clone(), list(g.out)
+
+    def _forward_batch_eager(self, idx, state):
+        with torch.no_grad():
+            w, a = self.w, self.args
+            B = idx.numel()
+            state = self.zero_batch_state(B) if state is None else list(state)
+            x = w["emb.weight"].index_select(0, idx)
             for i in range(a.n_layer):
                 if self.version == 4:
                     x = self._att_seq_v4(x, state, i, rows=True)

@@ -62,3 +62,28 @@ def test_forward_batch_from_zero_state():
         lo, _ = oracle.forward([t], None)
         assert (logits[b].cpu() - lo).abs().max().item() < TOL
     assert torch.equal(logits[0], logits[2])
+
+
+def test_forward_batch_graph_and_eager_agree(monkeypatch):
+    """The CUDA-graph replay (default) and direct launches give the same bits; a state list from another source
+    (a snapshot) can be passed back in."""
+    from chatrwkv_b200.model import RWKV
+    ck = synth.make_checkpoint(**TOY["v6"])
+    mg = RWKV(copy.deepcopy(ck), "cuda fp16i8", verbose=False)
+    monkeypatch.setenv("RWKV_B200_BATCH_GRAPH", "0")
+    me = RWKV(copy.deepcopy(ck), "cuda fp16i8", verbose=False)
+    monkeypatch.setenv("RWKV_B200_BATCH_GRAPH", "1")
+    sg = se = None
+    toks = [[3, 9, 27, 81, 243, 1, 2, 4, 8], [5, 25, 125, 7, 49, 11, 121, 13, 169]]
+    snap = None
+    for step in range(4):
+        t = toks[step % 2]
+        lg, sg = mg.forward_batch(t, sg)
+        le, se = me.forward_batch(t, se)
+        assert torch.equal(lg, le), step
+        if step == 1:
+            snap = copy.deepcopy(sg)
+            keep = lg.clone()
+    l2, _ = mg.forward_batch(toks[1], copy.deepcopy(snap))      # not the graph's own output list: copied in
+    l3, _ = me.forward_batch(toks[1], copy.deepcopy(snap))
+    assert torch.equal(l2, l3)
