@@ -189,6 +189,8 @@ def main():
     ap.add_argument("--sequences", type=int, default=0,
                     help="S independent sequences dealt to the ranks (s mod N), each with its own prefill of --prompt "
                          "tokens and --steps greedy tokens; value = decoded tokens of all sequences / time")
+    ap.add_argument("--sweep-part", default="all", choices=["all", "mm8", "wkv"], help="with --sweep: which operators")
+    ap.add_argument("--sweep-T", type=int, default=0, help="with --sweep: only this row / step count")
     ap.add_argument("--batch", type=int, default=0,
                     help="batched decode: B sequences per GPU advance one token per step through RWKV.forward_batch; "
                          "value = B x GPUs x steps / time")
@@ -223,7 +225,7 @@ def main():
 
     if a.sweep:
         if rank == 0:
-            print(json.dumps(operator_sweep(torch.device("cuda", local_rank))), flush=True)
+            print(json.dumps(operator_sweep(torch.device("cuda", local_rank), part=a.sweep_part, only_T=a.sweep_T)), flush=True)
         return
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -484,7 +486,7 @@ def main():
         dist.destroy_process_group()
 
 
-def operator_sweep(dev, iters=24):
+def operator_sweep(dev, iters=24, part="all", only_T=0):
     """mm8_one / mm8_seq through torch.ops.rwkv on seeded inputs (weights N(0, 0.02) packed on the GPU,
     activations N(0, 1)), each timed as a CUDA graph of `iters` calls that cycle through enough
     distinct packed matrices to exceed L2 several times over; CUDA events around 3 replays."""
@@ -493,7 +495,7 @@ def operator_sweep(dev, iters=24):
     torch.cuda.set_device(dev)
     peak, how = measured_peaks()
     out = []
-    for (N, M) in [(4096, 4096), (4096, 16384), (16384, 4096), (5120, 20480)]:
+    for (N, M) in ([(4096, 4096), (4096, 16384), (16384, 4096), (5120, 20480)] if part in ("all", "mm8") else []):
         copies = max(2, int(600e6 // (N * M)) + 1)
         g = torch.Generator(device=dev).manual_seed(3000)
         packs = []
@@ -501,7 +503,7 @@ def operator_sweep(dev, iters=24):
             w = (torch.randn(N, M, generator=g, device=dev) * 0.02).half().float()
             packs.append(ops.quantize_weight(w, torch.float16))
             del w
-        for T in (1, 16, 128, 1024):
+        for T in ((1, 16, 128, 1024) if only_T == 0 else (only_T,)):
             x = torch.randn((T, N) if T > 1 else (N,), generator=g, device=dev).half()
             y = torch.zeros(M, dtype=torch.float32, device=dev) if T == 1 else \
                 torch.empty((T, M), dtype=torch.float16, device=dev)
@@ -540,7 +542,7 @@ def operator_sweep(dev, iters=24):
     C, H = 4096, 64
     Nh = C // H
     g = torch.Generator(device=dev).manual_seed(3001)
-    for T in (16, 256, 2048):
+    for T in (((16, 256, 2048) if only_T == 0 else (only_T,)) if part in ("all", "wkv") else ()):
         k, v, r = (torch.randn(T, C, generator=g, device=dev) for _ in range(3))
         w6 = torch.exp(-torch.exp(torch.rand(T, C, generator=g, device=dev) * 6 - 5))
         w4, u = -torch.exp(torch.rand(C, generator=g, device=dev) * 6 - 5), torch.rand(C, generator=g, device=dev) * 2 - 1
