@@ -58,7 +58,7 @@ struct Batch {
     int trace_id;       // launch number for the optional timeline below
 };
 
-// Optional per-CTA timeline for tuning (compiled in only with -DRWKV_MM8_TRACE): eight words per
+// Optional per-CTA timeline for tuning (compiled in only with -DRWKV_MM8_TRACE): sixteen words per
 // CTA per launch -- %globaltimer at entry, ring issued, predecessor done, prologue done, stream
 // done, split reduction reached, exit; then the SM id.
 #ifdef RWKV_MM8_TRACE
@@ -75,7 +75,7 @@ __device__ __forceinline__ void mm8_stamp(unsigned long long* row, int slot) {
 // the row pointer is fetched once, at entry: a stamp is then one posted store
 #define MM8_TRACE_BEGIN(launch, cta)                                                                   \
     unsigned long long* mm8_tr = (threadIdx.x == 0 && g_mm8_trace != nullptr && (cta) < 1024)         \
-                                     ? g_mm8_trace + ((long long)(launch) * 1024 + (cta)) * 8 : nullptr
+                                     ? g_mm8_trace + ((long long)(launch) * 1024 + (cta)) * 16 : nullptr
 #define MM8_STAMP(launch, cta, slot) mm8_stamp(mm8_tr, slot)
 #else
 #define MM8_TRACE_BEGIN(launch, cta) do { } while (0)

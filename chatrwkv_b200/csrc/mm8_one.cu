@@ -29,7 +29,7 @@
 // Prologues (what x is) and epilogues (what happens to y) fuse the pointwise neighbours of
 // the matmuls in att_one / ffn_one (pkg/model.py:984-992, 1034-1055).
 #include "mm8_core.cuh"
-#include "mm8_cluster.cuh"
+#include "mm8_lean.cuh"
 
 namespace {
 
@@ -273,6 +273,29 @@ extern "C" size_t rwkv_mm8_one_workspace_bytes(int64_t N, int64_t M) {
     return mm8_ws_bytes_for(&m, 1);
 }
 
+#ifdef RWKV_MM8_TRACE
+// tuning builds only: where the per-CTA timeline goes ([launch][1024 CTAs][16] words); restarts the launch count
+extern "C" int rwkv_mm8_trace_set(unsigned long long* buffer) {
+    g_mm8_trace_next = 0;
+    return cudaMemcpyToSymbol(g_mm8_trace, &buffer, sizeof(buffer)) == cudaSuccess ? RWKV_OK : RWKV_ERR_LAUNCH;
+}
+#endif
+
+extern "C" int rwkv_mm8_one_take_error(void* stream, int* error) {
+    RWKV_CHECK_ARG(error != nullptr);
+    unsigned* word = lean_error_word();
+    if (word == nullptr) return RWKV_ERR_LAUNCH;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned v = 0;
+    if (cudaMemcpyAsync(&v, word, sizeof(v), cudaMemcpyDeviceToHost, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess) {
+        cudaGetLastError();
+        return RWKV_ERR_LAUNCH;
+    }
+    if (v != 0 && cudaMemsetAsync(word, 0, sizeof(v), st) != cudaSuccess) { cudaGetLastError(); return RWKV_ERR_LAUNCH; }
+    *error = int(v);
+    return RWKV_OK;
+}
+
 extern "C" size_t rwkv_mm8_one_batch_workspace_bytes(const rwkv_mm8_problem* problems, int count) {
     return mm8_batch_ws_bytes(problems, count);
 }
@@ -330,6 +353,10 @@ static int mm8_one_batch_impl(const rwkv_mm8_problem* problems, int count, const
     if (aligned && (g_variant & 3) == 0 && g_split_override == 0) {
         // K-splits of a panel as one thread-block cluster (mm8_cluster.cuh); falls through to the
         // ticket kernel when the batch is not eligible.
+        if (exp == nullptr && dtype == RWKV_F16 && (g_variant & 12) == 0) {
+            const int lrc = mm8_lean_launch(plan.b, count, (flags & RWKV_MM8_WIDE_BUILD) != 0, static_cast<cudaStream_t>(stream));
+            if (lrc != RWKV_ERR_UNSUPPORTED) return lrc;
+        }
         const int crc = mm8_cluster_launch(plan.b, count, dtype, (g_variant & 4) ? 0 : (g_variant & 8) ? 1 : 2, exp, (flags & RWKV_MM8_WIDE_BUILD) != 0,
                                            static_cast<cudaStream_t>(stream));
         if (crc != RWKV_ERR_UNSUPPORTED) return crc;

@@ -227,6 +227,11 @@ typedef struct {
 #define RWKV_MM8_WIDE_BUILD 1
 int rwkv_mm8_one_batch_flags(const rwkv_mm8_problem* problems, int count, const rwkv_mm8_exchange* exchange, int dtype,
                              int flags, void* workspace, size_t workspace_bytes, void* stream);
+/* Decode launches that qualify (fp16 activations, integer arithmetic, row slices that fit its staging areas, no
+ * exchange) run on a kernel that fetches its constants with bulk copies and waits for them on an mbarrier with an
+ * iteration limit.  1 in *error if such a wait gave up since the last call (results were then undefined); the word
+ * is cleared.  Synchronises `stream`.  RWKV_B200_LEAN=0 in the environment keeps every launch on the general kernel. */
+int rwkv_mm8_one_take_error(void* stream, int* error);
 int rwkv_mm8_one_batch_exchange(const rwkv_mm8_problem* problems, int count, const rwkv_mm8_exchange* exchange,
                                 int dtype, void* workspace, size_t workspace_bytes, void* stream);
 int rwkv_peer_alloc(size_t bytes, void** ptr_out);          /* zeroed device memory that can be exported */
