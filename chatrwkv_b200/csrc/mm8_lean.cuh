@@ -117,6 +117,11 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_lean_kernel(const __grid_cons
     F* s_mx = s_rx + kStageEpiCols;
     float* gather = reinterpret_cast<float*>(stage);     // [S][per] after the prologue: the ranks' sums of MY columns
     const int ncol8 = (kc1 - kc0) & ~7;                  // columns whose rx, mx come by bulk copy
+    // divisions that the code after the wait would otherwise pay for
+    const unsigned m_per = 0xffffffffu / unsigned(per) + 1u;            // per >= 8
+    const int qmax = min(32767, 0x7fffffff / (255 * max(nsteps, 1)));   // see the quantisation below
+    const float invn = 1.0f / float(P.N);
+    const int cnt = (active && sub < nrows) ? fast_div(nrows - sub + rpp - 1, rpp, m_rpp) : 0;     // rows of this thread
 
     // ---- before the preceding kernel is known to be done: model constants and last token's state ----
     if (tid == 0) {
@@ -240,7 +245,6 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_lean_kernel(const __grid_cons
         float t1 = 0.f, t2 = 0.f;
 #pragma unroll
         for (int w8 = 0; w8 < kWarps; ++w8) { t1 += sh8[w8]; t2 += sh8[kWarps + w8]; }
-        const float invn = 1.0f / float(P.N);
         const float dm = t1 * invn;
         const float mean = shift + dm;
         const float rstd = rsqrtf(fmaxf(fmaf(-dm, dm, t2 * invn), 0.f) + 1e-5f);
@@ -344,7 +348,6 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_lean_kernel(const __grid_cons
 #pragma unroll
     for (int w8 = 0; w8 < kWarps; ++w8) { xm = fmaxf(xm, ssum[w8][3]); xt += ssum[w8][1]; }
     if (!(xt == xt)) xm = __int_as_float(0x7f800000);    // a NaN does not show in a max but does in the sum
-    const int qmax = min(32767, 0x7fffffff / (255 * max(nsteps, 1)));
     const bool finite = xm < 3.0e38f;                    // false for inf and NaN
     const float scale = (finite && xm > 0.f) ? float(qmax) / xm : 0.f;
     const float inv_scale = !finite ? __int_as_float(0x7fc00000) : xm > 0.f ? xm / float(qmax) : 0.f;
@@ -370,7 +373,6 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_lean_kernel(const __grid_cons
 #pragma unroll
         for (int i = 0; i < 16; ++i) iacc[i] = 0;
         int sq = 0;
-        const int cnt = (active && sub < nrows) ? fast_div(nrows - sub + rpp - 1, rpp, m_rpp) : 0;     // rows of this thread
         const int* xq_ptr = xs + sub;
         const uint8_t* wn = wp + (long long)(kDepthC * kGroup) * step;
         const long long step2 = 2 * step, step3 = 3 * step;
@@ -422,7 +424,6 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_lean_kernel(const __grid_cons
     // every CTA of the cluster is past its prologue: its stage area may now receive column sums
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
     {
-        const unsigned m_per = 0xffffffffu / unsigned(per) + 1u;      // per >= 8
         const uint32_t gat = lean_s2u(gather) + uint32_t(rank * per) * 4u;
         for (int kk = tid; kk < ncols; kk += kThreads) {
             const float* src = red + (kk >> 4) * 20 + (kk & 15);
@@ -524,13 +525,15 @@ static inline int mm8_lean_launch(const Batch& plan_b, int count, bool wide_hint
     }
     int slots = cluster_slots(kern, S, smem, wide);
     if (slots <= 0) return RWKV_ERR_UNSUPPORTED;
-    // the same planning as mm8_cluster_launch: four fifths of the resident clusters unless told otherwise
+    // Planning as in mm8_cluster_launch: launches of several matrices take four fifths of the resident clusters
+    // (the free slots let the successor's first clusters fill their rings early); a launch of ONE matrix takes
+    // all of them (measured at the 7B shape: 608 -> 618 tok/s; with every launch on all slots: 600).
     {
         int planned = 0;
         for (int i = 0; i < g_plan_n; ++i) if (g_plan[i].cols == total_cols) planned = g_plan[i].clusters;
         if (planned > 0) { if (planned < slots) slots = planned; }
         else if (g_cluster_pw < 0) { if (-g_cluster_pw < slots) slots = -g_cluster_pw; }
-        else if (g_cluster_pw == 0 && slots >= 10) slots = slots * 4 / 5;
+        else if (g_cluster_pw == 0 && slots >= 10 && count > 1) slots = slots * 4 / 5;
     }
     int pw = g_cluster_pw > 0 ? (g_cluster_pw + 15) / 16 * 16 : 16;
     if (pw > kMaxPanelCols) pw = kMaxPanelCols;
