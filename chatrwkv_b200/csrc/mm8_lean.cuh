@@ -201,8 +201,23 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_lean_kernel(const __grid_cons
     }
     const bool writer = panel == 0;
     float sx = 0.f, sxr = 0.f, sxmy = 0.f, xmax = 0.f;
+    // Rows are dealt in pairs: thread t owns rows 2t, 2t + 1 (+ 512 per further round) of the CTA's slice, so that
+    // every operand of a pair is one 32-bit (fp16 pair) or 64-bit (fp32 pair) access.
     constexpr int RPT = ROWS / kThreads;                 // rows per thread: 8 or 10
-    float keep[RPT];                                     // this thread's x' (row tid + i * 256 of the slice)
+    constexpr int NI_PLAIN = RPT / 2, NI_STAGED = kLeanExtraRows / (2 * kThreads);
+    float keep[RPT];                                     // this thread's x' (rows 2 * (tid + 256 i) + {0, 1})
+    const __half2* ry2 = reinterpret_cast<const __half2*>(s_ry);
+    const __half2* my2 = reinterpret_cast<const __half2*>(s_my);
+    auto tail = [&](int slot, int lp, float2 xv) {       // x' = x * ry and the three sums the affine part needs
+        const float2 ryf = __half22float2(ry2[lp]), myf = __half22float2(my2[lp]);
+        const float xa = xv.x * ryf.x, xb = xv.y * ryf.y;
+        keep[slot] = xa;
+        keep[slot + 1] = xb;
+        sx += xv.x + xv.y;
+        sxr += xa + xb;
+        sxmy = fmaf(xv.x, myf.x, fmaf(xv.y, myf.y, sxmy));
+        xmax = fmaxf(xmax, fmaxf(fabsf(xa), fabsf(xb)));
+    };
     auto wait_staged = [&]() {
         const uint32_t bar = lean_s2u(&mbar);
         unsigned it = 0;
@@ -248,90 +263,97 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_lean_kernel(const __grid_cons
         const float dm = t1 * invn;
         const float mean = shift + dm;
         const float rstd = rsqrtf(fmaxf(fmaf(-dm, dm, t2 * invn), 0.f) + 1e-5f);
-        const F* lw = reinterpret_cast<const F*>(s_extra);
-        const F* lb = reinterpret_cast<const F*>(s_extra + 2048);
-        const F* mixv = reinterpret_cast<const F*>(s_extra + 4096);
-        const F* sxp = reinterpret_cast<const F*>(s_extra + 6144);
+        const __half2* x2 = reinterpret_cast<const __half2*>(s_xrow);
+        const __half2* lw2 = reinterpret_cast<const __half2*>(s_extra);
+        const __half2* lb2 = reinterpret_cast<const __half2*>(s_extra + 2048);
+        const __half2* mix2 = reinterpret_cast<const __half2*>(s_extra + 4096);
+        const __half2* sx2 = reinterpret_cast<const __half2*>(s_extra + 6144);
+        const int pmode = P.mode;
+        const bool put_xx = writer && P.q0 != nullptr;
 #pragma unroll
-        for (int i = 0; i < kLeanExtraRows / kThreads; ++i) {
-            const int l = tid + i * kThreads;
-            if (l < nrows) {
-                const float xx = r16((__half2float(s_xrow[l]) - mean) * rstd * __half2float(lw[l]) + __half2float(lb[l]));
-                if (writer && P.q0) static_cast<__half*>(P.q0)[j0 + l] = __float2half_rn(xx);
-                float xv = xx;
-                if (P.mode != 2) {
-                    const float sxv = __half2float(sxp[l]), mv = __half2float(mixv[l]);
-                    xv = P.mode == 0 ? r16(r16(xx * mv) + r16(sxv * r16(1.0f - mv))) : r16(xx + r16(r16(sxv - xx) * mv));
+        for (int i = 0; i < NI_STAGED; ++i) {
+            const int lp = tid + i * kThreads;
+            if (2 * lp < nrows) {
+                const float2 xf = __half22float2(x2[lp]), wf = __half22float2(lw2[lp]), bf = __half22float2(lb2[lp]);
+                float2 xx;
+                xx.x = r16((xf.x - mean) * rstd * wf.x + bf.x);
+                xx.y = r16((xf.y - mean) * rstd * wf.y + bf.y);
+                if (put_xx) reinterpret_cast<__half2*>(static_cast<__half*>(P.q0) + j0)[lp] = __floats2half2_rn(xx.x, xx.y);
+                float2 xv = xx;
+                if (pmode != 2) {
+                    const float2 sv = __half22float2(sx2[lp]), mv = __half22float2(mix2[lp]);
+                    if (pmode == 0) {
+                        xv.x = r16(r16(xx.x * mv.x) + r16(sv.x * r16(1.0f - mv.x)));
+                        xv.y = r16(r16(xx.y * mv.y) + r16(sv.y * r16(1.0f - mv.y)));
+                    } else {
+                        xv.x = r16(xx.x + r16(r16(sv.x - xx.x) * mv.x));
+                        xv.y = r16(xx.y + r16(r16(sv.y - xx.y) * mv.y));
+                    }
                 }
-                const float xp = xv * __half2float(s_ry[l]);
-                keep[i] = xp;
-                sx += xv;
-                sxr += xp;
-                sxmy = fmaf(xv, __half2float(s_my[l]), sxmy);
-                xmax = fmaxf(xmax, fabsf(xp));
+                tail(2 * i, lp, xv);
             }
         }
     } else if (P.prologue == RWKV_PRO_WKV4) {            // pkg/model.py:1041-1055
-        float rr[kLeanExtraRows / kThreads], kq[kLeanExtraRows / kThreads], vq[kLeanExtraRows / kThreads];
+        __half2 rr[NI_STAGED], kq[NI_STAGED], vq[NI_STAGED];
 #pragma unroll
-        for (int i = 0; i < kLeanExtraRows / kThreads; ++i) {
-            const int l = tid + i * kThreads;
-            rr[i] = kq[i] = vq[i] = 0.f;
-            if (l < nrows) { rr[i] = ldc<__half>(P.x, j0 + l); kq[i] = ldc<__half>(P.p0, j0 + l); vq[i] = ldc<__half>(P.p1, j0 + l); }
+        for (int i = 0; i < NI_STAGED; ++i) {
+            const int lp = tid + i * kThreads;
+            if (2 * lp < nrows) {
+                rr[i] = __ldcg(reinterpret_cast<const __half2*>(static_cast<const __half*>(P.x) + j0) + lp);
+                kq[i] = __ldcg(reinterpret_cast<const __half2*>(static_cast<const __half*>(P.p0) + j0) + lp);
+                vq[i] = __ldcg(reinterpret_cast<const __half2*>(static_cast<const __half*>(P.p1) + j0) + lp);
+            }
         }
         wait_staged();
-        const float* tdv = reinterpret_cast<const float*>(s_extra);
-        const float* tfv = reinterpret_cast<const float*>(s_extra + 4096);
-        const float* av = reinterpret_cast<const float*>(s_extra + 8192);
-        const float* bv = reinterpret_cast<const float*>(s_extra + 12288);
-        const float* pv = reinterpret_cast<const float*>(s_extra + 16384);
+        const float2* td2 = reinterpret_cast<const float2*>(s_extra);
+        const float2* tf2 = reinterpret_cast<const float2*>(s_extra + 4096);
+        const float2* a2 = reinterpret_cast<const float2*>(s_extra + 8192);
+        const float2* b2 = reinterpret_cast<const float2*>(s_extra + 12288);
+        const float2* p2 = reinterpret_cast<const float2*>(s_extra + 16384);
+        auto one = [&](float r, float kk, float vv, float a, float bq, float p0, float td, float tf, float& na, float& nb, float& np) {
+            float ww = tf + kk;
+            float p = fmaxf(p0, ww);
+            float e1 = expf(p0 - p), e2 = expf(ww - p);
+            const float wkv = r16((e1 * a + e2 * vv) / (e1 * bq + e2));
+            if (writer) {                                // the new state: once per launch, by the CTAs of the first panel
+                ww = td + p0;
+                p = fmaxf(ww, kk);
+                e1 = expf(ww - p); e2 = expf(kk - p);
+                na = e1 * a + e2 * vv;
+                nb = e1 * bq + e2;
+                np = p;
+            }
+            return r16(r * wkv);
+        };
 #pragma unroll
-        for (int i = 0; i < kLeanExtraRows / kThreads; ++i) {
-            const int l = tid + i * kThreads;
-            if (l < nrows) {
-                const float r = rr[i], kk = kq[i], vv = vq[i];
-                const float a = av[l], bq = bv[l], p0 = pv[l];
-                float ww = tfv[l] + kk;
-                float p = fmaxf(p0, ww);
-                float e1 = expf(p0 - p), e2 = expf(ww - p);
-                const float wkv = r16((e1 * a + e2 * vv) / (e1 * bq + e2));
+        for (int i = 0; i < NI_STAGED; ++i) {
+            const int lp = tid + i * kThreads;
+            if (2 * lp < nrows) {
+                const float2 r = __half22float2(rr[i]), kk = __half22float2(kq[i]), vv = __half22float2(vq[i]);
+                const float2 a = a2[lp], bq = b2[lp], p0 = p2[lp], td = td2[lp], tf = tf2[lp];
+                float2 na = make_float2(0.f, 0.f), nb = na, np = na, xv;
+                xv.x = one(r.x, kk.x, vv.x, a.x, bq.x, p0.x, td.x, tf.x, na.x, nb.x, np.x);
+                xv.y = one(r.y, kk.y, vv.y, a.y, bq.y, p0.y, td.y, tf.y, na.y, nb.y, np.y);
                 if (writer) {
-                    ww = tdv[l] + p0;
-                    p = fmaxf(ww, kk);
-                    e1 = expf(ww - p); e2 = expf(kk - p);
-                    P.g0[j0 + l] = e1 * a + e2 * vv;
-                    P.g1[j0 + l] = e1 * bq + e2;
-                    P.g2[j0 + l] = p;
+                    reinterpret_cast<float2*>(P.g0 + j0)[lp] = na;
+                    reinterpret_cast<float2*>(P.g1 + j0)[lp] = nb;
+                    reinterpret_cast<float2*>(P.g2 + j0)[lp] = np;
                 }
-                const float xv = r16(r * wkv);
-                const float xp = xv * __half2float(s_ry[l]);
-                keep[i] = xp;
-                sx += xv;
-                sxr += xp;
-                sxmy = fmaf(xv, __half2float(s_my[l]), sxmy);
-                xmax = fmaxf(xmax, fabsf(xp));
+                tail(2 * i, lp, xv);
             }
         }
     } else {
-        float xr[RPT];
+        __half2 xr[NI_PLAIN];
 #pragma unroll
-        for (int i = 0; i < RPT; ++i) {
-            const int l = tid + i * kThreads;
-            xr[i] = l < nrows ? ldc<F>(P.x, j0 + l) : 0.f;
+        for (int i = 0; i < NI_PLAIN; ++i) {
+            const int lp = tid + i * kThreads;
+            if (2 * lp < nrows) xr[i] = __ldcg(reinterpret_cast<const __half2*>(static_cast<const __half*>(P.x) + j0) + lp);
         }
         wait_staged();
 #pragma unroll
-        for (int i = 0; i < RPT; ++i) {
-            const int l = tid + i * kThreads;
-            if (l < nrows) {
-                const float xv = xr[i];
-                const float xp = xv * __half2float(s_ry[l]);
-                keep[i] = xp;
-                sx += xv;
-                sxr += xp;
-                sxmy = fmaf(xv, __half2float(s_my[l]), sxmy);
-                xmax = fmaxf(xmax, fabsf(xp));
-            }
+        for (int i = 0; i < NI_PLAIN; ++i) {
+            const int lp = tid + i * kThreads;
+            if (2 * lp < nrows) tail(2 * i, lp, __half22float2(xr[i]));
         }
     }
     sx = warp_sum(sx); sxr = warp_sum(sxr); sxmy = warp_sum(sxmy); xmax = warp_max(xmax);
@@ -353,13 +375,16 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_lean_kernel(const __grid_cons
     const float inv_scale = !finite ? __int_as_float(0x7fc00000) : xm > 0.f ? xm / float(qmax) : 0.f;
     {
         uint16_t* xq16 = reinterpret_cast<uint16_t*>(xs);
-        const int nkeep = (P.prologue == RWKV_PRO_PLAIN) ? RPT : kLeanExtraRows / kThreads;
+        const int ni = (P.prologue == RWKV_PRO_PLAIN) ? NI_PLAIN : NI_STAGED;
 #pragma unroll
-        for (int i = 0; i < RPT; ++i) {
-            const int l = tid + i * kThreads;
-            if (i < nkeep && l < nrows) {
-                const int st = fast_div(l, rpp, m_rpp), so = l - st * rpp;
-                xq16[(((st >> 1) * rpp + so) << 1) + (st & 1)] = uint16_t(__float2int_rn(keep[i] * scale));
+        for (int i = 0; i < NI_PLAIN; ++i) {
+            const int l = 2 * (tid + i * kThreads);
+            if (i < ni && l < nrows) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int st = fast_div(l + e, rpp, m_rpp), so = l + e - st * rpp;
+                    xq16[(((st >> 1) * rpp + so) << 1) + (st & 1)] = uint16_t(__float2int_rn(keep[2 * i + e] * scale));
+                }
             }
         }
     }
@@ -421,8 +446,10 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_lean_kernel(const __grid_cons
         for (int q = 0; q < 4; ++q) dst[q] = make_float4(acc[q * 4], acc[q * 4 + 1], acc[q * 4 + 2], acc[q * 4 + 3]);
     }
     __syncthreads();
+    MM8_STAMP(b.trace_id, blockIdx.x, 12);
     // every CTA of the cluster is past its prologue: its stage area may now receive column sums
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    MM8_STAMP(b.trace_id, blockIdx.x, 8);
     {
         const uint32_t gat = lean_s2u(gather) + uint32_t(rank * per) * 4u;
         for (int kk = tid; kk < ncols; kk += kThreads) {
@@ -440,20 +467,28 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_lean_kernel(const __grid_cons
             st_remote_f32(lean_s2u(&gat3[rank][tid & 3]), uint32_t(tid >> 2), s);
         }
     }
+    MM8_STAMP(b.trace_id, blockIdx.x, 14);
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     MM8_STAMP(b.trace_id, blockIdx.x, 5);
 
     // ---- finish this CTA's columns: the ranks' sums in rank order (bit-reproducible), affine tail, epilogue
     float tx = 0.f, txr = 0.f, txmy = 0.f;
-    for (int q = 0; q < S; ++q) { tx += gat3[q][0]; txr += gat3[q][1]; txmy += gat3[q][2]; }
+#pragma unroll
+    for (int q = 0; q < kMaxClusterSize; ++q) {
+        if (q < S) { tx += gat3[q][0]; txr += gat3[q][1]; txmy += gat3[q][2]; }
+    }
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
         const int kk = kc0 + tid + it * kThreads;
         if (kk < kc1) {
             const int e = kk - kc0;
+            float part[kMaxClusterSize];
+#pragma unroll
+            for (int q = 0; q < kMaxClusterSize; ++q) part[q] = q < S ? gather[q * per + e] : 0.f;
             float s = 0.f;
-            for (int q = 0; q < S; ++q) s += gather[q * per + e];
+#pragma unroll
+            for (int q = 0; q < kMaxClusterSize; ++q) s += part[q];
             const float rxk = __half2float(s_rx[e]), mxk = __half2float(s_mx[e]);
             const float val = fmaf(rxk, s, fmaf(rxk * 128.5f, txr, fmaf(mxk, tx, txmy)));
             store_epilogue_with<F>(P, col0 + kk, val, auxr[it], aux2r[it]);
@@ -501,9 +536,16 @@ static inline int mm8_lean_launch(const Batch& plan_b, int count, bool wide_hint
         if (q.prologue == RWKV_PRO_LN_MIX) {
             if (!lean_aligned16(q.p0) || !lean_aligned16(q.p1) || !lean_aligned16(q.x)) return RWKV_ERR_UNSUPPORTED;
             if (q.mode != 2 && (!lean_aligned16(q.p2) || !lean_aligned16(q.p3))) return RWKV_ERR_UNSUPPORTED;
+            if (q.q0 != nullptr && (reinterpret_cast<uintptr_t>(q.q0) & 3) != 0) return RWKV_ERR_UNSUPPORTED;
         } else if (q.prologue == RWKV_PRO_WKV4) {
             if (!lean_aligned16(q.f0) || !lean_aligned16(q.f1) || !lean_aligned16(q.f2) || !lean_aligned16(q.f3) || !lean_aligned16(q.f4))
                 return RWKV_ERR_UNSUPPORTED;
+            // rows go in pairs: fp16 pairs of r, k, v and fp32 pairs of the new state
+            if (((reinterpret_cast<uintptr_t>(q.x) | reinterpret_cast<uintptr_t>(q.p0) | reinterpret_cast<uintptr_t>(q.p1)) & 3) != 0 ||
+                ((reinterpret_cast<uintptr_t>(q.g0) | reinterpret_cast<uintptr_t>(q.g1) | reinterpret_cast<uintptr_t>(q.g2)) & 7) != 0)
+                return RWKV_ERR_UNSUPPORTED;
+        } else if ((reinterpret_cast<uintptr_t>(q.x) & 3) != 0) {
+            return RWKV_ERR_UNSUPPORTED;
         }
     }
     for (int i = count; i < kMaxProblems; ++i) lb.p[i] = lb.p[0];
