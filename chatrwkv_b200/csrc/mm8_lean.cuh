@@ -474,21 +474,24 @@ __global__ void __launch_bounds__(kThreads, 2) mm8_lean_kernel(const __grid_cons
 
     // ---- finish this CTA's columns: the ranks' sums in rank order (bit-reproducible), affine tail, epilogue
     float tx = 0.f, txr = 0.f, txmy = 0.f;
+    if (S == kMaxClusterSize) {                          // the usual case, unrolled: all loads first
 #pragma unroll
-    for (int q = 0; q < kMaxClusterSize; ++q) {
-        if (q < S) { tx += gat3[q][0]; txr += gat3[q][1]; txmy += gat3[q][2]; }
+        for (int q = 0; q < kMaxClusterSize; ++q) { tx += gat3[q][0]; txr += gat3[q][1]; txmy += gat3[q][2]; }
+    } else {
+        for (int q = 0; q < S; ++q) { tx += gat3[q][0]; txr += gat3[q][1]; txmy += gat3[q][2]; }
     }
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
         const int kk = kc0 + tid + it * kThreads;
         if (kk < kc1) {
             const int e = kk - kc0;
-            float part[kMaxClusterSize];
-#pragma unroll
-            for (int q = 0; q < kMaxClusterSize; ++q) part[q] = q < S ? gather[q * per + e] : 0.f;
             float s = 0.f;
+            if (S == kMaxClusterSize) {
 #pragma unroll
-            for (int q = 0; q < kMaxClusterSize; ++q) s += part[q];
+                for (int q = 0; q < kMaxClusterSize; ++q) s += gather[q * per + e];
+            } else {
+                for (int q = 0; q < S; ++q) s += gather[q * per + e];
+            }
             const float rxk = __half2float(s_rx[e]), mxk = __half2float(s_mx[e]);
             const float val = fmaf(rxk, s, fmaf(rxk * 128.5f, txr, fmaf(mxk, tx, txmy)));
             store_epilogue_with<F>(P, col0 + kk, val, auxr[it], aux2r[it]);
