@@ -426,13 +426,14 @@ def main():
     if rank == 0 and not sharded and a.layers == 0:
         from chatrwkv_b200 import _lib
         n_alt = min(64, a.steps)
-        alts = [("launch_per_matmul_fp32_arithmetic", "launch", 8)]
+        alts = [("launch_per_matmul_fp32_arithmetic", "launch", 8), ("launch_per_matmul_general_kernel", "launch", -1)]
         if version == 4:
             alts.append(("persistent_weight_stream_kernel", "stream", 0))
         for label, path, variant in alts:
             if path == path_default and variant == 0:
                 continue
-            _lib.lib().rwkv_mm8_one_set_variant(variant)
+            _lib.lib().rwkv_mm8_one_set_variant(max(variant, 0))
+            _lib.lib().rwkv_mm8_one_set_lean(0 if variant < 0 else -1)        # -1 here: mm8_cluster_kernel with the default arithmetic
             model.set_decode_path(path)
             tok, state = decode_loop(tok, state, 4)
             torch.cuda.synchronize(dev)
@@ -444,6 +445,7 @@ def main():
             if path == "stream":
                 other[label]["wait_error"] = model.stream_error()
         _lib.lib().rwkv_mm8_one_set_variant(0)
+        _lib.lib().rwkv_mm8_one_set_lean(-1)
         model.set_decode_path(path_default)
         tok, state = decode_loop(tok, state, 2)
 
@@ -610,7 +612,7 @@ def gemv_roofline(model, dev, reps=30):
         source = "scaled: DRAM bytes per algorithmic byte from an ncu capture of a 2-layer model of the same shape"
     except Exception:
         pass
-    kernel = "mm8_stream_kernel" if path == "stream" else "mm8_cluster_kernel"
+    kernel = "mm8_stream_kernel" if path == "stream" else "mm8_lean_kernel"
     return {"bound": "hbm", "kernel": kernel, "achieved": achieved,
             "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": how, "traffic": traffic,
             "traffic_source": source, "launches_per_step": n_launch, "avg_launch_us": ms / n_launch * 1e3,

@@ -64,6 +64,7 @@ SIGNATURES = {
     "rwkv_mm8_one_batch_workspace_bytes": (_sz, [C.POINTER(Mm8Problem), _i32]),
     "rwkv_mm8_one_batch": (_i32, [C.POINTER(Mm8Problem), _i32, _i32, _vp, _sz, _vp]),
     "rwkv_mm8_one_batch_exchange": (_i32, [C.POINTER(Mm8Problem), _i32, C.POINTER(Mm8Exchange), _i32, _vp, _sz, _vp]),
+    "rwkv_mm8_one_set_lean": (None, [_i32]),
     "rwkv_mm8_one_take_error": (_i32, [_vp, C.POINTER(C.c_int)]),
     "rwkv_mm8_one_batch_flags": (_i32, [C.POINTER(Mm8Problem), _i32, C.POINTER(Mm8Exchange), _i32, _i32, _vp, _sz, _vp]),
     "rwkv_peer_alloc": (_i32, [_sz, C.POINTER(_vp)]),

@@ -16,9 +16,11 @@
 //     (remote stores), so one cluster barrier replaces barrier + remote loads + barrier, and a CTA
 //     leaves as soon as its own columns are stored;
 //   * index arithmetic by multiply-high with reciprocals that the host tabulates for full-width panels.
-// Results are bit-identical to mm8_cluster_kernel's except for the LayerNorm statistics, which are
-// taken in one pass around x[0] instead of two passes (differences of an ulp of fp32 before the fp16
-// rounding).  Launches that do not qualify go to mm8_cluster_kernel.
+// The integer dot products are exact as in mm8_cluster_kernel and the split-K sums are added in the same rank
+// order; results differ from that kernel's by the order of a few fp32 additions (the scalar sums of x, the row
+// groups of a panel of another width) and by the LayerNorm statistics, taken in one pass around x[0] instead of
+// two passes: ulps of fp32 before the fp16 rounding.  Two runs of this kernel are bit-identical.  Launches that
+// do not qualify go to mm8_cluster_kernel.
 #pragma once
 #include "mm8_cluster.cuh"
 
@@ -38,6 +40,7 @@ struct LeanBatch {
 };
 
 __device__ unsigned g_lean_error = 0;
+int g_use_lean = -1;             // -1 = the environment decides (RWKV_B200_LEAN=0 turns it off), else 0 / 1
 
 __device__ __forceinline__ int fast_div(int n, int d, unsigned m) { return d == 1 ? n : int(__umulhi(unsigned(n), m)); }
 __device__ __forceinline__ uint32_t lean_s2u(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -518,12 +521,11 @@ static inline unsigned* lean_error_word() {
 static inline bool lean_aligned16(const void* p) { return p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 static inline int mm8_lean_launch(const Batch& plan_b, int count, bool wide_hint, cudaStream_t st) {
-    static int use_lean = -1;
-    if (use_lean < 0) {
+    if (g_use_lean < 0) {
         const char* e = getenv("RWKV_B200_LEAN");
-        use_lean = (e != nullptr && e[0] == '0') ? 0 : 1;
+        g_use_lean = (e != nullptr && e[0] == '0') ? 0 : 1;
     }
-    if (!use_lean || g_cluster_size < 0) return RWKV_ERR_UNSUPPORTED;
+    if (!g_use_lean || g_cluster_size < 0) return RWKV_ERR_UNSUPPORTED;
     LeanBatch lb;
     memset(&lb, 0, sizeof(lb));
     int min_n = INT32_MAX, max_n = 0;
@@ -534,7 +536,7 @@ static inline int mm8_lean_launch(const Batch& plan_b, int count, bool wide_hint
         if (q.N < min_n) min_n = q.N;
         if (q.N > max_n) max_n = q.N;
         total_cols += q.M;
-        if (q.N % 8 != 0 || q.epilogue == RWKV_EPI_ACC_F32) return RWKV_ERR_UNSUPPORTED;
+        if (q.N % 8 != 0) return RWKV_ERR_UNSUPPORTED;
         if (!lean_aligned16(q.ry) || !lean_aligned16(q.my) || !lean_aligned16(q.rx) || !lean_aligned16(q.mx)) return RWKV_ERR_UNSUPPORTED;
         if (q.prologue == RWKV_PRO_LN_MIX) {
             if (!lean_aligned16(q.p0) || !lean_aligned16(q.p1) || !lean_aligned16(q.x)) return RWKV_ERR_UNSUPPORTED;

@@ -281,6 +281,8 @@ extern "C" int rwkv_mm8_trace_set(unsigned long long* buffer) {
 }
 #endif
 
+extern "C" void rwkv_mm8_one_set_lean(int on) { g_use_lean = on < 0 ? -1 : (on != 0); }
+
 extern "C" int rwkv_mm8_one_take_error(void* stream, int* error) {
     RWKV_CHECK_ARG(error != nullptr);
     unsigned* word = lean_error_word();

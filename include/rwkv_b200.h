@@ -232,6 +232,9 @@ int rwkv_mm8_one_batch_flags(const rwkv_mm8_problem* problems, int count, const 
  * iteration limit.  1 in *error if such a wait gave up since the last call (results were then undefined); the word
  * is cleared.  Synchronises `stream`.  RWKV_B200_LEAN=0 in the environment keeps every launch on the general kernel. */
 int rwkv_mm8_one_take_error(void* stream, int* error);
+/* Tuning / test hook like rwkv_mm8_one_set_variant: 0 keeps every launch on the general kernel, 1 allows the kernel
+ * above, -1 lets the environment decide again.  Process-wide; not thread-safe. */
+void rwkv_mm8_one_set_lean(int on);
 int rwkv_mm8_one_batch_exchange(const rwkv_mm8_problem* problems, int count, const rwkv_mm8_exchange* exchange,
                                 int dtype, void* workspace, size_t workspace_bytes, void* stream);
 int rwkv_peer_alloc(size_t bytes, void** ptr_out);          /* zeroed device memory that can be exported */
