@@ -576,8 +576,8 @@ def operator_sweep(dev, iters=24, part="all", only_T=0):
 
 
 def gemv_roofline(model, dev, reps=30):
-    """HBM roofline of the decode kernel.  One decode step is timed with CUDA events on the
-    launching stream (direct launches, no graph, token id already on the device) and divided
+    """HBM roofline of the decode kernel.  Decode steps are timed with CUDA events on the
+    launching stream (token id already on the device) and divided
     into the algorithmic bytes of its mm8_one problems: N*M weight bytes + 6N (x, my, ry) +
     4M (mx, rx) + the output vector, summed over every matmul of the token."""
     import torch
@@ -590,13 +590,22 @@ def gemv_roofline(model, dev, reps=30):
             tot_b += N * M + 6 * N + 4 * M + (4 if name == "head.weight" else 2) * M
     step_fn = model._step_one_v4 if v4 else model._step_one_v56
     path = model.decode_path()
-    for _ in range(3):
-        step_fn(model._cur)                     # reads the current state set, writes the other one
+    # the step as the runtime issues it: the captured CUDA graph of a token (embedding row gather + the launches) when
+    # graphs are on, else direct launches; a step reads one state set and writes the other, hence the alternation
+    graphs = getattr(model, "_graphs", None)
+    use_graph = bool(getattr(model, "_use_graph", False)) and graphs is not None and all(g is not None for g in graphs)
+    run = (lambda c: graphs[c].replay()) if use_graph else step_fn
+    reps += reps & 1
+    cur = model._cur
+    for _ in range(4):
+        run(cur)
+        cur ^= 1
     torch.cuda.synchronize(dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(reps):
-        step_fn(model._cur)
+        run(cur)
+        cur ^= 1
     e1.record()
     torch.cuda.synchronize(dev)
     ms = e0.elapsed_time(e1) / reps
@@ -617,6 +626,7 @@ def gemv_roofline(model, dev, reps=30):
             "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": how, "traffic": traffic,
             "traffic_source": source, "launches_per_step": n_launch, "avg_launch_us": ms / n_launch * 1e3,
             "algorithmic_bytes_per_launch": tot_b / n_launch, "frac_of_8000": achieved / 8000.0,
+            "timed": "CUDA events around %d replays of the token's CUDA graph" % reps if use_graph else "CUDA events around %d steps of direct launches" % reps,
             "wait_error": model.stream_error() if path == "stream" else 0}
 
 

@@ -64,6 +64,8 @@ SIGNATURES = {
     "rwkv_mm8_one_batch_workspace_bytes": (_sz, [C.POINTER(Mm8Problem), _i32]),
     "rwkv_mm8_one_batch": (_i32, [C.POINTER(Mm8Problem), _i32, _i32, _vp, _sz, _vp]),
     "rwkv_mm8_one_batch_exchange": (_i32, [C.POINTER(Mm8Problem), _i32, C.POINTER(Mm8Exchange), _i32, _vp, _sz, _vp]),
+    "rwkv_sample_logits": (_i32, [_i64, _vp, C.c_float, C.c_float, _i64, _vp, _vp, _vp, _vp, C.c_float, C.c_float, C.c_float,
+                                  _vp, _i64, _vp, _vp, _vp, _vp]),
     "rwkv_mm8_one_set_lean": (None, [_i32]),
     "rwkv_mm8_one_take_error": (_i32, [_vp, C.POINTER(C.c_int)]),
     "rwkv_mm8_one_batch_flags": (_i32, [C.POINTER(Mm8Problem), _i32, C.POINTER(Mm8Exchange), _i32, _i32, _vp, _sz, _vp]),

@@ -502,6 +502,28 @@ int rwkv_wkv56_one(int64_t H, int64_t N, const void* r, const void* k, const voi
                    const float* u, const float* state, float* new_state, const float* lnx_w,
                    const float* lnx_b, const void* g, void* out, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Token sampling on the device — PIPELINE.sample_logits and the penalty bookkeeping of
+ * PIPELINE.generate (pkg/utils.py:55-135), without the host round trip and without a sort.
+ *
+ * logits: fp32 [V] as forward() returns them (not modified), V <= 65536.  In order: banned[id] != 0 sets a logit to
+ * -inf; every id with seen[id] != 0 loses alpha_presence + occurrence[id] * alpha_frequency (utils.py:97-100);
+ * softmax; temperature == 0 means temperature 1 and top_p 0 (greedy); probabilities below the nucleus cutoff are
+ * dropped (the cutoff is the largest probability v whose probabilities >= v sum to at least top_p; if nothing
+ * reaches top_p only the most likely token stays, as in the reference); all but the top_k most likely are dropped
+ * (0 = off; ties by lowest id); p ** (1 / temperature); one draw by inverse CDF in id order on
+ * uniforms[*counter % n_uniforms] (numbers in [0, 1) supplied by the caller; NULL = 0.5; 0 picks the lowest id that
+ * has mass), after which *counter grows by one.  *token_out receives the id.  probs_out (or NULL) receives the
+ * normalised distribution the draw was made from.  Then, when occurrence / seen are given (both or neither):
+ * occurrence[id] *= alpha_decay for every seen id, occurrence[token] += token_weight[token] (NULL = 1), seen[token]
+ * = 1 (utils.py:111-122).  One cluster of 8 CTAs; safe inside stream capture.
+ * ------------------------------------------------------------------------------------- */
+int rwkv_sample_logits(int64_t V, const float* logits, float temperature, float top_p, int64_t top_k,
+                       float* occurrence, unsigned char* seen, const unsigned char* banned, const float* token_weight,
+                       float alpha_presence, float alpha_frequency, float alpha_decay,
+                       const float* uniforms, int64_t n_uniforms, uint32_t* counter,
+                       int64_t* token_out, float* probs_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
