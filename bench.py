@@ -21,6 +21,7 @@ streams (token seed 2000 + rank), no collective on the data path: weak scaling.
 from __future__ import annotations
 
 import argparse
+import copy as _copy
 import json
 import os
 import statistics
@@ -449,6 +450,34 @@ def main():
         model.set_decode_path(path_default)
         tok, state = decode_loop(tok, state, 2)
 
+    # ---- generation with the sampler on the device (nucleus sampling, penalties): the loop of PIPELINE.generate
+    sampling = None
+    if rank == 0 and not sharded and a.layers == 0 and version == 4:
+        from chatrwkv_b200.pipeline import PIPELINE, PIPELINE_ARGS
+        n_gen = min(64, a.steps)
+        pl = PIPELINE(model, seed=1)
+        pargs = PIPELINE_ARGS(temperature=1.0, top_p=0.85, top_k=0, alpha_frequency=0.2, alpha_presence=0.2)
+        sampling = {"steps": n_gen, "args": "temperature 1.0, top_p 0.85, presence/frequency penalties 0.2 (the reference's defaults)"}
+        for label, fn in (("token_stays_on_device", lambda st: pl.generate_tokens([int(tok)], n_gen, pargs, st)),
+                          ("token_to_host_every_step", lambda st: (pl.generate([int(tok)], n_gen, pargs, None, st), None))):
+            fn(_copy.deepcopy(state))
+            torch.cuda.synchronize(dev)
+            t0 = time.perf_counter()
+            fn(_copy.deepcopy(state))
+            torch.cuda.synchronize(dev)
+            sampling[label + "_tokens_per_s"] = n_gen / (time.perf_counter() - t0)
+        from chatrwkv_b200.pipeline import Sampler
+        smp = Sampler(V, dev, pargs, seed=2)
+        lg = torch.randn(V, device=dev)
+        for _ in range(3):
+            smp.sample(lg)
+        ev0.record()
+        for _ in range(20):
+            smp.sample(lg)
+        ev1.record()
+        torch.cuda.synchronize(dev)
+        sampling["sampler_kernel_us"] = ev0.elapsed_time(ev1) / 20 * 1e3
+
     # ---- roofline of the dominant kernel (rank 0): one decode step of direct launches, event-timed
     roof = None
     if rank == 0:
@@ -477,7 +506,7 @@ def main():
             "decode_path": path_default, "graph": bool(model._use_graph),
             "arithmetic": "x*ry as 30-bit fixed point per vector, exact 64-bit integer sums" if path_default == "stream"
                           else "x*ry as 16-bit fixed point per CTA slice, exact 32-bit integer sums (other_decode_paths: fp32)",
-            "other_decode_paths": other,
+            "other_decode_paths": other, "sampling": sampling,
             "prefill": {"tokens": a.prompt, "ms": prefill_ms, "tokens_per_s": a.prompt / (prefill_ms / 1e3)},
             "clocks": clocks, "roofline": roof, "cpu_baseline": cb,
         }
