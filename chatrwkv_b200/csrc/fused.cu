@@ -101,6 +101,101 @@ __global__ void __launch_bounds__(kLnThreads) ln_mix_kernel(const LnMixArgs a) {
     }
 }
 
+// The same computation with 16-byte accesses, every load of a row issued before the first reduction: the form for
+// aligned operands (D % 8 == 0, pointers 16-byte aligned, strides multiples of 8).  With a handful of rows (batched
+// decode) the per-element form above spends ~30 us in dependent scalar loads from cold memory; this one ~4 us.
+template <int VPT>      // vectors of 8 per thread: D <= 2048 * VPT
+__global__ void __launch_bounds__(kLnThreads) ln_mix_vec_kernel(const LnMixArgs a) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float sh[kLnThreads / 32];
+    const int t = blockIdx.x;
+    const int nvec = a.D >> 3;
+    const bool own_state = t == 0 || a.sx_stride != 0;      // else the previous row's LayerNorm output is the state
+    const bool mixing = a.n_mix > 0;
+    uint4 xv[VPT], pv[VPT], wv[VPT], bv[VPT], mv[5][VPT];
+    const uint4* xrow = reinterpret_cast<const uint4*>(a.x + (long long)t * a.x_stride);
+    const uint4* prow = mixing ? (own_state ? reinterpret_cast<const uint4*>(a.sx + (long long)t * a.sx_stride)
+                                            : reinterpret_cast<const uint4*>(a.x + (long long)(t - 1) * a.x_stride)) : nullptr;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * kLnThreads;
+        const bool ok = v < nvec;
+        xv[i] = ok ? xrow[v] : make_uint4(0, 0, 0, 0);
+        pv[i] = (ok && mixing) ? prow[v] : make_uint4(0, 0, 0, 0);
+        wv[i] = ok ? reinterpret_cast<const uint4*>(a.ln_w)[v] : make_uint4(0, 0, 0, 0);
+        bv[i] = ok ? reinterpret_cast<const uint4*>(a.ln_b)[v] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int m = 0; m < 5; ++m)
+            mv[m][i] = (ok && m < a.n_mix) ? reinterpret_cast<const uint4*>(a.mix[m] + (long long)t * a.mix_stride)[v] : make_uint4(0, 0, 0, 0);
+    }
+    // statistics of this row and, in sequence mode, of the previous one (two passes each, as layer_norm_row)
+    auto stats = [&](const uint4 (&r)[VPT], float& mean, float& rstd) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const __half2* h = reinterpret_cast<const __half2*>(&r[i]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h[e]); s += f.x; s += f.y; }
+        }
+        mean = block_sum(s, sh) / float(a.D);
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            if (threadIdx.x + i * kLnThreads < nvec) {
+                const __half2* h = reinterpret_cast<const __half2*>(&r[i]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(h[e]);
+                    q = fmaf(f.x - mean, f.x - mean, q);
+                    q = fmaf(f.y - mean, f.y - mean, q);
+                }
+            }
+        }
+        rstd = rsqrtf(block_sum(q, sh) / float(a.D) + 1e-5f);
+    };
+    float mean, rstd, pmean = 0.f, prstd = 0.f;
+    stats(xv, mean, rstd);
+    if (mixing && !own_state) stats(pv, pmean, prstd);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * kLnThreads;
+        if (v >= nvec) continue;
+        const __half* hx = reinterpret_cast<const __half*>(&xv[i]);
+        const __half* hp = reinterpret_cast<const __half*>(&pv[i]);
+        const __half* hw = reinterpret_cast<const __half*>(&wv[i]);
+        const __half* hb = reinterpret_cast<const __half*>(&bv[i]);
+        float xx[8], prev[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float w = __half2float(hw[e]), b = __half2float(hb[e]);
+            xx[e] = r16((__half2float(hx[e]) - mean) * rstd * w + b);
+            prev[e] = own_state ? __half2float(hp[e]) : r16((__half2float(hp[e]) - pmean) * prstd * w + b);
+        }
+        uint4 o;
+        __half* ho = reinterpret_cast<__half*>(&o);
+        if (a.xx_out || (t == a.T - 1 && a.new_state)) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ho[e] = __float2half_rn(xx[e]);
+            if (a.xx_out) reinterpret_cast<uint4*>(a.xx_out + (long long)t * a.xx_stride)[v] = o;
+            if (t == a.T - 1 && a.new_state) reinterpret_cast<uint4*>(a.new_state)[v] = o;
+        }
+#pragma unroll
+        for (int m = 0; m < 5; ++m) {
+            if (m < a.n_mix) {
+                const __half* hm = reinterpret_cast<const __half*>(&mv[m][i]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float mvv = __half2float(hm[e]);
+                    const float r = a.mode == 0 ? r16(r16(xx[e] * mvv) + r16(prev[e] * r16(1.0f - mvv))) : r16(xx[e] + r16(r16(prev[e] - xx[e]) * mvv));
+                    ho[e] = __float2half_rn(r);
+                }
+                reinterpret_cast<uint4*>(a.out[m] + (long long)t * a.out_stride)[v] = o;
+            }
+        }
+    }
+}
+
 // RWKV-4 one-step WKV (pkg/model.py:1041-1055): k, v are the fp16 matmul results widened to
 // fp32; r already went through sigmoid; out = r * wkv in fp16; state in place.
 __global__ void wkv4_one_kernel(int C, const float* __restrict__ t_decay, const float* __restrict__ t_first,
@@ -155,6 +250,20 @@ extern "C" int rwkv_ln_mix_rows(int64_t T, int64_t D, const void* x, int64_t x_s
     a.xx_out = (__half*)xx_out; a.xx_stride = xx_stride; a.new_state = (__half*)new_state;
     a.T = int(T); a.D = int(D); a.n_mix = n_mix; a.mode = mode;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // aligned operands: the 16-byte form
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    bool vec = D % 8 == 0 && al16(x) && x_stride % 8 == 0 && al16(ln_w) && al16(ln_b) && mix_stride % 8 == 0 && out_stride % 8 == 0 &&
+               (xx_out == nullptr || (al16(xx_out) && xx_stride % 8 == 0)) && (new_state == nullptr || al16(new_state)) &&
+               (n_mix == 0 || (al16(sx) && sx_stride % 8 == 0));
+    for (int m = 0; m < n_mix; ++m) vec = vec && al16(mix[m]) && al16(out[m]);
+    static int use_vec = -1;
+    if (use_vec < 0) { const char* e = getenv("RWKV_B200_LN_VEC"); use_vec = (e != nullptr && e[0] == '0') ? 0 : 1; }
+    if (vec && use_vec) {
+        const int vpt = int((D / 8 + kLnThreads - 1) / kLnThreads);
+        if (vpt <= 1) return rwkv_launch_pdl(ln_mix_vec_kernel<1>, dim3(int(T)), dim3(kLnThreads), 0, st, a);
+        if (vpt <= 2) return rwkv_launch_pdl(ln_mix_vec_kernel<2>, dim3(int(T)), dim3(kLnThreads), 0, st, a);
+        return rwkv_launch_pdl(ln_mix_vec_kernel<4>, dim3(int(T)), dim3(kLnThreads), 0, st, a);
+    }
     const int per = int((D + kLnThreads - 1) / kLnThreads);
     if (per <= 4) return rwkv_launch_pdl(ln_mix_kernel<4>, dim3(int(T)), dim3(kLnThreads), 0, st, a);
     if (per <= 16) return rwkv_launch_pdl(ln_mix_kernel<16>, dim3(int(T)), dim3(kLnThreads), 0, st, a);

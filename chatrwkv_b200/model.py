@@ -304,6 +304,7 @@ class RWKV:
                             os.environ.get("RWKV_B200_STREAM", "0") == "1")
         self._stream = None
         self._mm = {}
+        self._mm_pad = {}
         self._tile_cache = {}
         self._batch_graphs = {}
         # a matrix with more than 16384 in-features needs the decode kernel's second build: ask for it on every launch
@@ -759,7 +760,19 @@ class RWKV:
     def _mm_epi(self, x, name, epilogue, aux=None, aux2=None, out_scale=1.0, out=None):
         """mm8_seq with the reference's next pointwise op(s) fused into the store (single-GPU path)."""
         wq, mx, rx, my, ry = self._scales(name)
-        y = out if out is not None else torch.empty((x.shape[0], wq.shape[1]), dtype=torch.float16, device=x.device)
+        M = wq.shape[1]
+        if M % 8 != 0 and out is None and aux is None and aux2 is None and wq.stride(0) >= (M + 7) // 8 * 8:
+            # An out-feature count like 50277 would send the whole matrix to the CUDA-core kernel (the tensor-core one
+            # stores columns in groups of 8): run it on the view that includes the row padding (up to 7 more columns,
+            # whose results are dropped) with mx, rx padded alike.
+            pad = self._mm_pad.get(name)
+            if pad is None:
+                Mp = (M + 7) // 8 * 8
+                pad = self._mm_pad[name] = (torch.as_strided(wq, (wq.shape[0], Mp), (wq.stride(0), 1), wq.storage_offset()),
+                                            torch.nn.functional.pad(mx, (0, Mp - M)), torch.nn.functional.pad(rx, (0, Mp - M)))
+            y = torch.empty((x.shape[0], pad[0].shape[1]), dtype=torch.float16, device=x.device)
+            return ops.mm8_seq_epi(x, pad[0], pad[1], pad[2], my, ry, y, epilogue, None, None, out_scale)[:, :M]
+        y = out if out is not None else torch.empty((x.shape[0], M), dtype=torch.float16, device=x.device)
         return ops.mm8_seq_epi(x, wq, mx, rx, my, ry, y, epilogue, aux, aux2, out_scale)
 
     def _att_seq_v4(self, x, st, i, rows=False):
@@ -1009,7 +1022,9 @@ class RWKV:
             x = x[-1:, :]
         xln = torch.empty_like(x)
         self._ln_mix(x.shape[0], x, None, w["ln_out.weight"], w["ln_out.bias"], 0, [], [], xx_out=xln)
-        if full_output or self._world > 1:
+        if full_output and self._world == 1:
+            out = self._mm_epi(xln, "head.weight", EPI_STORE)
+        elif full_output or self._world > 1:
             out = self._mm_seq(xln, "head.weight")
             if not full_output:
                 out = out[0]
