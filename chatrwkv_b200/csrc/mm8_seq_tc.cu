@@ -255,7 +255,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Only what the preceding kernels wrote has to wait for them: the operand images and row sums of the preparation
+    // kernel, the residual inputs, and the output itself.  The producers' whole main loop reads nothing but the
+    // packed matrix, so it runs ahead of the wait (under programmatic dependent launch: while the preparation kernel
+    // and the tail of the previous matmul are still at work).
 
     if (warp < kProdWarps) {
         // ================= producers =================
@@ -320,6 +323,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
             }
         }
         // ================= epilogue =================
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         if (ok) ok = mbar_wait(accum_bar, 0);
         if (!ok) atomicExch(failed, 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -399,6 +403,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
     } else if (warp == kProdWarps + 1) {
         // ================= A tiles: one bulk copy each (hi, lo) of the 16 KB image the preparation kernel laid out
         if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             for (int kb = 0; kb < nkb; ++kb) {
                 const int s = kb % STAGES;
