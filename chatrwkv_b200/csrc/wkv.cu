@@ -157,6 +157,7 @@ enum { PASS_WHOLE = 0, PASS_SUM = 1, PASS_OUT = 2 };
 
 struct Wkv56Args {
     int T, C, H, Lc, NC, model_layout;
+    int vec;                // r, k, v, w allow 16-byte copies
     const float* state;     // the caller's state
     float* state_out;       // where the new state goes (PASS_WHOLE, last chunk of PASS_OUT); may be `state`
     float* sums;            // [NC][H][N][N]: PASS_SUM writes chunk sums; the scan leaves the state after chunk c in [c]
@@ -176,6 +177,31 @@ __device__ __forceinline__ long long wkv56_state_index(int model_layout, int h, 
     return model_layout ? ((long long)h * N + j) * N + i : ((long long)h * N + i) * N + j;
 }
 
+__device__ __forceinline__ void cp16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+template <typename F> __device__ __forceinline__ float2 load_pair(const F* p);
+template <> __device__ __forceinline__ float2 load_pair<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <> __device__ __forceinline__ float2 load_pair<__half>(const __half* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }
+template <> __device__ __forceinline__ float2 load_pair<__nv_bfloat16>(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+// Two fp32 multiply-adds / multiplies per instruction (sm_100); each lane rounds as fmaf / a product does.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<const unsigned long long&>(a)), "l"(reinterpret_cast<const unsigned long long&>(b)),
+          "l"(reinterpret_cast<const unsigned long long&>(c)));
+    return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<const unsigned long long&>(a)), "l"(reinterpret_cast<const unsigned long long&>(b)));
+    return d;
+}
+
 template <typename FI, typename FO, int N, bool PER_TOKEN_W, int PASS>
 __global__ void __launch_bounds__(Wkv56Tile<N>::NT * Wkv56Tile<N>::NT)
 wkv56_seq_kernel(const Wkv56Args a, const FI* __restrict__ r_, const FI* __restrict__ k_, const FI* __restrict__ v_,
@@ -186,105 +212,182 @@ wkv56_seq_kernel(const Wkv56Args a, const FI* __restrict__ r_, const FI* __restr
     const int t_begin = PASS == PASS_WHOLE ? 0 : chunk * a.Lc;
     const int t_end = PASS == PASS_WHOLE ? a.T : min(a.T, t_begin + a.Lc);
 
-    __shared__ __align__(16) float sr[TC][N], sk[TC][N], sv[TC][N], sw[PER_TOKEN_W ? TC : 1][N];
+    // r, k, v (and the per-token decay) of TCN steps at a time, in the caller's dtype, double-buffered: the next
+    // block's 16-byte cp.async copies are in flight while this block's steps run
+    constexpr int TCN = N >= 128 ? TC / 2 : TC;
+    __shared__ __align__(16) FI sr[2][TCN][N], sk[2][TCN][N], sv[2][TCN][N];
+    __shared__ __align__(16) float sw[2][PER_TOKEN_W ? TCN : 1][N];
 
-    float S[TL][TL], P[TL], u[TL];
+    float2 S2[TL][TL / 2], P2[TL / 2], u2[TL / 2];       // the state tile, the decay product and u as pairs along j
     const float* src = PASS == PASS_OUT ? (chunk == 0 ? a.start : a.sums + (long long)(chunk - 1) * a.H * N * N) : a.state;
     const int src_layout = PASS == PASS_OUT ? 0 : a.model_layout;
+    auto stage = [&](int t0, int buf) {
+        const int nt = min(TCN, t_end - t0);
+        if (a.vec) {
+            constexpr int CI = N * int(sizeof(FI)) / 16, CW = N * 4 / 16;         // 16-byte pieces per row
+            for (int e = tid; e < nt * CI; e += THREADS) {
+                const int tt = e / CI, c = e - tt * CI;
+                const long long g = ((long long)(t0 + tt) * C + h * N) * (long long)sizeof(FI) + c * 16;
+                cp16(reinterpret_cast<uint8_t*>(&sr[buf][tt][0]) + c * 16, reinterpret_cast<const uint8_t*>(r_) + g);
+                cp16(reinterpret_cast<uint8_t*>(&sk[buf][tt][0]) + c * 16, reinterpret_cast<const uint8_t*>(k_) + g);
+                cp16(reinterpret_cast<uint8_t*>(&sv[buf][tt][0]) + c * 16, reinterpret_cast<const uint8_t*>(v_) + g);
+            }
+            if (PER_TOKEN_W)
+                for (int e = tid; e < nt * CW; e += THREADS) {
+                    const int tt = e / CW, c = e - tt * CW;
+                    cp16(reinterpret_cast<uint8_t*>(&sw[buf][tt][0]) + c * 16,
+                         reinterpret_cast<const uint8_t*>(w_) + ((long long)(t0 + tt) * C + h * N) * 4 + c * 16);
+                }
+        } else {
+            for (int e = tid; e < nt * N; e += THREADS) {
+                const int tt = e / N, j = e % N;
+                const long long g = (long long)(t0 + tt) * C + h * N + j;
+                sr[buf][tt][j] = r_[g];
+                sk[buf][tt][j] = k_[g];
+                sv[buf][tt][j] = v_[g];
+                if (PER_TOKEN_W) sw[buf][tt][j] = w_[g];
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (t_begin < t_end) stage(t_begin, 0);
 #pragma unroll
-    for (int jj = 0; jj < TL; ++jj) {
-        P[jj] = 1.f;
-        u[jj] = to_f32<FO>(u_[h * N + j0 + jj]);
+    for (int q = 0; q < TL / 2; ++q) {
+        P2[q] = make_float2(1.f, 1.f);
+        u2[q] = make_float2(to_f32<FO>(u_[h * N + j0 + 2 * q]), to_f32<FO>(u_[h * N + j0 + 2 * q + 1]));
     }
 #pragma unroll
     for (int ii = 0; ii < TL; ++ii)
 #pragma unroll
-        for (int jj = 0; jj < TL; ++jj)
-            S[ii][jj] = PASS == PASS_SUM ? 0.f : src[wkv56_state_index<N, TL>(src_layout, h, i0 + ii, j0 + jj)];
+        for (int q = 0; q < TL / 2; ++q) {
+            S2[ii][q].x = PASS == PASS_SUM ? 0.f : src[wkv56_state_index<N, TL>(src_layout, h, i0 + ii, j0 + 2 * q)];
+            S2[ii][q].y = PASS == PASS_SUM ? 0.f : src[wkv56_state_index<N, TL>(src_layout, h, i0 + ii, j0 + 2 * q + 1)];
+        }
     if (!PER_TOKEN_W)
-        for (int j = tid; j < N; j += THREADS) sw[0][j] = w_[h * N + j];
+        for (int j = tid; j < N; j += THREADS) sw[0][0][j] = sw[1][0][j] = w_[h * N + j];
 
-    for (int t0 = t_begin; t0 < t_end; t0 += TC) {
-        const int nt = min(TC, t_end - t0);
-        __syncthreads();
-        for (int e = tid; e < nt * N; e += THREADS) {
-            const int tt = e / N, j = e % N;
-            const long long g = (long long)(t0 + tt) * C + h * N + j;
-            sr[tt][j] = to_f32<FI>(r_[g]);
-            sk[tt][j] = to_f32<FI>(k_[g]);
-            sv[tt][j] = to_f32<FI>(v_[g]);
-            if (PER_TOKEN_W) sw[tt][j] = w_[g];
+    int buf = 0;
+    for (int t0 = t_begin; t0 < t_end; t0 += TCN, buf ^= 1) {
+        const int nt = min(TCN, t_end - t0);
+        if (t0 + TCN < t_end) {
+            stage(t0 + TCN, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            float r[TL], k[TL], w[TL], v[TL];
-            const float* wrow = PER_TOKEN_W ? sw[tt] : sw[0];
+            // operands as pairs: the multiply-adds below are two-wide fp32 instructions (same roundings as fmaf)
+            float2 r2[TL / 2], k2[TL / 2], w2[TL / 2];
+            float v[TL];
+            const float* wrow = PER_TOKEN_W ? sw[buf][tt] : sw[0][0];
 #pragma unroll
-            for (int q = 0; q < TL; ++q) { r[q] = sr[tt][j0 + q]; k[q] = sk[tt][j0 + q]; w[q] = wrow[j0 + q]; v[q] = sv[tt][i0 + q]; }
+            for (int q = 0; q < TL / 2; ++q) {
+                r2[q] = load_pair<FI>(&sr[buf][tt][j0 + 2 * q]);
+                k2[q] = load_pair<FI>(&sk[buf][tt][j0 + 2 * q]);
+                w2[q] = *reinterpret_cast<const float2*>(&wrow[j0 + 2 * q]);
+            }
+#pragma unroll
+            for (int q = 0; q < TL / 2; ++q) {
+                const float2 vp = load_pair<FI>(&sv[buf][tt][i0 + 2 * q]);
+                v[2 * q] = vp.x;
+                v[2 * q + 1] = vp.y;
+            }
             if (PASS != PASS_SUM) {
-                float ruk = 0.f;
+                float2 ruk2 = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int jj = 0; jj < TL; ++jj) ruk = fmaf(r[jj] * u[jj], k[jj], ruk);
+                for (int q = 0; q < TL / 2; ++q) ruk2 = ffma2(fmul2(r2[q], u2[q]), k2[q], ruk2);
+                const float ruk = ruk2.x + ruk2.y;
                 float y[TL];
 #pragma unroll
                 for (int ii = 0; ii < TL; ++ii) {
-                    float acc = v[ii] * ruk;
+                    float2 acc = make_float2(v[ii] * ruk, 0.f);
 #pragma unroll
-                    for (int jj = 0; jj < TL; ++jj) acc = fmaf(r[jj], S[ii][jj], acc);
-                    y[ii] = acc;
+                    for (int q = 0; q < TL / 2; ++q) acc = ffma2(r2[q], S2[ii][q], acc);
+                    y[ii] = acc.x + acc.y;
                 }
+                // sum over the NT threads of a row of tiles: whole exchanges while there are more lanes than values,
+                // then halving exchanges (each lane keeps half of what it holds), so that lane tj ends with y[tj]
 #pragma unroll
-                for (int o = NT >> 1; o > 0; o >>= 1) {
+                for (int o = NT >> 1; o >= TL; o >>= 1) {
 #pragma unroll
                     for (int ii = 0; ii < TL; ++ii) y[ii] += __shfl_xor_sync(0xffffffffu, y[ii], o);
                 }
-                if (tj == 0) {
-                    FO* yo = y_ + (long long)(t0 + tt) * C + h * N + i0;
 #pragma unroll
-                    for (int ii = 0; ii < TL; ++ii) yo[ii] = from_f32<FO>(y[ii]);
+                for (int o = (TL < NT ? TL : NT) >> 1; o > 0; o >>= 1) {
+                    const bool upper = (tj & o) != 0;
+#pragma unroll
+                    for (int q = 0; q < o; ++q) {
+                        const float send = upper ? y[q] : y[q + o];
+                        const float keep = upper ? y[q + o] : y[q];
+                        y[q] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                    }
                 }
+                if (tj < TL) y_[(long long)(t0 + tt) * C + h * N + i0 + tj] = from_f32<FO>(y[0]);
             }
 #pragma unroll
-            for (int ii = 0; ii < TL; ++ii)
+            for (int ii = 0; ii < TL; ++ii) {
+                const float2 vv = make_float2(v[ii], v[ii]);
 #pragma unroll
-                for (int jj = 0; jj < TL; ++jj) S[ii][jj] = fmaf(S[ii][jj], w[jj], k[jj] * v[ii]);
+                for (int q = 0; q < TL / 2; ++q) S2[ii][q] = ffma2(S2[ii][q], w2[q], fmul2(k2[q], vv));
+            }
             if (PASS == PASS_SUM) {
 #pragma unroll
-                for (int jj = 0; jj < TL; ++jj) P[jj] *= w[jj];
+                for (int q = 0; q < TL / 2; ++q) P2[q] = fmul2(P2[q], w2[q]);
             }
         }
+        __syncthreads();                                 // this block's buffer is refilled two rounds on
     }
     if (PASS == PASS_SUM) {
         float* out = a.sums + (long long)chunk * a.H * N * N;
 #pragma unroll
         for (int ii = 0; ii < TL; ++ii)
 #pragma unroll
-            for (int jj = 0; jj < TL; ++jj) out[wkv56_state_index<N, TL>(0, h, i0 + ii, j0 + jj)] = S[ii][jj];
+            for (int q = 0; q < TL / 2; ++q) {
+                out[wkv56_state_index<N, TL>(0, h, i0 + ii, j0 + 2 * q)] = S2[ii][q].x;
+                out[wkv56_state_index<N, TL>(0, h, i0 + ii, j0 + 2 * q + 1)] = S2[ii][q].y;
+            }
         if (ti == 0) {
 #pragma unroll
-            for (int jj = 0; jj < TL; ++jj) a.prods[((long long)chunk * a.H + h) * N + j0 + jj] = P[jj];
+            for (int q = 0; q < TL / 2; ++q) {
+                a.prods[((long long)chunk * a.H + h) * N + j0 + 2 * q] = P2[q].x;
+                a.prods[((long long)chunk * a.H + h) * N + j0 + 2 * q + 1] = P2[q].y;
+            }
         }
     } else if (PASS == PASS_WHOLE || chunk == a.NC - 1) {
 #pragma unroll
         for (int ii = 0; ii < TL; ++ii)
 #pragma unroll
-            for (int jj = 0; jj < TL; ++jj) a.state_out[wkv56_state_index<N, TL>(a.model_layout, h, i0 + ii, j0 + jj)] = S[ii][jj];
+            for (int q = 0; q < TL / 2; ++q) {
+                a.state_out[wkv56_state_index<N, TL>(a.model_layout, h, i0 + ii, j0 + 2 * q)] = S2[ii][q].x;
+                a.state_out[wkv56_state_index<N, TL>(a.model_layout, h, i0 + ii, j0 + 2 * q + 1)] = S2[ii][q].y;
+            }
     }
 }
 
-// start <- the caller's state (operator layout); sums[c] <- state after chunk c, for c = 0 .. NC - 2
+// start <- the caller's state (operator layout); sums[c] <- state after chunk c, for c = 0 .. NC - 2.
+// One thread per state element; every load of the chain is issued before the first multiply-add.
 template <int N>
 __global__ void __launch_bounds__(256) wkv56_scan_kernel(const Wkv56Args a) {
     const int h = blockIdx.x;
-    for (int e = threadIdx.x; e < N * N; e += 256) {
-        const int i = e / N, j = e % N;
-        const long long at = ((long long)h * N + i) * N + j;
-        float S = a.state[wkv56_state_index<N, 1>(a.model_layout, h, i, j)];
-        a.start[at] = S;
-        for (int c = 0; c + 1 < a.NC; ++c) {
-            float* sm = a.sums + (long long)c * a.H * N * N + at;
-            S = fmaf(S, a.prods[((long long)c * a.H + h) * N + j], *sm);
-            *sm = S;
+    const int e = blockIdx.y * 256 + threadIdx.x;
+    if (e >= N * N) return;
+    const int i = e / N, j = e % N;
+    const long long at = ((long long)h * N + i) * N + j;
+    float add[kWkv56MaxChunks], mul[kWkv56MaxChunks];
+#pragma unroll
+    for (int c = 0; c < kWkv56MaxChunks - 1; ++c) {
+        const bool on = c + 1 < a.NC;
+        add[c] = on ? a.sums[(long long)c * a.H * N * N + at] : 0.f;
+        mul[c] = on ? a.prods[((long long)c * a.H + h) * N + j] : 1.f;
+    }
+    float S = a.state[wkv56_state_index<N, 1>(a.model_layout, h, i, j)];
+    a.start[at] = S;
+#pragma unroll
+    for (int c = 0; c < kWkv56MaxChunks - 1; ++c) {
+        if (c + 1 < a.NC) {
+            S = fmaf(S, mul[c], add[c]);
+            a.sums[(long long)c * a.H * N * N + at] = S;
         }
     }
 }
@@ -311,6 +414,8 @@ int launch56(int T, int C, int H, const float* state, float* state_out, const vo
     const int N = C / H;
     Wkv56Args a;
     a.T = T; a.C = C; a.H = H; a.model_layout = model_layout; a.state = state; a.state_out = state_out;
+    a.vec = ((reinterpret_cast<uintptr_t>(r) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+              reinterpret_cast<uintptr_t>(w)) % 16 == 0 && (size_t(C) * sizeof(FI)) % 16 == 0 && (size_t(N) * sizeof(FI)) % 16 == 0) ? 1 : 0;
     wkv56_chunks(T, a.Lc, a.NC);
     if (a.NC > 1 && (workspace == nullptr || workspace_bytes < wkv56_ws_bytes(T, C, H))) { a.NC = 1; a.Lc = T; }
     a.sums = static_cast<float*>(workspace);
@@ -326,7 +431,7 @@ int launch56(int T, int C, int H, const float* state, float* state_out, const vo
         } else {                                                                                              \
             wkv56_seq_kernel<FI, FO, NN, PER_TOKEN_W, PASS_SUM><<<dim3(gx, unsigned(a.NC - 1)), THR, 0, st>>>( \
                 a, (const FI*)r, (const FI*)k, (const FI*)v, w, (const FO*)u, (FO*)y);                        \
-            wkv56_scan_kernel<NN><<<gx, 256, 0, st>>>(a);                                                     \
+            wkv56_scan_kernel<NN><<<dim3(gx, unsigned((NN * NN + 255) / 256)), 256, 0, st>>>(a);                                                     \
             wkv56_seq_kernel<FI, FO, NN, PER_TOKEN_W, PASS_OUT><<<dim3(gx, unsigned(a.NC)), THR, 0, st>>>(    \
                 a, (const FI*)r, (const FI*)k, (const FI*)v, w, (const FO*)u, (FO*)y);                        \
         }                                                                                                     \
