@@ -1,13 +1,15 @@
-"""`RWKV(model, strategy).forward(tokens, state)` for the 'cuda fp16i8' strategy, on sm_100a
-kernels.
+"""`RWKV(model, strategy).forward(tokens, state)` for the 'cuda fp16i8' strategy (and its mixes with 'cuda fp16'),
+on sm_100a kernels.
 
 Mirrors the public surface of the reference runtime class (rwkv_pip_package/src/rwkv/
 model.py:612-1677): constructor arguments, `forward(tokens, state, full_output)`, the state
 list layout (model.py:1448-1471), `.args`, `.version`, `.strategy[i].{device,atype,wtype}`
 and the tensor names in `.w`.  What differs, by design:
 
-  * only single-device `cuda[:N] fp16i8` strategies are implemented (anything else the
-    reference's strategy grammar accepts raises NotImplementedError);
+  * single-device strategies with fp16 activations are implemented: `cuda[:N] fp16i8`, `cuda[:N] fp16` and splits
+    by layer count such as `cuda fp16i8 *20 -> cuda fp16` (anything else the reference's strategy grammar accepts
+    raises NotImplementedError).  int8 layers run on this library's kernels; plain fp16 layers are library GEMMs plus
+    the reference's pointwise ops, and a model that has any takes the sequence path for one-token calls too;
   * the loader packs on the GPU (ops.quantize_weight) and keeps `emb.weight` on the GPU;
   * packed matrices have a row stride padded to 16 bytes (their shape is unchanged);
   * a one-token `forward` is a single CUDA-graph replay of fused kernels; the state tensors
@@ -65,10 +67,16 @@ class RWKV:
         if not re.match(STRATEGY_REGEX, strategy):
             raise ValueError("Invalid strategy. Please read https://pypi.org/project/rwkv/")
         strategy = ("->".join([x.strip() for x in strategy.split("->")])).replace("->", " -> ")
-        m = re.fullmatch(r"(cuda(?::\d+)?) fp16i8", strategy)
-        if m is None:
+        # one device, fp16 activations, int8 or fp16 weights per group of layers: 'cuda fp16i8', 'cuda fp16',
+        # 'cuda fp16i8 *20 -> cuda fp16', ... (model.py:684-749 without streaming, other devices or dtypes)
+        segments = [re.fullmatch(r"(cuda(?::\d+)?) (fp16i8|fp16)(?: \*(\d+))?", x) for x in strategy.split(" -> ")]
+        if any(g is None for g in segments) or len({g.group(1) for g in segments}) != 1:
             raise NotImplementedError(
-                f"strategy '{strategy}': this runtime implements single-device 'cuda[:N] fp16i8' only")
+                f"strategy '{strategy}': this runtime implements single-device 'cuda[:N] fp16i8' / 'cuda[:N] fp16' and "
+                "splits between the two by layer count ('cuda fp16i8 *K -> cuda fp16')")
+        m = segments[0]
+        if shard_world > 1 and not (len(segments) == 1 and m.group(2) == "fp16i8"):
+            raise NotImplementedError("column sharding is implemented for 'cuda fp16i8'")
         lib()  # fail loudly now if the CUDA library is not built
         self.device = torch.device(m.group(1) if ":" in m.group(1) else "cuda:%d" % torch.cuda.current_device())
         dev = self.device
@@ -134,9 +142,35 @@ class RWKV:
             if self.version not in (4, 5.2, 6):
                 raise NotImplementedError(f"RWKV v{self.version}: this runtime implements v4, v5.2 and v6")
 
-            self.strategy = [types.SimpleNamespace(device=str(dev) if ":" in m.group(1) else "cuda",
-                                                   atype=torch.float16, wtype=torch.uint8, stream=False)
-                             for _ in range(args.n_layer + 1)]
+            # layers per strategy segment, as the reference deals them (model.py:684-737; n_layer + 1 "layers": the
+            # last one holds ln_out and the head)
+            plan = [0] * len(segments)
+            to_allocate, allocated, free_slots = args.n_layer + 1, 0, 0
+            for i, g in enumerate(segments):
+                if g.group(3) is not None:
+                    plan[i] = int(g.group(3))
+                    allocated += plan[i]
+                    if allocated >= to_allocate:
+                        plan[i] += to_allocate - allocated
+                        break
+                else:
+                    free_slots += 1
+            if free_slots > 0 and to_allocate > allocated:
+                for i in range(len(segments)):
+                    if plan[i] == 0:
+                        plan[i] = (to_allocate - allocated) // free_slots
+                        allocated += plan[i]
+                        free_slots -= 1
+            if to_allocate > allocated:
+                plan[-1] += to_allocate - allocated
+            for i in range(1, len(plan)):
+                plan[i] += plan[i - 1]
+            self.strategy = []
+            for n in range(args.n_layer + 1):
+                g = segments[next(i for i in range(len(segments)) if n < plan[i])]
+                self.strategy.append(types.SimpleNamespace(
+                    device=str(dev) if ":" in m.group(1) else "cuda", atype=torch.float16,
+                    wtype=torch.uint8 if g.group(2) == "fp16i8" else torch.float16, stream=False))
 
             if not already:                                          # model.py:754-760
                 emb = w["emb.weight"].to(dev)
@@ -188,7 +222,8 @@ class RWKV:
                         t = t.reshape(args.n_head, -1, 1)
                 elif ".ln_x" in x:
                     t = t.float()
-                elif len(t.shape) == 2 and "emb" not in x and "_w1" not in x and "_w2" not in x:
+                elif len(t.shape) == 2 and "emb" not in x and "_w1" not in x and "_w2" not in x and \
+                        self.strategy[layer_id].wtype == torch.uint8:
                     q, mx, rx, my, ry = ops.quantize_weight(t, torch.float16, scale)
                     t = q
                     w[x + "_mx"], w[x + "_rx"], w[x + "_my"], w[x + "_ry"] = mx, rx, my, ry
@@ -211,6 +246,10 @@ class RWKV:
 
             if self.version != 4:
                 args.n_head = w["blocks.0.att.time_first"].shape[0]
+            # the fused one-token path and the batched path are built for int8 matrices throughout; a model with plain
+            # fp16 layers runs every call through the sequence path (library GEMMs for those layers)
+            self._all_i8 = all(w[k].dtype == torch.uint8 for k in w
+                               if torch.is_tensor(w[k]) and any(sk in k for sk in _MATRIX_KEYS) and k.endswith(".weight"))
             self._full_m = {}
             if self._world > 1:
                 if self.version != 4:
@@ -365,10 +404,10 @@ class RWKV:
             if state is None:
                 state = self._zero_state()
             if torch.is_tensor(tokens):
-                if tokens.is_cuda and tokens.numel() == 1:
+                if tokens.is_cuda and tokens.numel() == 1 and self._all_i8:
                     return self._forward_one(tokens, state)      # token id stays on the device
                 tokens = tokens.tolist()
-            if len(tokens) == 1:
+            if len(tokens) == 1 and self._all_i8:
                 return self._forward_one(int(tokens[0]), state)
             return self._forward_seq([int(t) for t in tokens], state, full_output)
 
@@ -742,7 +781,31 @@ class RWKV:
             op()
 
     # ----- sequence ------------------------------------------------------------------------
+    def _plain(self, x, name, epilogue=EPI_STORE, aux=None, aux2=None, out_scale=1.0, out=None):
+        """A layer kept in fp16 ('cuda fp16', model.py:143-167): a library GEMM with fp32 accumulation, then the
+        reference's own pointwise ops on fp16 tensors (one rounding each)."""
+        y = x @ self.w[name]
+        if epilogue == EPI_SIGMOID:
+            y = torch.sigmoid(y)
+        elif epilogue == EPI_RELU_SQ:
+            y = torch.relu(y) ** 2
+        elif epilogue == EPI_RESIDUAL:
+            y = aux + y
+        elif epilogue == EPI_MUL_RESIDUAL:
+            y = aux + aux2 * y
+        elif epilogue == EPI_SILU:
+            y = F.silu(y)
+        if out_scale != 1.0:
+            y = y * out_scale
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
     def _mm_seq(self, x, name, out_dtype=None):
+        if self.w[name].dtype != torch.uint8:
+            y = self._plain(x, name)
+            return y if out_dtype is None else y.to(out_dtype)
         wq, mx, rx, my, ry = self._scales(name)
         T = x.shape[0]
         N, M = wq.shape
@@ -759,6 +822,8 @@ class RWKV:
 
     def _mm_epi(self, x, name, epilogue, aux=None, aux2=None, out_scale=1.0, out=None):
         """mm8_seq with the reference's next pointwise op(s) fused into the store (single-GPU path)."""
+        if self.w[name].dtype != torch.uint8:
+            return self._plain(x, name, epilogue, aux, aux2, out_scale, out)
         wq, mx, rx, my, ry = self._scales(name)
         M = wq.shape[1]
         if M % 8 != 0 and out is None and aux is None and aux2 is None and wq.stride(0) >= (M + 7) // 8 * 8:
@@ -1028,6 +1093,8 @@ class RWKV:
             out = self._mm_seq(xln, "head.weight")
             if not full_output:
                 out = out[0]
+        elif w["head.weight"].dtype != torch.uint8:
+            out = self._plain(xln, "head.weight")[0]
         else:
             wq, mx, rx, my, ry = self._scales("head.weight")
             y = torch.zeros(wq.shape[1], dtype=torch.float32, device=self.device)

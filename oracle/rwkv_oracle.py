@@ -186,8 +186,12 @@ class OracleRWKV:
     state, RESCALE_LAYER 6 (pkg/model.py:634).
     """
 
-    def __init__(self, ckpt: dict, atype=torch.float16, rescale_layer=None):
+    def __init__(self, ckpt: dict, atype=torch.float16, rescale_layer=None, i8_layers=None):
+        """`i8_layers`: how many layers, from the first, hold int8 matrices (the reference's 'xxx fp16i8 *K -> xxx
+        fp16', pkg/model.py:684-749: the rest and the head keep plain weights of the activation dtype); None = all
+        layers and the head ('xxx fp16i8'), 0 = none ('xxx fp16')."""
         self.atype = atype
+        self.i8_layers = i8_layers
         self.RESCALE_LAYER = (6 if atype == torch.float16 else 0) if rescale_layer is None else rescale_layer
         w = {k: v.clone() for k, v in ckpt.items()}
         args = types.SimpleNamespace()
@@ -254,7 +258,8 @@ class OracleRWKV:
             elif ".ln_x" in x:
                 w[x] = w[x].float()
             else:
-                if len(w[x].shape) == 2 and "emb" not in x and "_w1" not in x and "_w2" not in x:
+                packed = i8_layers is None or layer_id < i8_layers
+                if len(w[x].shape) == 2 and "emb" not in x and "_w1" not in x and "_w2" not in x and packed:
                     q, mx, rx, my, ry = quantize_weight(w[x], atype)
                     w[x] = q
                     w[x + "_mx"], w[x + "_rx"], w[x + "_my"], w[x + "_ry"] = mx, rx, my, ry
@@ -267,6 +272,9 @@ class OracleRWKV:
     def _mm(self, x, name, out_dtype=None):
         """pkg/model.py:127-138: mm8 in the activation dtype, then `.to(output_dtype)`."""
         w = self.w
+        if w[name].dtype != torch.uint8:                 # pkg/model.py:143-167: a plain matmul in the activation dtype
+            y = (x.float() @ w[name].float()).to(self.atype)
+            return y if out_dtype is None else y.to(out_dtype)
         if name not in self._deq:
             self._deq[name] = dequant(w[name], w[name + "_mx"].float(), w[name + "_rx"].float(),
                                       w[name + "_my"].float(), w[name + "_ry"].float())

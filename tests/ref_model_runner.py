@@ -58,7 +58,7 @@ def main(ckpt, job_path, outp):
         job = json.load(f)
     prompt, n = job["prompt"], int(job["decode"])
     t0 = time.perf_counter()
-    model = RWKV(ckpt, "cuda fp16i8", verbose=False)
+    model = RWKV(ckpt, job.get("strategy", "cuda fp16i8"), verbose=False)
     load_s = time.perf_counter() - t0
     out = {"load_s": np.float64(load_s)}
 

@@ -54,11 +54,11 @@ def _reference_ready():
                ("wkv_cuda_ref.so", "rwkv5_ref.so", "rwkv6_ref.so", os.path.join("pkg", "rwkv", "model.py")))
 
 
-def _run_reference(tmp, converted, prompt, n, repeat):
+def _run_reference(tmp, converted, prompt, n, repeat, strategy="cuda fp16i8"):
     ck, job, out = str(tmp / "converted.pth"), str(tmp / "job.json"), str(tmp / "ref.npz")
     torch.save(converted, ck)
     with open(job, "w") as f:
-        json.dump({"prompt": prompt, "decode": n, "repeat": int(repeat)}, f)
+        json.dump({"prompt": prompt, "decode": n, "repeat": int(repeat), "strategy": strategy}, f)
     r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "ref_model_runner.py"), ck, job, out],
                        capture_output=True, text=True, timeout=1500)
     os.remove(ck)
@@ -163,3 +163,25 @@ def test_logits_and_greedy_tokens_match_reference_cuda_path(name, tmp_path):
         r = report["product"][label]
         assert r["max_abs"] <= tol, report
         assert r["argmax_mismatch_steps"] == r["forgiven_steps"], report
+
+
+@pytest.mark.parametrize("strategy", ["cuda fp16", "cuda fp16i8 *6 -> cuda fp16"])
+def test_plain_and_mixed_strategies_match_reference_cuda_path(strategy, tmp_path):
+    """The 169M shape under the strategies with plain fp16 layers: the reference runs its cuBLAS GEMM operator for
+    them (model.py:143-167), this runtime a library GEMM too; logits after the prompt and at every teacher-forced step."""
+    if not _reference_ready():
+        pytest.skip("oracle/_ref (reference operators + staged runtime) not built")
+    from chatrwkv_b200.model import RWKV
+    L, D, Fn, V = synth.SHAPES["v4-169m"]
+    ck = synth.make_checkpoint(4, L, D, Fn, V, seed=1000, device=torch.device("cuda", 0))
+    model = RWKV(ck, strategy, verbose=False)
+    del ck
+    prompt = synth.make_tokens(64, V, 2000)
+    ref = _run_reference(tmp_path, model.export_converted(), prompt, 64, True, strategy)
+    logits, state = model.forward(prompt, None)
+    err_p = (logits - torch.from_numpy(ref["logits_prefill"]).cuda()).abs().max().item()
+    worst, mismatch, forgiven, _, _ = _decode(model, state, ref["tokens"], ref["logits_steps"])
+    tol = max(TOL, 1.5 * float(ref["noise_max"]))
+    print(json.dumps({"strategy": strategy, "prefill_max_abs": err_p, "decode_max_abs": worst, "mismatch": mismatch,
+                      "forgiven": forgiven, "reference_noise": float(ref["noise_max"])}))
+    assert err_p <= tol and worst <= tol and mismatch == forgiven

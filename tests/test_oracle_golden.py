@@ -104,3 +104,22 @@ def test_reference_converted_checkpoint_matches_oracle_packing():
             assert v.shape == ref.shape and torch.equal(v.view(torch.int16), ref.view(torch.int16)), (key, name)
         n += 1
     assert n == 8 * 7 + 1
+
+
+def test_plain_and_mixed_strategies_match_the_reference():
+    """Unquantised layers ('cpu fp32') and the per-layer split of 'cpu fp32i8 *2 -> cpu fp32', against logits the
+    reference produced (tests/golden/reference_cpu_plain.npz, made by tests/golden/make_plain_golden.py)."""
+    import os
+    import numpy as np
+    from chatrwkv_b200 import synth
+    from tests.golden.make_golden import TOKENS, TOY
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_cpu_plain.npz"))
+    for name in ("v4", "v6"):
+        for tag, k in (("plain", 0), ("mixed", 2)):
+            m = orc.OracleRWKV(synth.make_checkpoint(**TOY[name]), atype=torch.float32, i8_layers=k)
+            full, _ = m.forward(TOKENS, None, full_output=True)
+            assert torch.allclose(full, torch.from_numpy(g[f"{name}/{tag}/full"]), rtol=2e-4, atol=2e-5), (name, tag)
+            st = None
+            for i, t in enumerate(TOKENS):
+                o, st = m.forward([t], st)
+                assert torch.allclose(o, torch.from_numpy(g[f"{name}/{tag}/one"][i]), rtol=2e-4, atol=2e-5), (name, tag, i)
