@@ -61,7 +61,8 @@ def test_strategy_validation():
     from chatrwkv_b200.model import RWKV
     with pytest.raises(ValueError):
         RWKV({}, "gpu fp16", verbose=False)
-    for s in ("cpu fp32i8", "cuda fp16", "cuda fp16i8 *10 -> cpu fp32", "cuda:0 fp16i8 *4+"):
+    for s in ("cpu fp32i8", "cuda fp32", "cuda bf16", "cuda fp16i8 *10 -> cpu fp32", "cuda:0 fp16i8 *4+",
+              "cuda:0 fp16i8 *4 -> cuda:1 fp16"):
         with pytest.raises(NotImplementedError):
             RWKV({}, s, verbose=False)
 
