@@ -92,6 +92,11 @@ class RWKV:
         # (process-wide; about 20 % slower; see rwkv_mm8_one_set_variant in include/rwkv_b200.h)
         if os.environ.get("RWKV_B200_EXACT", "0") == "1":
             lib().rwkv_mm8_one_set_variant(8)
+        # RWKV_B200_SEQ_SINGLE=1: the sequence matmuls multiply fp16(x*ry) in one tensor-core pass instead of the exact
+        # hi + lo pair (process-wide; about 1e-4 of the output RMS less accurate, below the fp16 rounding of the result;
+        # half the tensor work; see rwkv_mm8_seq_set_path in include/rwkv_b200.h)
+        if os.environ.get("RWKV_B200_SEQ_SINGLE", "0") == "1":
+            lib().rwkv_mm8_seq_set_path(4)
 
         if isinstance(model, dict):
             args.MODEL_NAME = "<dict>"
