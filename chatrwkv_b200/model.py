@@ -425,10 +425,11 @@ class RWKV:
         """Make `state` the tensors the next decode step reads."""
         if self._st is None:
             self._st = [[s.contiguous().clone() for s in state], [s.contiguous().clone() for s in state]]
+            self._st_ids = [tuple(map(id, lst)) for lst in self._st]      # identity check of a whole list at C speed
             self._cur = 0
             return
         g = self._st[self._cur]
-        if len(g) == len(state) and all(a is b for a, b in zip(g, state)):
+        if tuple(map(id, state)) == self._st_ids[self._cur]:
             if isinstance(state, _StateList) and state.owner is self and state.step != self._steps:
                 self._stale(state)
             return
