@@ -240,7 +240,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full0 + s * 8, kProducers + 1);    // every producer's B part + the thread that starts the A copies
+            mbar_init(full0 + s * 8, kProdWarps + 1);    // one arrival per producer warp (its B part is stored and fenced)
+                                                         // + the thread that starts the A copies
             mbar_init(empty0 + s * 8, 1);                // tcgen05.commit
         }
         mbar_init(accum_bar, 1);
@@ -317,7 +318,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) mm8_seq_tc_kernel(const TcArgs 
 #pragma unroll
                 for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(bt + j * 16) = bytes_to_half8(lo4[j], hi4[j]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(full0 + s * 8);
+                __syncwarp();                                // 512 arrivals per stage on one barrier word were the
+                if (lane == 0) mbar_arrive(full0 + s * 8);   // kernel's limit (~1 us per K block): one per warp instead
                 SEQ_STAMP(kb, 2);
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
