@@ -11,6 +11,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include <algorithm>
 
 namespace cg = cooperative_groups;
 
@@ -321,6 +322,7 @@ constexpr int kPT = 512;
 
 struct AttPre {
     int D, Lm, Ld, rows, ncta;   // ncta: CTAs of the one cluster (8, or 16 where the device allows it)
+    int wsm;                     // 1: this CTA's slices of the four weight matrices are staged in shared memory
     const __half *x, *ln_w, *ln_b, *state, *maa_x, *w1, *w2, *dw1, *dw2;
     const __half* maa[5];
     const float* decay;
@@ -341,6 +343,7 @@ __device__ __forceinline__ float block_sum512(float v, float* sh16) {
 }
 
 // part[c] = sum over this CTA's rows l of vin[l] * W[l][c]   (W row-major [nrows][R], R % 8 == 0)
+template <bool SM>      // SM: W points into shared memory (plain loads) instead of global memory (read-only loads)
 __device__ __forceinline__ void slab_gemv(const float* vin, int nrows, const __half* W, int R, float* red, float* part) {
     const int tid = threadIdx.x;
     const int cc = R >> 3, nrg = kPT / cc, rg = tid / cc, c = tid - rg * cc;
@@ -353,7 +356,8 @@ __device__ __forceinline__ void slab_gemv(const float* vin, int nrows, const __h
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const int l = l0 + u * nrg;
-                wv[u] = l < nrows ? __ldg(reinterpret_cast<const uint4*>(W + (long long)l * R) + c) : make_uint4(0, 0, 0, 0);
+                const uint4* src = reinterpret_cast<const uint4*>(W + (long long)l * R) + c;
+                wv[u] = l < nrows ? (SM ? *src : __ldg(src)) : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
@@ -383,7 +387,7 @@ __device__ __forceinline__ void slab_gemv(const float* vin, int nrows, const __h
 
 // For this CTA's columns d = j0 + l (l < ncols, ncols % 8 == 0) and every group f < G:
 // fin(f, l, r16(sum over the group's hidden units u of h[f*L + u] * W2[f*L + u][d])).
-template <typename Fin>
+template <bool SM, typename Fin>
 __device__ __forceinline__ void cols_gemv(const float* h, int G, int L, const __half* W2, int D, int j0, int ncols, Fin fin) {
     const int tid = threadIdx.x, rs = tid & 7;
     const int nch = ncols >> 3;
@@ -400,7 +404,8 @@ __device__ __forceinline__ void cols_gemv(const float* h, int G, int L, const __
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
                         const int l = l0 + 8 * u;
-                        wv[u] = l < L ? __ldg(reinterpret_cast<const uint4*>(W2 + ((long long)f * L + l) * D + j0) + c) : make_uint4(0, 0, 0, 0);
+                        const uint4* src = reinterpret_cast<const uint4*>(W2 + ((long long)f * L + l) * D + j0) + c;
+                        wv[u] = l < L ? (SM ? *src : __ldg(src)) : make_uint4(0, 0, 0, 0);
                     }
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
@@ -449,9 +454,60 @@ __global__ void __launch_bounds__(kPT) v6_att_pre_kernel(const AttPre a) {
     __shared__ float sh16[kPT / 32];
     const int j0 = rank * a.rows;
     const int nrows = max(0, min(a.D, j0 + a.rows) - j0);     // multiple of 8
+    // a.wsm: this CTA's slices of the weights in shared memory, fetched by cp.async while the LayerNorm runs:
+    //   sw1 [nrows][R1] (later dw2's columns [R3][ld]), sw2 [R1][ld], sdw1 [nrows][R3];  ld = rows + 8 halves keeps
+    //   the eight rows a warp reads at once on different banks.  Without it every stage paid one or more round
+    //   trips to L2 / DRAM per group of rows (the launch cannot start early enough for a prefetch to land: a CTA of
+    //   512 threads needs a whole SM's registers), 25 us per layer; with it the stages read shared memory.
+    const int ld = a.rows + 8;
+    __half* sw1 = reinterpret_cast<__half*>(red + 4096);
+    __half* sw2 = sw1 + max(a.rows * R1, R3 * ld);
+    __half* sdw1 = sw2 + R1 * ld;
+    auto cp16 = [](void* dst, const void* src) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+    };
+    // contiguous copy of `halves` fp16 values (a multiple of 8), and a copy of `nr` rows of `nrows` values each (the
+    // row length in 16-byte pieces is a power of two for the usual D / 16 = 256: a shift instead of a division)
+    auto copy_flat = [&](__half* dst, const __half* src, int halves) {
+        for (int i = tid; i < (halves >> 3); i += kPT) cp16(dst + i * 8, src + i * 8);
+    };
+    auto copy_rows = [&](__half* dst, const __half* src, int nr, int src_ld, int dst_ld) {
+        const int per = nrows >> 3;
+        if ((per & (per - 1)) == 0 && per > 0) {
+            const int sh = 31 - __clz(per);
+            for (int i = tid; i < nr * per; i += kPT) {
+                const int r = i >> sh, c = i & (per - 1);
+                cp16(dst + (long long)r * dst_ld + c * 8, src + (long long)r * src_ld + c * 8);
+            }
+        } else {
+            for (int i = tid; i < nr * per; i += kPT) {
+                const int r = i / per, c = i - r * per;
+                cp16(dst + (long long)r * dst_ld + c * 8, src + (long long)r * src_ld + c * 8);
+            }
+        }
+    };
+    auto commit = []() { asm volatile("cp.async.commit_group;" ::: "memory"); };
+    // the per-channel constants of this CTA's rows and the previous token's vector, staged with the first group:
+    // [ln w | ln b | maa x | state | maa 0..4] fp16 and [decay] fp32, `rows` entries each
+    __half* svec = sdw1 + a.rows * R3;
+    float* sdecay = reinterpret_cast<float*>(svec + 9 * a.rows);
 
     pdl_open();
-    {   // weights of this CTA, toward L2: its rows of w1 / dw1, its 16-byte column pieces of w2 / dw2
+    if (a.wsm) {
+        copy_flat(sw1, a.w1 + (long long)j0 * R1, nrows * R1);
+        copy_flat(svec, a.ln_w + j0, nrows);
+        copy_flat(svec + a.rows, a.ln_b + j0, nrows);
+        copy_flat(svec + 2 * a.rows, a.maa_x + j0, nrows);
+        copy_flat(svec + 3 * a.rows, a.state + j0, nrows);
+#pragma unroll
+        for (int f = 0; f < 5; ++f) copy_flat(svec + (4 + f) * a.rows, a.maa[f] + j0, nrows);
+        copy_flat(reinterpret_cast<__half*>(sdecay), reinterpret_cast<const __half*>(a.decay + j0), nrows * 2);
+        commit();
+        copy_rows(sw2, a.w2 + j0, R1, a.D, ld);
+        commit();
+        copy_flat(sdw1, a.dw1 + (long long)j0 * R3, nrows * R3);
+        commit();
+    } else {   // weights of this CTA, toward L2: its rows of w1 / dw1, its 16-byte column pieces of w2 / dw2
         const char* b1 = reinterpret_cast<const char*>(a.w1 + (long long)j0 * R1);
         for (long long o = (long long)tid * 128; o < (long long)nrows * R1 * 2; o += (long long)kPT * 128) l2_line(b1 + o);
         const char* b3 = reinterpret_cast<const char*>(a.dw1 + (long long)j0 * R3);
@@ -494,15 +550,25 @@ __global__ void __launch_bounds__(kPT) v6_att_pre_kernel(const AttPre a) {
                 }
             }
         }
-        const float rstd = rsqrtf(block_sum512(q, sh16) / float(a.D) + 1e-5f);
+        if (a.wsm) asm volatile("cp.async.wait_group 2;" ::: "memory");     // the first group (w1, the vectors): the
+        const float rstd = rsqrtf(block_sum512(q, sh16) / float(a.D) + 1e-5f);    // barriers of the sum publish them
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int j8 = (tid + i * kPT) * 8;
             if (j8 >= j0 && j8 < j0 + nrows) {
-                const uint4 s4 = __ldcg(reinterpret_cast<const uint4*>(a.state) + (j8 >> 3));
-                const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(a.ln_w) + (j8 >> 3));
-                const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(a.ln_b) + (j8 >> 3));
-                const uint4 m4 = __ldg(reinterpret_cast<const uint4*>(a.maa_x) + (j8 >> 3));
+                uint4 s4, w4, b4, m4;
+                if (a.wsm) {                     // staged before the wait (the first copy group has landed: see below)
+                    const int o = j8 - j0;
+                    w4 = *reinterpret_cast<const uint4*>(svec + o);
+                    b4 = *reinterpret_cast<const uint4*>(svec + a.rows + o);
+                    m4 = *reinterpret_cast<const uint4*>(svec + 2 * a.rows + o);
+                    s4 = *reinterpret_cast<const uint4*>(svec + 3 * a.rows + o);
+                } else {
+                    s4 = __ldcg(reinterpret_cast<const uint4*>(a.state) + (j8 >> 3));
+                    w4 = __ldg(reinterpret_cast<const uint4*>(a.ln_w) + (j8 >> 3));
+                    b4 = __ldg(reinterpret_cast<const uint4*>(a.ln_b) + (j8 >> 3));
+                    m4 = __ldg(reinterpret_cast<const uint4*>(a.maa_x) + (j8 >> 3));
+                }
                 const __half* hx = reinterpret_cast<const __half*>(&xv4[i]);
                 const __half* hs = reinterpret_cast<const __half*>(&s4);
                 const __half* hw = reinterpret_cast<const __half*>(&w4);
@@ -531,33 +597,60 @@ __global__ void __launch_bounds__(kPT) v6_att_pre_kernel(const AttPre a) {
     __syncthreads();
 
     // ---- xxx @ w1 -> tanh -> five offsets -> wx, kx, vx, rx, gx (model.py:1268-1276) ----------
-    slab_gemv(vin, nrows, a.w1 + (long long)j0 * R1, R1, red, part1);
+    if (a.wsm) {
+        asm volatile("cp.async.wait_group 2;" ::: "memory");         // w1 has landed
+        __syncthreads();
+        slab_gemv<true>(vin, nrows, sw1, R1, red, part1);
+        copy_rows(sw1, a.dw2 + j0, R3, a.D, ld);                     // w1's room is free: dw2's columns go there
+        commit();
+    } else {
+        slab_gemv<false>(vin, nrows, a.w1 + (long long)j0 * R1, R1, red, part1);
+    }
     cluster.sync();
     for (int c = tid; c < R1; c += kPT) {
         float s = 0.f;
         for (int q = 0; q < a.ncta; ++q) s += cluster.map_shared_rank(part1, q)[c];
         h[c] = r16(tanhf(r16(s)));
     }
-    __syncthreads();
-    cols_gemv(h, 5, a.Lm, a.w2, a.D, j0, nrows, [&](int f, int l, float m) {
-        const float v = r16(xxs[l] + r16(dds[l] * r16(__half2float(a.maa[f][j0 + l]) + m)));
+    auto mix_out = [&](int f, int l, float m) {
+        const float mf = __half2float(a.wsm ? svec[(4 + f) * a.rows + l] : a.maa[f][j0 + l]);
+        const float v = r16(xxs[l] + r16(dds[l] * r16(mf + m)));
         a.out[f][j0 + l] = __float2half_rn(v);
         if (f == 0) vin[l] = v;                 // wx: the input of the decay product
-    });
+    };
+    if (a.wsm) {
+        asm volatile("cp.async.wait_group 2;" ::: "memory");         // w2 has landed (dw1, dw2 may still be on their way)
+        __syncthreads();
+        cols_gemv<true>(h, 5, a.Lm, sw2, ld, 0, nrows, mix_out);
+    } else {
+        __syncthreads();
+        cols_gemv<false>(h, 5, a.Lm, a.w2, a.D, j0, nrows, mix_out);
+    }
     __syncthreads();
 
     // ---- w = exp(-exp(time_decay + tanh(wx @ dw1) @ dw2)) (model.py:1286-1287) ---------------
-    slab_gemv(vin, nrows, a.dw1 + (long long)j0 * R3, R3, red, part3);
+    if (a.wsm) {
+        asm volatile("cp.async.wait_group 1;" ::: "memory");         // dw1 has landed
+        __syncthreads();
+        slab_gemv<true>(vin, nrows, sdw1, R3, red, part3);
+    } else {
+        slab_gemv<false>(vin, nrows, a.dw1 + (long long)j0 * R3, R3, red, part3);
+    }
     cluster.sync();
     for (int c = tid; c < R3; c += kPT) {
         float s = 0.f;
         for (int q = 0; q < a.ncta; ++q) s += cluster.map_shared_rank(part3, q)[c];
         h[c] = r16(tanhf(r16(s)));
     }
-    __syncthreads();
-    cols_gemv(h, 1, a.Ld, a.dw2, a.D, j0, nrows, [&](int, int l, float m) {
-        a.w_out[j0 + l] = expf(-expf(a.decay[j0 + l] + m));
-    });
+    auto decay_out = [&](int, int l, float m) { a.w_out[j0 + l] = expf(-expf((a.wsm ? sdecay[l] : a.decay[j0 + l]) + m)); };
+    if (a.wsm) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");         // dw2 has landed
+        __syncthreads();
+        cols_gemv<true>(h, 1, a.Ld, sw1, ld, 0, nrows, decay_out);
+    } else {
+        __syncthreads();
+        cols_gemv<false>(h, 1, a.Ld, a.dw2, a.D, j0, nrows, decay_out);
+    }
     cluster.sync();                             // nobody leaves while its shares are being read
 }
 
@@ -679,8 +772,28 @@ extern "C" int rwkv_v6_att_pre(int64_t D, int64_t Lm, int64_t Ld, const void* x,
         a.out[f] = static_cast<__half*>(out5[f]);
     }
     const int R1 = int(5 * Lm), R3 = int(Ld);
-    const size_t smem = size_t(3 * a.rows + R1 + R3 + (R1 > R3 ? R1 : R3) + 4096) * sizeof(float);
-    if (smem > 48 * 1024) return RWKV_ERR_UNSUPPORTED;
+    const size_t work = size_t(3 * a.rows + R1 + R3 + (R1 > R3 ? R1 : R3) + 4096) * sizeof(float);
+    if (work > 48 * 1024) return RWKV_ERR_UNSUPPORTED;
+    // the CTA's weight slices in shared memory when they fit next to the working arrays (RWKV_B200_V6_PRE_SMEM=0: never)
+    auto weights_bytes = [&](int rows) {
+        const size_t ldw = size_t(rows) + 8;
+        return (std::max(size_t(rows) * R1, size_t(R3) * ldw) + size_t(R1) * ldw + size_t(rows) * R3 + 9 * size_t(rows)) * sizeof(__half) +
+               size_t(rows) * sizeof(float);
+    };
+    static int use_wsm = -1;
+    if (use_wsm < 0) { const char* e = getenv("RWKV_B200_V6_PRE_SMEM"); use_wsm = (e != nullptr && e[0] == '0') ? 0 : 1; }
+    static bool big_smem[64] = {};           // the opt-in to more than 48 KB is per device
+    a.wsm = (use_wsm && work + weights_bytes(a.rows) <= 226 * 1024) ? 1 : 0;
+    if (a.wsm && dev >= 0 && !big_smem[dev]) {
+        if (cudaFuncSetAttribute(v6_att_pre_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) {
+            cudaGetLastError();
+            a.wsm = 0;
+        } else {
+            big_smem[dev] = true;
+        }
+    }
+    if (dev < 0) a.wsm = 0;
+    size_t smem = work + (a.wsm ? weights_bytes(a.rows) : 0);
     static int use_pdl = -1;
     if (use_pdl < 0) {
         const char* e = getenv("RWKV_B200_PDL");
@@ -706,6 +819,9 @@ extern "C" int rwkv_v6_att_pre(int64_t D, int64_t Lm, int64_t Ld, const void* x,
         big = 0;
         a.ncta = 8;
         a.rows = int(((D + 7) / 8 + 7) / 8 * 8);
+        a.wsm = (a.wsm && work + weights_bytes(a.rows) <= 226 * 1024) ? 1 : 0;
+        smem = work + (a.wsm ? weights_bytes(a.rows) : 0);
+        cfg.dynamicSmemBytes = smem;
         cfg.gridDim = dim3(8);
         attr[0].val.clusterDim.x = 8;
         e = cudaLaunchKernelEx(&cfg, v6_att_pre_kernel, a);
