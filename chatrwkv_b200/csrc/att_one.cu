@@ -380,7 +380,8 @@ __device__ __forceinline__ void slab_gemv(const float* vin, int nrows, const __h
     __syncthreads();
     for (int c2 = tid; c2 < R; c2 += kPT) {
         float s = 0.f;
-        for (int q = 0; q < nrg; ++q) s += red[q * R + c2];
+#pragma unroll 8
+        for (int q = 0; q < nrg; ++q) s += red[q * R + c2];      // unrolled: the loads go out together, only the adds chain
         part[c2] = s;
     }
 }
