@@ -349,6 +349,8 @@ class RWKV:
         self._stream = None
         self._mm = {}
         self._mm_pad = {}
+        self._fork_streams = []
+        self._batch_fork = os.environ.get("RWKV_B200_BATCH_FORK", "1") != "0"
         self._tile_cache = {}
         self._batch_graphs = {}
         # a matrix with more than 16384 in-features needs the decode kernel's second build: ask for it on every launch
@@ -846,6 +848,35 @@ class RWKV:
         y = out if out is not None else torch.empty((x.shape[0], M), dtype=torch.float16, device=x.device)
         return ops.mm8_seq_epi(x, wq, mx, rx, my, ry, y, epilogue, aux, aux2, out_scale)
 
+    def _mm_fork(self, jobs):
+        """Independent matmuls of a batched decode step (r / k / v, or the two of the channel mix) on parallel
+        streams: `jobs` = [(x, name, epilogue)]; returns the outputs.  At a handful of rows every matmul is a
+        latency-bound chain of three short kernels, and the chains of independent matmuls overlap instead of queueing
+        (also inside a captured graph: the side streams fork from and join the capturing stream)."""
+        outs = [torch.empty((x.shape[0], self.w[name].shape[1]), dtype=torch.float16, device=x.device) for x, name, _ in jobs]
+        if not self._batch_fork or len(jobs) < 2:
+            for (x, name, epi), y in zip(jobs, outs):
+                self._mm_epi(x, name, epi, out=y)
+            return outs
+        main = torch.cuda.current_stream(self.device)
+        while len(self._fork_streams) < len(jobs) - 1:
+            self._fork_streams.append(torch.cuda.Stream(self.device))
+        start = torch.cuda.Event()
+        start.record(main)
+        joins = []
+        for side, (x, name, epi), y in zip(self._fork_streams, jobs[1:], outs[1:]):
+            side.wait_event(start)
+            with torch.cuda.stream(side):
+                self._mm_epi(x, name, epi, out=y)
+                ev = torch.cuda.Event()
+                ev.record(side)
+                joins.append(ev)
+        x, name, epi = jobs[0]
+        self._mm_epi(x, name, epi, out=outs[0])
+        for ev in joins:
+            main.wait_event(ev)
+        return outs
+
     def _att_seq_v4(self, x, st, i, rows=False):
         """cuda_att_seq (model.py:1346-1360): LayerNorm + mixes, r/k/v matmuls (sigmoid in the store), the WKV
         recurrence parallel in time with r * wkv in its store, output matmul with the residual in the store."""
@@ -857,10 +888,14 @@ class RWKV:
         self._ln_mix(T, x, st[i * 5 + 0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 0,
                      [w[att + "time_mix_k"], w[att + "time_mix_v"], w[att + "time_mix_r"]], [kx, vx, rx],
                      new_state=None if rows else new_sx, xx_out=new_sx if rows else None, rows=rows)
-        if self._world == 1:
+        if self._world == 1 and rows:
+            r, k, v = self._mm_fork([(rx, att + "receptance.weight", EPI_SIGMOID), (kx, att + "key.weight", EPI_STORE),
+                                     (vx, att + "value.weight", EPI_STORE)])
+        elif self._world == 1:
             r = self._mm_epi(rx, att + "receptance.weight", EPI_SIGMOID)
             k = self._mm_epi(kx, att + "key.weight", EPI_STORE)             # fp16 k, v: the kernel widens them, as
             v = self._mm_epi(vx, att + "value.weight", EPI_STORE)           # model.py:1355-1356 does before the op
+        if self._world == 1:
             if rows:        # T sequences of one step each: the operator's batch dimension, state [T, C]
                 ops.wkv4_seq(w[att + "time_decay"], w[att + "time_first"], k.view(T, 1, C), v.view(T, 1, C), k.view(T, 1, C),
                              st[i * 5 + 1], st[i * 5 + 2], st[i * 5 + 3], r=r.view(T, 1, C))
@@ -929,10 +964,14 @@ class RWKV:
                          [w[att + f"time_mix_{n}"] for n in "kvrg"], [kx, vx, rx, gx],
                          new_state=None if rows else new_sx, xx_out=new_sx if rows else None, rows=rows)
             decay = w[att + "time_decay"].reshape(-1)
-        r = self._mm_epi(rx, att + "receptance.weight", EPI_STORE)        # fp16-rounded r, k, v: the kernel widens them
-        k = self._mm_epi(kx, att + "key.weight", EPI_STORE)               # (model.py:1413, 1425-1427)
-        v = self._mm_epi(vx, att + "value.weight", EPI_STORE)
-        g = self._mm_epi(gx, att + "gate.weight", EPI_SILU)
+        if rows:    # fp16-rounded r, k, v: the kernel widens them (model.py:1413, 1425-1427)
+            r, k, v, g = self._mm_fork([(rx, att + "receptance.weight", EPI_STORE), (kx, att + "key.weight", EPI_STORE),
+                                        (vx, att + "value.weight", EPI_STORE), (gx, att + "gate.weight", EPI_SILU)])
+        else:
+            r = self._mm_epi(rx, att + "receptance.weight", EPI_STORE)
+            k = self._mm_epi(kx, att + "key.weight", EPI_STORE)
+            v = self._mm_epi(vx, att + "value.weight", EPI_STORE)
+            g = self._mm_epi(gx, att + "gate.weight", EPI_SILU)
         y = torch.empty((T, D), dtype=torch.float32, device=dev)
         S_in = st2[1] if st2[1].is_contiguous() else st2[1].contiguous()
         S = torch.empty_like(S_in)                  # the caller's state stays as it is, as with the reference's copy
@@ -973,8 +1012,11 @@ class RWKV:
                      [w[ffn + ("time_maa_k" if v6 else "time_mix_k")], w[ffn + ("time_maa_r" if v6 else "time_mix_r")]], [kx, rx],
                      new_state=None if rows else new_sx, xx_out=new_sx if rows else None, rows=rows)
         if self._world == 1:
-            r = self._mm_epi(rx, ffn + "receptance.weight", EPI_SIGMOID)
-            vx = self._mm_epi(kx, ffn + "key.weight", EPI_RELU_SQ)
+            if rows:
+                r, vx = self._mm_fork([(rx, ffn + "receptance.weight", EPI_SIGMOID), (kx, ffn + "key.weight", EPI_RELU_SQ)])
+            else:
+                r = self._mm_epi(rx, ffn + "receptance.weight", EPI_SIGMOID)
+                vx = self._mm_epi(kx, ffn + "key.weight", EPI_RELU_SQ)
             # x + r * (vx @ Wv), and the halving after every RESCALE_LAYER-th layer (model.py:1660-1662), in the store
             half = self.RESCALE_LAYER > 0 and (i + 1) % self.RESCALE_LAYER == 0
             return self._mm_epi(vx, ffn + "value.weight", EPI_MUL_RESIDUAL, aux=x, aux2=r, out_scale=0.5 if half else 1.0,
