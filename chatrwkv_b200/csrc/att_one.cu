@@ -493,6 +493,7 @@ __global__ void __launch_bounds__(kPT) v6_att_pre_kernel(const AttPre a) {
     __half* svec = sdw1 + a.rows * R3;
     float* sdecay = reinterpret_cast<float*>(svec + 9 * a.rows);
 
+    const bool dec = a.dw1 != nullptr;          // false: the token shift alone (the caller runs rwkv_v6_decay beside the matmuls)
     pdl_open();
     if (a.wsm) {
         copy_flat(sw1, a.w1 + (long long)j0 * R1, nrows * R1);
@@ -502,19 +503,19 @@ __global__ void __launch_bounds__(kPT) v6_att_pre_kernel(const AttPre a) {
         copy_flat(svec + 3 * a.rows, a.state + j0, nrows);
 #pragma unroll
         for (int f = 0; f < 5; ++f) copy_flat(svec + (4 + f) * a.rows, a.maa[f] + j0, nrows);
-        copy_flat(reinterpret_cast<__half*>(sdecay), reinterpret_cast<const __half*>(a.decay + j0), nrows * 2);
+        if (dec) copy_flat(reinterpret_cast<__half*>(sdecay), reinterpret_cast<const __half*>(a.decay + j0), nrows * 2);
         commit();
         copy_rows(sw2, a.w2 + j0, R1, a.D, ld);
         commit();
-        copy_flat(sdw1, a.dw1 + (long long)j0 * R3, nrows * R3);
-        commit();
+        if (dec) copy_flat(sdw1, a.dw1 + (long long)j0 * R3, nrows * R3);
+        commit();                                                     // (an empty group keeps the wait counts below)
     } else {   // weights of this CTA, toward L2: its rows of w1 / dw1, its 16-byte column pieces of w2 / dw2
         const char* b1 = reinterpret_cast<const char*>(a.w1 + (long long)j0 * R1);
         for (long long o = (long long)tid * 128; o < (long long)nrows * R1 * 2; o += (long long)kPT * 128) l2_line(b1 + o);
         const char* b3 = reinterpret_cast<const char*>(a.dw1 + (long long)j0 * R3);
-        for (long long o = (long long)tid * 128; o < (long long)nrows * R3 * 2; o += (long long)kPT * 128) l2_line(b3 + o);
+        for (long long o = (long long)tid * 128; dec && o < (long long)nrows * R3 * 2; o += (long long)kPT * 128) l2_line(b3 + o);
         const int lines = (nrows * 2 + 127) / 128;
-        for (int i = tid; i < (R1 + R3) * lines; i += kPT) {
+        for (int i = tid; i < (R1 + (dec ? R3 : 0)) * lines; i += kPT) {
             const int row = i / lines, ln = i - row * lines;
             const __half* base = row < R1 ? a.w2 + (long long)row * a.D : a.dw2 + (long long)(row - R1) * a.D;
             l2_line(reinterpret_cast<const char*>(base + j0) + ln * 128);
@@ -602,7 +603,7 @@ __global__ void __launch_bounds__(kPT) v6_att_pre_kernel(const AttPre a) {
         asm volatile("cp.async.wait_group 2;" ::: "memory");         // w1 has landed
         __syncthreads();
         slab_gemv<true>(vin, nrows, sw1, R1, red, part1);
-        copy_rows(sw1, a.dw2 + j0, R3, a.D, ld);                     // w1's room is free: dw2's columns go there
+        if (dec) copy_rows(sw1, a.dw2 + j0, R3, a.D, ld);            // w1's room is free: dw2's columns go there
         commit();
     } else {
         slab_gemv<false>(vin, nrows, a.w1 + (long long)j0 * R1, R1, red, part1);
@@ -626,6 +627,10 @@ __global__ void __launch_bounds__(kPT) v6_att_pre_kernel(const AttPre a) {
     } else {
         __syncthreads();
         cols_gemv<false>(h, 5, a.Lm, a.w2, a.D, j0, nrows, mix_out);
+    }
+    if (!dec) {
+        cluster.sync();                         // nobody leaves while its share of the first product is being read
+        return;
     }
     __syncthreads();
 
@@ -740,11 +745,13 @@ extern "C" int rwkv_v6_att_pre(int64_t D, int64_t Lm, int64_t Ld, const void* x,
                                const float* time_decay, void* xx_out, void* d_out, void* const* out5, float* w_out,
                                void* stream) {
     RWKV_CHECK_ARG(D >= 8 && D % 8 == 0 && Lm >= 1 && Ld >= 1);
-    RWKV_CHECK_ARG(x && state && new_state && ln_w && ln_b && maa_x && maa5 && tm_w1 && tm_w2 && td_w1 && td_w2 &&
-                   time_decay && xx_out && d_out && out5 && w_out);
+    RWKV_CHECK_ARG(x && state && new_state && ln_w && ln_b && maa_x && maa5 && tm_w1 && tm_w2 && xx_out && d_out && out5);
+    // the four decay arguments all given, or all NULL: the token shift alone, rwkv_v6_decay to follow
+    const bool with_decay = td_w1 != nullptr;
+    RWKV_CHECK_ARG((td_w2 != nullptr) == with_decay && (time_decay != nullptr) == with_decay && (w_out != nullptr) == with_decay);
     if (D > 8 * 2 * kPT || (5 * Lm) % 8 != 0 || Ld % 8 != 0 || 5 * Lm > 1024 || Ld > 1024) return RWKV_ERR_UNSUPPORTED;
     const void* al[] = {x, state, new_state, ln_w, ln_b, maa_x, tm_w1, tm_w2, td_w1, td_w2, xx_out, d_out};
-    for (const void* p : al) RWKV_CHECK_ALIGN(p, 16);
+    for (const void* p : al) RWKV_CHECK_ALIGN(p, 16);            // (NULL passes)
     AttPre a = {};
     a.D = int(D); a.Lm = int(Lm); a.Ld = int(Ld);
     // 16 CTAs (a non-portable cluster size) halve every CTA's share of the weights; 8 where the

@@ -351,6 +351,7 @@ class RWKV:
         self._mm_pad = {}
         self._fork_streams = []
         self._batch_fork = os.environ.get("RWKV_B200_BATCH_FORK", "1") != "0"
+        self._v6_decay_fork = os.environ.get("RWKV_B200_V6_DECAY_FORK", "1") != "0"
         self._tile_cache = {}
         self._batch_graphs = {}
         # a matrix with more than 16384 in-features needs the decode kernel's second build: ask for it on every launch
@@ -735,15 +736,21 @@ class RWKV:
                 out5 = ptrs([b.m0, b.m1, b.m2, b.m3, b.m4])
                 keep += [maa5, out5]
                 ws = self._lora_ws
-                if (5 * Lm) % 8 == 0 and Ld % 8 == 0 and D <= 8192:
-                    # token shift and decay as one single-cluster launch
-                    plan.append(lambda s=s, att=att, ln1=ln1, Lm=Lm, Ld=Ld, maa5=maa5, out5=out5: check(
+                fused = (5 * Lm) % 8 == 0 and Ld % 8 == 0 and D <= 8192
+                split = fused and self._v6_decay_fork
+                run_decay = lambda att=att, Ld=Ld, ws=ws: check(
+                    L.rwkv_v6_decay(D, Ld, b.m0.data_ptr(), w[att + "time_decay_w1"].data_ptr(),
+                                    w[att + "time_decay_w2"].data_ptr(), w[att + "time_decay"].data_ptr(), ws.data_ptr(),
+                                    ws.numel(), b.wdec.data_ptr(), stream()), "v6_decay")
+                if fused:
+                    # token shift (and, unless it runs beside the matmuls, the decay) as one single-cluster launch
+                    dw = [None] * 3 if split else [w[att + "time_decay_" + n].data_ptr() for n in ("w1", "w2")] + [w[att + "time_decay"].data_ptr()]
+                    plan.append(lambda s=s, att=att, ln1=ln1, Lm=Lm, Ld=Ld, maa5=maa5, out5=out5, dw=dw, split=split: check(
                         L.rwkv_v6_att_pre(D, Lm, Ld, b.x.data_ptr(), sin[s].data_ptr(), sout[s].data_ptr(), ln1[0].data_ptr(),
                                           ln1[1].data_ptr(), w[att + "time_maa_x"].data_ptr(), maa5,
                                           w[att + "time_maa_w1"].data_ptr(), w[att + "time_maa_w2"].data_ptr(),
-                                          w[att + "time_decay_w1"].data_ptr(), w[att + "time_decay_w2"].data_ptr(),
-                                          w[att + "time_decay"].data_ptr(), b.xln.data_ptr(), b.dd.data_ptr(), out5,
-                                          b.wdec.data_ptr(), stream()), "v6_att_pre"))
+                                          dw[0], dw[1], dw[2], b.xln.data_ptr(), b.dd.data_ptr(), out5,
+                                          None if split else b.wdec.data_ptr(), stream()), "v6_att_pre"))
                 else:
                     plan.append(lambda s=s, att=att, ln1=ln1, Lm=Lm, maa5=maa5, out5=out5, ws=ws: check(
                         L.rwkv_v6_token_shift(D, Lm, b.x.data_ptr(), sin[s].data_ptr(), sout[s].data_ptr(), ln1[0].data_ptr(),
@@ -751,12 +758,29 @@ class RWKV:
                                               w[att + "time_maa_w1"].data_ptr(), w[att + "time_maa_w2"].data_ptr(),
                                               ws.data_ptr(), ws.numel(), b.xln.data_ptr(), b.dd.data_ptr(), out5, stream()),
                         "v6_token_shift"))
-                    plan.append(lambda att=att, Ld=Ld, ws=ws: check(
-                        L.rwkv_v6_decay(D, Ld, b.m0.data_ptr(), w[att + "time_decay_w1"].data_ptr(),
-                                        w[att + "time_decay_w2"].data_ptr(), w[att + "time_decay"].data_ptr(), ws.data_ptr(),
-                                        ws.numel(), b.wdec.data_ptr(), stream()), "v6_decay"))
+                    plan.append(run_decay)
+                if split:
+                    # the decay only feeds the recurrence: its two small launches run on a side stream beside the
+                    # r / k / v / g matmuls (which leave a fifth of the SM slots free) and join before rwkv_wkv56_one
+                    joined = [None]
+
+                    def fork_decay(run_decay=run_decay, joined=joined):
+                        main = torch.cuda.current_stream(dev)
+                        if not self._fork_streams:
+                            self._fork_streams.append(torch.cuda.Stream(dev))
+                        side = self._fork_streams[0]
+                        start = torch.cuda.Event()
+                        start.record(main)
+                        side.wait_event(start)
+                        with torch.cuda.stream(side):
+                            run_decay()
+                            joined[0] = torch.cuda.Event()
+                            joined[0].record(side)
+                    plan.append(fork_decay)
                 gemv([P(b.m3, att + "receptance.weight", b.r, EPI_STORE), P(b.m1, att + "key.weight", b.k, EPI_STORE),
                       P(b.m2, att + "value.weight", b.v, EPI_STORE), P(b.m4, att + "gate.weight", b.g, EPI_SILU)])
+                if split:
+                    plan.append(lambda joined=joined: torch.cuda.current_stream(dev).wait_event(joined[0]))
                 decay = b.wdec
             else:
                 mix = lambda n: w[att + "time_mix_" + n]
@@ -848,31 +872,34 @@ class RWKV:
         y = out if out is not None else torch.empty((x.shape[0], M), dtype=torch.float16, device=x.device)
         return ops.mm8_seq_epi(x, wq, mx, rx, my, ry, y, epilogue, aux, aux2, out_scale)
 
-    def _mm_fork(self, jobs):
+    def _mm_fork(self, jobs, extra=None):
         """Independent matmuls of a batched decode step (r / k / v, or the two of the channel mix) on parallel
         streams: `jobs` = [(x, name, epilogue)]; returns the outputs.  At a handful of rows every matmul is a
         latency-bound chain of three short kernels, and the chains of independent matmuls overlap instead of queueing
-        (also inside a captured graph: the side streams fork from and join the capturing stream)."""
+        (also inside a captured graph: the side streams fork from and join the capturing stream).  `extra`: one more
+        independent piece of work (a callable that launches on the current stream), run on a stream of its own."""
         outs = [torch.empty((x.shape[0], self.w[name].shape[1]), dtype=torch.float16, device=x.device) for x, name, _ in jobs]
-        if not self._batch_fork or len(jobs) < 2:
-            for (x, name, epi), y in zip(jobs, outs):
-                self._mm_epi(x, name, epi, out=y)
+        work = [lambda x=x, name=name, epi=epi, y=y: self._mm_epi(x, name, epi, out=y) for (x, name, epi), y in zip(jobs, outs)]
+        if extra is not None:
+            work.append(extra)
+        if not self._batch_fork or len(work) < 2:
+            for f in work:
+                f()
             return outs
         main = torch.cuda.current_stream(self.device)
-        while len(self._fork_streams) < len(jobs) - 1:
+        while len(self._fork_streams) < len(work) - 1:
             self._fork_streams.append(torch.cuda.Stream(self.device))
         start = torch.cuda.Event()
         start.record(main)
         joins = []
-        for side, (x, name, epi), y in zip(self._fork_streams, jobs[1:], outs[1:]):
+        for side, f in zip(self._fork_streams, work[1:]):
             side.wait_event(start)
             with torch.cuda.stream(side):
-                self._mm_epi(x, name, epi, out=y)
+                f()
                 ev = torch.cuda.Event()
                 ev.record(side)
                 joins.append(ev)
-        x, name, epi = jobs[0]
-        self._mm_epi(x, name, epi, out=outs[0])
+        work[0]()
         for ev in joins:
             main.wait_event(ev)
         return outs
@@ -949,15 +976,20 @@ class RWKV:
                                     m5.data_ptr(), maa5, out5, stream),
                   "v6_seq_mix")
             wx, kx, vx, rx, gx = mixes.unbind(0)
-            # per-token decay exp(-exp(time_decay + tanh(wx @ dw1) @ dw2))
+            # per-token decay exp(-exp(time_decay + tanh(wx @ dw1) @ dw2)): only the recurrence needs it, so in a
+            # batched decode step its four launches run beside the r / k / v / g matmuls
             dw1, dw2 = w[att + "time_decay_w1"], w[att + "time_decay_w2"]
-            h2 = h(T, dw1.shape[1])
-            torch.ops.rwkv.gemm_fp16_cublas(wx, dw1, h2)
-            check(L.rwkv_tanh_regroup_f16(T, 1, h2.shape[1], h2.data_ptr(), h2.data_ptr(), stream), "tanh")
-            d2 = h(T, D)
-            torch.ops.rwkv.gemm_fp16_cublas(h2, dw2, d2)
+            h2, d2 = h(T, dw1.shape[1]), h(T, D)
             decay = torch.empty((T, D), dtype=torch.float32, device=dev)
-            check(L.rwkv_v6_seq_decay(T, D, w[att + "time_decay"].data_ptr(), d2.data_ptr(), decay.data_ptr(), stream), "v6_seq_decay")
+
+            def decay_chain():
+                s_ = torch.cuda.current_stream(dev).cuda_stream
+                torch.ops.rwkv.gemm_fp16_cublas(wx, dw1, h2)
+                check(L.rwkv_tanh_regroup_f16(T, 1, h2.shape[1], h2.data_ptr(), h2.data_ptr(), s_), "tanh")
+                torch.ops.rwkv.gemm_fp16_cublas(h2, dw2, d2)
+                check(L.rwkv_v6_seq_decay(T, D, w[att + "time_decay"].data_ptr(), d2.data_ptr(), decay.data_ptr(), s_), "v6_seq_decay")
+            if not rows:
+                decay_chain()
         else:
             kx, vx, rx, gx = (torch.empty_like(x) for _ in range(4))
             self._ln_mix(T, x, st2[0], w[bb + "ln1.weight"], w[bb + "ln1.bias"], 0,
@@ -966,7 +998,8 @@ class RWKV:
             decay = w[att + "time_decay"].reshape(-1)
         if rows:    # fp16-rounded r, k, v: the kernel widens them (model.py:1413, 1425-1427)
             r, k, v, g = self._mm_fork([(rx, att + "receptance.weight", EPI_STORE), (kx, att + "key.weight", EPI_STORE),
-                                        (vx, att + "value.weight", EPI_STORE), (gx, att + "gate.weight", EPI_SILU)])
+                                        (vx, att + "value.weight", EPI_STORE), (gx, att + "gate.weight", EPI_SILU)],
+                                       extra=decay_chain if self.version == 6 else None)
         else:
             r = self._mm_epi(rx, att + "receptance.weight", EPI_STORE)
             k = self._mm_epi(kx, att + "key.weight", EPI_STORE)

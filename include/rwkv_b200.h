@@ -484,6 +484,8 @@ int rwkv_wkv4_one(int64_t C, const float* t_decay, const float* t_first, const v
  * of a single 8-CTA cluster that exchanges the low-rank intermediates through distributed shared
  * memory; same values, no scratch.  Returns RWKV_ERR_UNSUPPORTED (and launches nothing) unless
  * 5*Lm and Ld are multiples of 8 and D <= 8192: callers then use the two calls above.
+ * With td_w1, td_w2, time_decay and w_out all NULL it does the token shift alone (a caller can then
+ * run rwkv_v6_decay on another stream beside the matmuls that only need the shifted vectors).
  * ------------------------------------------------------------------------------------- */
 size_t rwkv_v6_scratch_bytes(int64_t D, int64_t rank);
 int rwkv_v6_att_pre(int64_t D, int64_t Lm, int64_t Ld, const void* x, const void* state, void* new_state,

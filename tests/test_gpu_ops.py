@@ -403,6 +403,21 @@ def test_v6_token_shift_and_decay(ops, D, Lm, Ld):
             assert (out5b[f].cpu().float() - ref5[f].float()).abs().max() <= 2e-2, f
             assert (out5b[f].float() - out5[f].float()).abs().max() <= 8e-3, f
         assert (w_b.cpu() - ref_w).abs().max() <= 5e-3
+        # the token shift alone (no decay arguments): the same five vectors bit for bit, nothing written elsewhere
+        out5c = [torch.zeros(D, dtype=torch.float16, device="cuda") for _ in range(5)]
+        xx_c, dd_c, ns_c = (torch.zeros(D, dtype=torch.float16, device="cuda") for _ in range(3))
+        rc = lib().rwkv_v6_att_pre(D, Lm, Ld, dx.data_ptr(), dsx.data_ptr(), ns_c.data_ptr(), dlw.data_ptr(), dlb.data_ptr(),
+                                   dmx.data_ptr(), arr(dmaa), dw[0].data_ptr(), dw[1].data_ptr(), None, None, None,
+                                   xx_c.data_ptr(), dd_c.data_ptr(), arr(out5c), None, st)
+        torch.cuda.synchronize()
+        assert rc == 0
+        assert torch.equal(xx_c, xx_b) and torch.equal(dd_c, dd_b) and torch.equal(ns_c, ns_b)
+        for f in range(5):
+            assert torch.equal(out5c[f], out5b[f]), f
+        # decay arguments given in part: refused before any launch
+        assert lib().rwkv_v6_att_pre(D, Lm, Ld, dx.data_ptr(), dsx.data_ptr(), ns_c.data_ptr(), dlw.data_ptr(), dlb.data_ptr(),
+                                     dmx.data_ptr(), arr(dmaa), dw[0].data_ptr(), dw[1].data_ptr(), dw[2].data_ptr(), None, None,
+                                     xx_c.data_ptr(), dd_c.data_ptr(), arr(out5c), None, st) == -1
     else:
         assert rc == _lib_unsupported()
 
