@@ -489,6 +489,14 @@ def main():
         if c0 is not None:
             cb["config0"] = c0
 
+    # ---- one RWKV-4 14B-shape model column-sharded over all ranks (peer stores in the matmul epilogue), 64 tokens
+    graph_default = bool(model._use_graph)
+    sharded_14b = None
+    if world > 1 and not sharded and a.layers == 0 and a.shape == WORKLOAD and os.environ.get("RWKV_B200_BENCH_SHARDED", "1") != "0":
+        del model, state, logits
+        torch.cuda.empty_cache()
+        sharded_14b = sharded_14b_decode(dev, local_rank, rank, world, barrier, steps=64)
+
     if rank == 0:
         line = {
             "metric": metric, "value": (1 if sharded else world) * a.steps / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world,
@@ -503,18 +511,66 @@ def main():
             "e2e": {"value": (1 if sharded else world) * a.steps / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 8,
                     "d2h_bytes_per_step": V * 4},
             "gpu_launches": launches_default * a.steps * 2,
-            "decode_path": path_default, "graph": bool(model._use_graph),
+            "decode_path": path_default, "graph": graph_default,
             "arithmetic": "x*ry as 30-bit fixed point per vector, exact 64-bit integer sums" if path_default == "stream"
                           else "x*ry as 16-bit fixed point per CTA slice, exact 32-bit integer sums (other_decode_paths: fp32)",
             "other_decode_paths": other, "sampling": sampling,
             "prefill": {"tokens": a.prompt, "ms": prefill_ms, "tokens_per_s": a.prompt / (prefill_ms / 1e3)},
             "clocks": clocks, "roofline": roof, "cpu_baseline": cb,
         }
+        if sharded_14b is not None:
+            line["sharded_14b"] = sharded_14b
         if a.layers > 0:
             line["note"] = f"profiling run with {a.layers} layers: not a benchmark result"
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def sharded_14b_decode(dev, local_rank, rank, world, barrier, steps=64):
+    """Greedy decode of ONE RWKV-4 14B-shape model whose matrices are split by output columns over all ranks
+    (every rank streams 1/world of the weights per token; the kernels store their columns into the peers' buffers
+    and wait, bounded, on arrival words).  Every rank takes part; returns the record on every rank (max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    from chatrwkv_b200 import synth
+    from chatrwkv_b200.model import RWKV
+    rec = {"n_gpus": world, "steps": steps, "exchange": "peer stores from the matmul epilogue + arrival words (no collective)"}
+    ok = 1
+    try:
+        L, D, Fn, V = synth.SHAPES["v4-14b"]
+        ck = synth.make_checkpoint(4, L, D, Fn, V, seed=1002, device=dev)
+        m = RWKV(ck, f"cuda:{local_rank} fp16i8", verbose=False, shard_rank=rank, shard_world=world)
+        del ck
+        torch.cuda.empty_cache()
+        tok = torch.zeros(1, dtype=torch.int64, device=dev)
+        st = None
+        for _ in range(6):
+            lg, st = m.forward(tok, st)
+            tok = torch.argmax(lg).reshape(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            lg, st = m.forward(tok, st)
+            tok = torch.argmax(lg).reshape(1)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        err = int(m.peer_error())
+        graph = bool(m._use_graph)
+    except Exception as e:                      # reported, and the other ranks still meet this rank below
+        ok, ms, err, graph = 0, 0.0, -1, False
+        rec["error"] = f"{type(e).__name__}: {e}"[:200]
+    t = torch.tensor([ms, float(err != 0), float(1 - ok)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, any_err, any_fail = t.tolist()
+    if any_fail:
+        rec.setdefault("error", "another rank failed")
+        return rec
+    rec.update({"tok_s": steps / (ms / 1e3), "ms_per_step": ms / steps, "wait_ran_out": bool(any_err), "graph": graph,
+                "shape": "rwkv v4-14b (L=40, D=5120, ffn=20480)"})
+    return rec
 
 
 def operator_sweep(dev, iters=24, part="all", only_T=0):
