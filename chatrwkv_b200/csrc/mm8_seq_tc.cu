@@ -483,10 +483,11 @@ __global__ void __launch_bounds__(256) mm8_seq_reduce(int T, int M, int m_pad, i
 
 int g_tc_single = 0;
 
-// K splits of a launch: 1 unless it is a single row tile whose column tiles leave most SMs idle.
+// K splits of a launch: 1 unless its output tiles (a few row tiles x the column tiles) leave most SMs idle.
 static inline int tc_ksplit(int64_t B, int64_t N, int64_t M) {
-    if (B > BM) return 1;
-    const int tiles = int((M + BN - 1) / BN), nkb = int((N + BK - 1) / BK);
+    const int64_t tiles64 = ((M + BN - 1) / BN) * ((B + BM - 1) / BM);
+    if (tiles64 > rwkv_sm_count() / 2) return 1;
+    const int tiles = int(tiles64), nkb = int((N + BK - 1) / BK);
     int ks = rwkv_sm_count() / tiles;
     if (ks > 8) ks = 8;
     if (ks > nkb / 4) ks = nkb / 4;

@@ -1148,10 +1148,33 @@ class RWKV:
             self._ln_mix(B, x, None, w["ln_out.weight"], w["ln_out.bias"], 0, [], [], xx_out=xln)
             return self._mm_epi(xln, "head.weight", EPI_STORE).float(), state
 
+    def _stage_tokens(self, tokens):
+        """Token ids to the device through pinned memory (two slots, reused in turn): a copy from pageable memory would
+        make the host wait for everything queued before it, so consecutive chunks of a prompt could not be queued ahead."""
+        T = len(tokens)
+        if not hasattr(self, "_seq_tok"):
+            self._seq_tok = [None, None]
+            self._seq_tok_ev = [None, None]
+            self._seq_tok_slot = 0
+        slot = self._seq_tok_slot = 1 - self._seq_tok_slot
+        if self._seq_tok_ev[slot] is not None:
+            self._seq_tok_ev[slot].synchronize()
+        if self._seq_tok[slot] is None or self._seq_tok[slot].numel() < T:
+            self._seq_tok[slot] = torch.empty(max(4096, T), dtype=torch.int64).pin_memory()
+            self._seq_tok_ev[slot] = torch.cuda.Event()
+        host = self._seq_tok[slot][:T]
+        host.copy_(torch.tensor(tokens, dtype=torch.int64))
+        idx = torch.empty(T, dtype=torch.int64, device=self.device)
+        idx.copy_(host, non_blocking=True)
+        self._seq_tok_ev[slot].record(torch.cuda.current_stream(self.device))
+        return idx
+
     def _forward_seq(self, tokens, state, full_output):
+        # (Replaying a prompt length that comes back as a CUDA graph was tried: with the copies of the state in and out
+        # it was slower than these direct launches at 64, 256 and 1024 tokens.)
         w, a = self.w, self.args
         state = list(state)
-        idx = torch.tensor(tokens, dtype=torch.int64, device=self.device)
+        idx = self._stage_tokens(tokens)
         x = w["emb.weight"].index_select(0, idx)
         for i in range(a.n_layer):
             if self.version == 4:
