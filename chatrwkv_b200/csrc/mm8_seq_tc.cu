@@ -533,7 +533,9 @@ int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_st
     const int vec_x = (reinterpret_cast<uintptr_t>(x) % 16 == 0 && x_stride % 8 == 0) ? 1 : 0;
     const int vec_v = (reinterpret_cast<uintptr_t>(ry) % 16 == 0 && reinterpret_cast<uintptr_t>(my) % 16 == 0) ? 1 : 0;
     const int groups = int((B + 7) / 8);                                       // 8-row groups
-    int shares = std::min(kMaxSumShares, std::max(1, 2 * rwkv_sm_count() / groups));
+    static int share_mul = -1;
+    if (share_mul < 0) { const char* e = getenv("RWKV_B200_PREP_SHARES"); share_mul = e ? atoi(e) : 8; }
+    int shares = std::min(kMaxSumShares, std::max(1, share_mul * rwkv_sm_count() / groups));
     shares = std::max(1, std::min(shares, nkb_all * 8 / 32));                  // at least one chunk per thread
     const int chunks_per = (nkb_all * 8 + shares - 1) / shares;
     shares = (nkb_all * 8 + chunks_per - 1) / chunks_per;                      // no empty share

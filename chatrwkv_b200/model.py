@@ -387,24 +387,27 @@ class RWKV:
 
     # -----------------------------------------------------------------------------------
     def _zero_state(self):
-        """model.py:1448-1471."""
+        """model.py:1448-1471.  The entries are rows of two zero-filled allocations (one per dtype, rows padded to 256
+        bytes) instead of five tensors per layer: three fill launches for the whole list."""
         a, dev = self.args, self.device
+        L = a.n_layer
+        pad = lambda n, per: (n + per - 1) // per * per
+        h = torch.zeros((L, 2, pad(a.n_embd, 128)), dtype=torch.float16, device=dev)
         st = []
-        for i in range(a.n_layer):
-            if self.version == 4:
-                st += [torch.zeros(a.n_embd, dtype=torch.float16, device=dev),
-                       torch.zeros(a.n_att, dtype=torch.float32, device=dev),
-                       torch.zeros(a.n_att, dtype=torch.float32, device=dev),
-                       torch.zeros(a.n_att, dtype=torch.float32, device=dev) - 1e30,
-                       torch.zeros(a.n_embd, dtype=torch.float16, device=dev)]
+        if self.version == 4:
+            f = torch.zeros((L, 3, pad(a.n_att, 64)), dtype=torch.float32, device=dev)
+            f[:, 2].fill_(-1e30)
+            for i in range(L):
+                st += [h[i, 0, :a.n_embd], f[i, 0, :a.n_att], f[i, 1, :a.n_att], f[i, 2, :a.n_att], h[i, 1, :a.n_embd]]
+            return st
+        N = a.n_att // a.n_head
+        S = None if a.time_state else torch.zeros((L, a.n_head, N, N), dtype=torch.float32, device=dev)
+        for i in range(L):
+            if a.time_state:
+                s = self.w[f"blocks.{i}.att.time_state"].transpose(1, 2).to(dtype=torch.float, device=dev).contiguous()
             else:
-                N = a.n_att // a.n_head
-                if a.time_state:
-                    s = self.w[f"blocks.{i}.att.time_state"].transpose(1, 2).to(dtype=torch.float, device=dev).contiguous()
-                else:
-                    s = torch.zeros((a.n_head, N, N), dtype=torch.float32, device=dev)
-                st += [torch.zeros(a.n_embd, dtype=torch.float16, device=dev), s,
-                       torch.zeros(a.n_embd, dtype=torch.float16, device=dev)]
+                s = S[i]
+            st += [h[i, 0, :a.n_embd], s, h[i, 1, :a.n_embd]]
         return st
 
     def forward(self, tokens, state, full_output=False):
