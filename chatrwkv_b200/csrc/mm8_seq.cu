@@ -102,12 +102,14 @@ int rwkv_mm8_seq_tc(int64_t B, int64_t N, int64_t M, const void* x, int64_t x_st
                     void* workspace, size_t workspace_bytes, void* stream);
 
 extern "C" void rwkv_mm8_seq_tc_set_single(int single);
+void rwkv_mm8_seq_tc_set_no_pair(int no_pair);
 static int g_seq_path = 0;      // 0 = automatic, 1 = CUDA cores only, 2 = tensor cores whenever the layout allows
 // bit 2 (value 4) of `path`: the tensor-core kernel multiplies fp16(x*ry) in one pass instead of the exact
-// hi + lo pair
+// hi + lo pair; bit 3 (value 8): one CTA per output tile always (never the CTA-pair form; same results)
 extern "C" void rwkv_mm8_seq_set_path(int path) {
     g_seq_path = path & 3;
     rwkv_mm8_seq_tc_set_single((path & 4) != 0);
+    rwkv_mm8_seq_tc_set_no_pair((path & 8) != 0);
 }
 constexpr int kTcMinRows = 8;   // below this the CUDA-core kernel; from here on the 128-row tensor-core tile (mostly padding up to
                                 // 64 rows, but 4x faster than the CUDA-core kernel already at 16 rows: W is converted once per CTA)

@@ -335,7 +335,9 @@ int rwkv_mm8_stream_take_error(uint32_t* sync_words, void* stream, int* error_ou
  * everything else (or workspace == NULL) runs on a CUDA-core kernel that accepts any layout.
  * rwkv_mm8_seq_set_path: 0 automatic, 1 CUDA cores only, 2 tensor cores whenever possible; adding 4
  * makes the tensor-core kernel multiply fp16(x*ry) in ONE pass instead of the exact hi + lo pair
- * (about 1e-4 of the output's RMS less accurate, 10-35 % faster at T = 1024; off by default).
+ * (about 1e-4 of the output's RMS less accurate, 10-35 % faster at T = 1024; off by default); adding 8
+ * keeps one CTA per output tile (by default launches with an even number of 128-row tiles and no K
+ * split run as clusters of two CTAs sharing one 256-row UMMA, tcgen05 cta_group::2; same results).
  * rwkv_mm8_seq_tc_take_error synchronises `stream` and returns/clears the workspace's error
  * word (1 if a bounded wait inside the tensor-core kernel gave up; outputs then undefined).
  * ------------------------------------------------------------------------------------- */

@@ -305,6 +305,38 @@ def test_mm8_seq_tensor_core_path(ops, T, N, M):
     assert ((y.float() - y2.float()).abs() <= y2.float().abs() * 2 ** -9 + 2e-4).all()
 
 
+@pytest.mark.parametrize("T,N,M", [(256, 320, 9728), (200, 200, 19464), (512, 128, 5000 * 8), (1024, 4096, 4096)])
+def test_mm8_seq_cta_pair_form(ops, T, N, M):
+    """Launches with an even number of 128-row tiles and no K split (more output tiles than half of the SMs) run as
+    clusters of two CTAs that share one 256-row UMMA (tcgen05 cta_group::2), each converting half of the B tile.
+    Same sums in the same order: bit-identical to the one-CTA form (set_path bit 3), and both match the oracle.
+    Includes a ragged last row tile and ragged N and M."""
+    import ctypes
+    from chatrwkv_b200 import _lib
+    from tests.util import packed_case
+    cpu, dev = packed_case(N, M, seed=N + M + T)
+    g = torch.Generator().manual_seed(T + 1)
+    x = torch.randn(T, N, generator=g).half()
+    xd = x.cuda()
+    y = torch.empty((T, M), dtype=torch.float16, device="cuda")
+    torch.ops.rwkv.mm8_seq(T, N, M, xd, *dev, y)
+    _lib.lib().rwkv_mm8_seq_set_path(8)
+    try:
+        y1 = torch.empty_like(y)
+        torch.ops.rwkv.mm8_seq(T, N, M, xd, *dev, y1)
+    finally:
+        _lib.lib().rwkv_mm8_seq_set_path(0)
+    torch.cuda.synchronize()
+    ws = ops.workspace(torch.device("cuda", torch.cuda.current_device()), 1024, "mm8_seq")
+    e = ctypes.c_int(0)
+    assert _lib.lib().rwkv_mm8_seq_tc_take_error(ws.data_ptr(), None, ctypes.byref(e)) == 0 and e.value == 0
+    assert torch.equal(y, y1)
+    if T * N * M <= 256 * 320 * 9728 * 4:           # the oracle's fp64 product in seconds
+        ref = orc.mm8_kernel(x, *cpu)
+        err = (y.float().cpu() - ref).abs()
+        assert (err <= ref.abs() * 2 ** -10 + 1e-4).all(), err.max().item()
+
+
 def test_mm8_seq_ignores_stale_scratch_rows(ops):
     """The operand images keep whatever the scratch held in the rows past T of the last 128-row tile
     (here: NaN patterns); no stored output may depend on them."""
