@@ -108,6 +108,7 @@ SIGNATURES = {
     "rwkv_ln_mix": (_i32, [_i64, _i64, _vp, _i64, _vp, _vp, _vp, _i32, _i32, C.POINTER(_vp), _i64, C.POINTER(_vp), _i64, _vp, _i64, _vp, _vp]),
     "rwkv_ln_mix_rows": (_i32, [_i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i32, _i32, C.POINTER(_vp), _i64, C.POINTER(_vp), _i64, _vp, _i64,
                                 _vp, _vp]),
+    "rwkv_embed_row": (_i32, [_i64, _i64, _vp, _i64, _vp, _vp, _vp]),
     "rwkv_wkv4_one": (_i32, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "rwkv_v6_scratch_bytes": (_sz, [_i64, _i64]),
     "rwkv_v6_att_pre": (_i32, [_i64, _i64, _i64] + [_vp] * 17),

@@ -4,6 +4,7 @@
 // (pkg/model.py:1044-1055).  Every torch op on fp16 tensors in the reference rounds once to
 // fp16; r16() marks the same rounding points here.
 #include "common.cuh"
+#include <algorithm>
 
 namespace {
 
@@ -221,6 +222,24 @@ __global__ void wkv4_one_kernel(int C, const float* __restrict__ t_decay, const 
     out[c] = __float2half_rn(__half2float(r[c]) * wkv);
 }
 
+// x = emb[token]: the embedding row of a decode step (model.py:1475), the first node of a token's CUDA graph.  The
+// launch that follows starts under it (programmatic dependent launch) and fills its weight ring meanwhile; a library
+// gather in this place is a full kernel boundary.  An id outside [0, V) reads row 0 or V - 1 instead of faulting.
+__global__ void __launch_bounds__(256) embed_row_kernel(int D, long long V, const __half* __restrict__ emb, long long row_stride,
+                                                        const long long* __restrict__ token, __half* __restrict__ out, int vec) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    long long t = *token;
+    t = t < 0 ? 0 : (t >= V ? V - 1 : t);
+    const __half* row = emb + t * row_stride;
+    if (vec) {
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < (D >> 3); i += gridDim.x * blockDim.x)
+            reinterpret_cast<uint4*>(out)[i] = __ldg(reinterpret_cast<const uint4*>(row) + i);
+    } else {
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < D; i += gridDim.x * blockDim.x) out[i] = row[i];
+    }
+}
+
 }  // namespace
 
 extern "C" int rwkv_ln_mix(int64_t T, int64_t D, const void* x, int64_t x_stride, const void* sx,
@@ -268,6 +287,17 @@ extern "C" int rwkv_ln_mix_rows(int64_t T, int64_t D, const void* x, int64_t x_s
     if (per <= 4) return rwkv_launch_pdl(ln_mix_kernel<4>, dim3(int(T)), dim3(kLnThreads), 0, st, a);
     if (per <= 16) return rwkv_launch_pdl(ln_mix_kernel<16>, dim3(int(T)), dim3(kLnThreads), 0, st, a);
     return rwkv_launch_pdl(ln_mix_kernel<kLnMaxPer>, dim3(int(T)), dim3(kLnThreads), 0, st, a);
+}
+
+extern "C" int rwkv_embed_row(int64_t D, int64_t V, const void* emb, int64_t row_stride, const int64_t* token, void* out,
+                              void* stream) {
+    RWKV_CHECK_ARG(D >= 1 && D <= INT32_MAX && V >= 1 && row_stride >= D && emb && token && out);
+    const int vec = (D % 8 == 0 && row_stride % 8 == 0 && reinterpret_cast<uintptr_t>(emb) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(out) % 16 == 0) ? 1 : 0;
+    const int per = vec ? int(D / 8) : int(D);
+    return rwkv_launch_pdl(embed_row_kernel, dim3(unsigned(std::min(8, (per + 255) / 256))), dim3(256), 0,
+                           static_cast<cudaStream_t>(stream), int(D), (long long)V, static_cast<const __half*>(emb),
+                           (long long)row_stride, reinterpret_cast<const long long*>(token), static_cast<__half*>(out), vec);
 }
 
 extern "C" int rwkv_wkv4_one(int64_t C, const float* t_decay, const float* t_first, const void* r,

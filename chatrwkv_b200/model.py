@@ -455,6 +455,10 @@ class RWKV:
         if torch.is_tensor(token):
             self._b.tok.copy_(token.reshape(1))
         else:
+            V = self.w["emb.weight"].shape[0]
+            if not -V <= token < V:             # as indexing the embedding matrix on the host would (model.py:1475)
+                raise IndexError(f"token id {token} is out of range for a vocabulary of {V}")
+            token %= V
             slot = self._tok_slot = (self._tok_slot + 1) % self._tok_host.numel()
             if self._tok_events[slot] is not None:
                 self._tok_events[slot].synchronize()
@@ -529,13 +533,19 @@ class RWKV:
         launches.append([ln(P(b.x, "head.weight", b.logits, EPI_STORE_F32), w["ln_out.weight"], w["ln_out.bias"], 2)])
         return launches
 
+    def _embed_row(self):
+        """x = emb[token] of a decode step, by a kernel of this library (the launch after it starts under it)."""
+        e = self.w["emb.weight"]
+        check(lib().rwkv_embed_row(e.shape[1], e.shape[0], e.data_ptr(), e.stride(0), self._b.tok.data_ptr(), self._b.x.data_ptr(),
+                                   torch.cuda.current_stream(self.device).cuda_stream), "embed_row")
+
     def _step_one_v4_sharded(self, cur):
         """One RWKV-4 token with every matmul split by output columns over the ranks: the same
         launches as `_launches_v4` on this rank's column slices, an all-gather of the fp16
         slices after each (r, k, v; x; ffn r, k; x; logits) -- four gathers per layer."""
         b, w, a = self._b, self.w, self.args
         G, R = self._world, self._rank
-        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
+        self._embed_row()
         sin, sout = self._st[cur], self._st[1 - cur]
         P, ln, wk = self._problem, ops.with_ln_mix, ops.with_wkv4
         D, Fn = a.n_embd, a.n_ffn
@@ -593,7 +603,7 @@ class RWKV:
         G, R = self._world, self._rank
         stream = torch.cuda.current_stream(self.device).cuda_stream
         pr.begin_token(4 * a.n_layer + 1, stream)
-        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
+        self._embed_row()
         sin, sout = self._st[cur], self._st[1 - cur]
         P, ln, wk = self._problem, ops.with_ln_mix, ops.with_wkv4
         D, Fn = a.n_embd, a.n_ffn
@@ -694,7 +704,7 @@ class RWKV:
         b, w = self._b, self.w
         if self._use_stream and self._stream is None and not self._build_stream():
             self._use_stream = False
-        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
+        self._embed_row()
         if self._use_stream:
             st = self._stream
             host, dev = st.tables[cur]
@@ -809,7 +819,7 @@ class RWKV:
 
     def _step_one_v56(self, cur):
         b, w = self._b, self.w
-        torch.index_select(w["emb.weight"], 0, b.tok, out=b.x.view(1, -1))
+        self._embed_row()
         if not hasattr(self, "_plans56"):
             self._plans56 = [self._plan_v56(0), self._plan_v56(1)]
         for op in self._plans56[cur]:

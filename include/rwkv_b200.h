@@ -453,6 +453,14 @@ int rwkv_ln_mix_rows(int64_t T, int64_t D, const void* x, int64_t x_stride, cons
                      void* xx_out, int64_t xx_stride, void* new_state, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * rwkv_embed_row: out[0..D) = emb[*token] (fp16; `token` a device int64), the embedding lookup that opens a
+ * decode step (pkg/model.py:1475 `x = w['emb.weight'][tokens[0]]`) as a kernel of this library, so that the
+ * launch after it starts under it.  An id outside [0, V) reads the nearest valid row.
+ * ------------------------------------------------------------------------------------- */
+int rwkv_embed_row(int64_t D, int64_t V, const void* emb, int64_t row_stride, const int64_t* token, void* out,
+                   void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * RWKV-4 one-step WKV — the fp32 island of att_one (pkg/model.py:1044-1055).
  * r (after sigmoid), k, v: fp16 [C]; t_decay = -exp(time_decay), t_first: fp32 [C];
  * aa, bb, pp: fp32 [C] updated in place; out = r * wkv in fp16 (the operand of the output
