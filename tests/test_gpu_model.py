@@ -150,6 +150,20 @@ def test_device_token_input():
     assert torch.equal(a, b)
 
 
+def test_token_id_range_follows_host_indexing():
+    """A token id indexes the embedding matrix as on the host (pkg/model.py:1475): negative ids count from the end,
+    ids outside [-V, V) raise IndexError before anything is launched."""
+    m, _ = _models("v4")
+    V = m.w["emb.weight"].shape[0]
+    a, _ = m.forward([V - 1], None)
+    a = a.clone()
+    b, _ = m.forward([-1], None)
+    assert torch.equal(a, b)
+    for bad in (V, V + 7, -V - 1):
+        with pytest.raises(IndexError):
+            m.forward([bad], None)
+
+
 def test_config0_shape_greedy_vs_oracle():
     """RWKV-4 169M shape (12 x 768, ffn 3072, vocab 50277): 64-token prompt, then greedy
     decoding.  Teacher-forced on the oracle's tokens: logits within 2e-2 at every step; the

@@ -627,3 +627,19 @@ def test_wkv56_time_parallel_matches_sequential_oracle(ops, which, T):
     assert (y2.cpu() - ref2).abs().max().item() <= 2e-4 * max(1.0, ref2.abs().max().item())
     torch.testing.assert_close(s_out.transpose(-1, -2).cpu(), s_ref2, rtol=2e-4, atol=2e-4)
     assert torch.equal(s_in, s_keep)
+
+
+@pytest.mark.parametrize("D,V", [(4096, 1000), (100, 7), (768, 50277)])
+def test_embed_row(ops, D, V):
+    """rwkv_embed_row copies the row a device-side token id names (pkg/model.py:1475); an id outside the vocabulary
+    reads the nearest valid row instead of faulting."""
+    from chatrwkv_b200._lib import check, lib
+    g = torch.Generator().manual_seed(D + V)
+    emb = torch.randn(V, D, generator=g).half().cuda()
+    out = torch.zeros(D, dtype=torch.float16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    for tok, row in ((0, 0), (V - 1, V - 1), (V // 2, V // 2), (V + 5, V - 1), (-3, 0)):
+        t = torch.tensor([tok], dtype=torch.int64, device="cuda")
+        check(lib().rwkv_embed_row(D, V, emb.data_ptr(), emb.stride(0), t.data_ptr(), out.data_ptr(), st), "embed_row")
+        torch.cuda.synchronize()
+        assert torch.equal(out, emb[row]), tok
